@@ -1,0 +1,900 @@
+// Bandwidth-bound kernels of the GPT stage program. All use 128-bit accesses, fp32 math and
+// grids sized against the 148 SMs of a B200; none of them allocates.
+#include "elementwise.cuh"
+#include "gemm_sm100.cuh"
+#include "sm100_common.cuh"
+
+namespace ethb {
+namespace {
+
+constexpr int kSMs = 148;
+
+template <typename T> struct Vec8 {  // 8 x 16-bit = 16 bytes, or 8 x fp32 = 32 bytes
+  T v[8];
+};
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const T* h = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = HalfTraits<T>::to_f(h[i]);
+  } else {
+    float4 a = reinterpret_cast<const float4*>(p)[0];
+    float4 b = reinterpret_cast<const float4*>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    uint4 u;
+    T* h = reinterpret_cast<T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = HalfTraits<T>::from_f(f[i]);
+    *reinterpret_cast<uint4*>(p) = u;
+  } else {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum; `red` is a 32-float shared buffer. All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : -INFINITY;
+  return warp_max(r);
+}
+
+#define ETHB_DISPATCH(dtype, T, ...)                                  \
+  do {                                                                 \
+    if ((dtype) == kBF16) { using T = __nv_bfloat16; __VA_ARGS__; }    \
+    else if ((dtype) == kF16) { using T = __half; __VA_ARGS__; }       \
+    else { using T = float; __VA_ARGS__; }                             \
+  } while (0)
+
+// =============================================================================================
+// LayerNorm
+// =============================================================================================
+// One CTA per row; each thread keeps ITERS 8-element slices of the row in registers.
+template <typename T, int kLnMaxIter>
+__global__ void ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                              const T* __restrict__ beta, T* __restrict__ y,
+                              float* __restrict__ mean, float* __restrict__ rstd, int rows,
+                              int hidden, float eps) {
+  __shared__ float red[32];
+  const int nvec = hidden >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + static_cast<int64_t>(row) * hidden;
+    float v[kLnMaxIter][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxIter; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nvec) {
+        load8(xr + c * 8, v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[i][j];
+      }
+    }
+    const float mu = block_sum(s, red) / hidden;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxIter; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; q += d * d; }
+      }
+    }
+    const float rs = rsqrtf(block_sum(q, red) / hidden + eps);
+    if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
+    T* yr = y + static_cast<int64_t>(row) * hidden;
+#pragma unroll
+    for (int i = 0; i < kLnMaxIter; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nvec) {
+        float g[8], b[8], o[8];
+        load8(gamma + c * 8, g);
+        load8(beta + c * 8, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mu) * rs * g[j] + b[j];
+        store8(yr + c * 8, o);
+      }
+    }
+  }
+}
+
+// Backward: a persistent grid strides over rows; every thread owns fixed columns, so the
+// dgamma/dbeta partial sums stay in registers and are written once per CTA to the workspace.
+template <typename T, int kLnMaxIter>
+__global__ void ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                              const T* __restrict__ gamma, const float* __restrict__ mean,
+                              const float* __restrict__ rstd, T* __restrict__ dx,
+                              float* __restrict__ ws, int rows, int hidden) {
+  __shared__ float red[32];
+  const int nvec = hidden >> 3;
+  float g[kLnMaxIter][8], dg[kLnMaxIter][8], db[kLnMaxIter][8];
+#pragma unroll
+  for (int i = 0; i < kLnMaxIter; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; g[i][j] = 0.f; }
+    if (c < nvec) load8(gamma + c * 8, g[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int64_t off = static_cast<int64_t>(row) * hidden;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[kLnMaxIter][8], wdy[kLnMaxIter][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxIter; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nvec) {
+        float xv[8], dyv[8];
+        load8(x + off + c * 8, xv);
+        load8(dy + off + c * 8, dyv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xv[j] - mu) * rs;
+          wdy[i][j] = dyv[j] * g[i][j];
+          s1 += wdy[i][j];
+          s2 += wdy[i][j] * xh[i][j];
+          dg[i][j] += dyv[j] * xh[i][j];
+          db[i][j] += dyv[j];
+        }
+      }
+    }
+    const float m1 = block_sum(s1, red) / hidden;
+    const float m2 = block_sum(s2, red) / hidden;
+#pragma unroll
+    for (int i = 0; i < kLnMaxIter; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (wdy[i][j] - m1 - xh[i][j] * m2) * rs;
+        store8(dx + off + c * 8, o);
+      }
+    }
+  }
+  float* wg = ws + static_cast<int64_t>(blockIdx.x) * hidden;
+  float* wb = ws + static_cast<int64_t>(gridDim.x + blockIdx.x) * hidden;
+#pragma unroll
+  for (int i = 0; i < kLnMaxIter; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nvec) {
+      store8(wg + c * 8, dg[i]);
+      store8(wb + c * 8, db[i]);
+    }
+  }
+}
+
+// out[c] (+)= sum_p ws[p, c]   for two stacked workspaces (dgamma | dbeta) or one (colsum).
+template <typename G>
+__global__ void reduce_parts_kernel(const float* __restrict__ ws, G* __restrict__ out0,
+                                    G* __restrict__ out1, int parts, int cols, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float a = 0.f, b = 0.f;
+  for (int p = 0; p < parts; ++p) {
+    a += ws[static_cast<int64_t>(p) * cols + c];
+    if (out1) b += ws[static_cast<int64_t>(parts + p) * cols + c];
+  }
+  if (accumulate) {
+    a += HalfTraits<G>::to_f(out0[c]);
+    if (out1) b += HalfTraits<G>::to_f(out1[c]);
+  }
+  out0[c] = HalfTraits<G>::from_f(a);
+  if (out1) out1[c] = HalfTraits<G>::from_f(b);
+}
+
+// =============================================================================================
+// bias + GeLU, dropout + residual
+// =============================================================================================
+template <typename T>
+__global__ void bias_gelu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                     T* __restrict__ y, int64_t nvec, int cvec) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float a[8], b[8], o[8];
+    load8(x + i * 8, a);
+    if (bias) load8(bias + (i % cvec) * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = gelu_tanh(a[j] + (bias ? b[j] : 0.f));
+    store8(y + i * 8, o);
+  }
+}
+template <typename T>
+__global__ void bias_gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                     const T* __restrict__ bias, T* __restrict__ dx, int64_t nvec,
+                                     int cvec) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float a[8], b[8], d[8], o[8];
+    load8(x + i * 8, a);
+    load8(dy + i * 8, d);
+    if (bias) load8(bias + (i % cvec) * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = d[j] * gelu_tanh_grad(a[j] + (bias ? b[j] : 0.f));
+    store8(dx + i * 8, o);
+  }
+}
+
+// Philox-4x32-10 keyed by (seed, offset); one call yields 4 x 32 random bits for counter `ctr`.
+__device__ __forceinline__ uint4 philox4(uint64_t seed, uint64_t ctr, uint64_t offset) {
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+  uint32_t c0 = static_cast<uint32_t>(ctr), c1 = static_cast<uint32_t>(ctr >> 32);
+  uint32_t c2 = static_cast<uint32_t>(offset), c3 = static_cast<uint32_t>(offset >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+// keep-bits for the 8 elements of vector i: 16 random bits per element
+__device__ __forceinline__ void keep8(uint64_t seed, uint64_t offset, int64_t i, float p,
+                                      bool (&keep)[8]) {
+  const uint4 r = philox4(seed, static_cast<uint64_t>(i), offset);
+  const uint32_t thr = static_cast<uint32_t>(p * 65536.0f);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    keep[2 * j] = (w[j] & 0xffffu) >= thr;
+    keep[2 * j + 1] = (w[j] >> 16) >= thr;
+  }
+}
+
+template <typename T>
+__global__ void bias_dropout_add_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                        const T* __restrict__ residual, T* __restrict__ out,
+                                        int64_t nvec, int cvec, float p, uint64_t seed,
+                                        uint64_t offset) {
+  const float inv_keep = p > 0.f ? 1.0f / (1.0f - p) : 1.0f;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float a[8], b[8], r[8], o[8];
+    load8(x + i * 8, a);
+    if (bias) load8(bias + (i % cvec) * 8, b);
+    if (residual) load8(residual + i * 8, r);
+    bool keep[8];
+    if (p > 0.f) keep8(seed, offset, i, p, keep);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = a[j] + (bias ? b[j] : 0.f);
+      if (p > 0.f) v = keep[j] ? v * inv_keep : 0.f;
+      o[j] = v + (residual ? r[j] : 0.f);
+    }
+    store8(out + i * 8, o);
+  }
+}
+template <typename T>
+__global__ void dropout_bwd_kernel(const T* __restrict__ dy, T* __restrict__ dx, int64_t nvec,
+                                   float p, uint64_t seed, uint64_t offset) {
+  const float inv_keep = 1.0f / (1.0f - p);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float d[8], o[8];
+    load8(dy + i * 8, d);
+    bool keep[8];
+    keep8(seed, offset, i, p, keep);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = keep[j] ? d[j] * inv_keep : 0.f;
+    store8(dx + i * 8, o);
+  }
+}
+
+// =============================================================================================
+// column sums
+// =============================================================================================
+// CTA (32 x 8): 32 lanes cover 256 consecutive columns (8 each), 8 row-lanes stride over the rows
+// of this CTA's row slab. grid = (col blocks, parts).
+template <typename T>
+__global__ void colsum_partial_kernel(const T* __restrict__ x, float* __restrict__ ws,
+                                      int64_t rows, int cols) {
+  __shared__ float sm[8][256 + 8];
+  const int c0 = (blockIdx.x * 32 + threadIdx.x) * 8;
+  const int parts = gridDim.y;
+  const int64_t per = (rows + parts - 1) / parts;
+  const int64_t r0 = per * blockIdx.y, r1 = min(rows, r0 + per);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c0 < cols) {
+    for (int64_t r = r0 + threadIdx.y; r < r1; r += 8) {
+      float v[8];
+      load8(x + r * cols + c0, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sm[threadIdx.y][threadIdx.x * 8 + j] = acc[j];
+  __syncthreads();
+  const int t = threadIdx.y * 32 + threadIdx.x;  // 0..255
+  const int c = blockIdx.x * 256 + t;
+  if (c < cols) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += sm[k][t];
+    ws[static_cast<int64_t>(blockIdx.y) * cols + c] = s;
+  }
+}
+
+// =============================================================================================
+// softmax family: one CTA (128 threads) per row, three passes over an L2-resident row.
+// =============================================================================================
+template <typename T>
+__global__ void softmax_fwd_kernel(const T* __restrict__ x, const uint8_t* __restrict__ mask,
+                                   T* __restrict__ y, int heads, int sq, int sk, float scale,
+                                   int mode, int mask_batch) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int q = static_cast<int>(row % sq);
+  const int64_t bh = row / sq;
+  const int64_t b = bh / heads;
+  const T* xr = x + row * sk;
+  T* yr = y + row * sk;
+  const uint8_t* mr = nullptr;
+  if (mode == 2) mr = mask + ((mask_batch == 1 ? 0 : b) * sq + q) * static_cast<int64_t>(sk);
+  const int limit = (mode == 1) ? q + 1 : sk;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < limit; c += blockDim.x) {
+    float v = HalfTraits<T>::to_f(xr[c]) * scale;
+    if (mr && mr[c]) v = -10000.0f;
+    mx = fmaxf(mx, v);
+  }
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < limit; c += blockDim.x) {
+    float v = HalfTraits<T>::to_f(xr[c]) * scale;
+    if (mr && mr[c]) v = -10000.0f;
+    sum += __expf(v - mx);
+  }
+  sum = block_sum(sum, red);
+  const float inv = 1.0f / sum;
+  for (int c = threadIdx.x; c < sk; c += blockDim.x) {
+    float o = 0.f;
+    if (c < limit) {
+      float v = HalfTraits<T>::to_f(xr[c]) * scale;
+      if (mr && mr[c]) v = -10000.0f;
+      o = __expf(v - mx) * inv;
+    }
+    yr[c] = HalfTraits<T>::from_f(o);
+  }
+}
+template <typename T>
+__global__ void softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y,
+                                   T* __restrict__ dx, int sq, int sk, float scale, int mode) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int q = static_cast<int>(row % sq);
+  const int limit = (mode == 1) ? q + 1 : sk;
+  const T* dyr = dy + row * sk;
+  const T* yr = y + row * sk;
+  T* dxr = dx + row * sk;
+  float dot = 0.f;
+  for (int c = threadIdx.x; c < limit; c += blockDim.x)
+    dot += HalfTraits<T>::to_f(dyr[c]) * HalfTraits<T>::to_f(yr[c]);
+  dot = block_sum(dot, red);
+  for (int c = threadIdx.x; c < sk; c += blockDim.x) {
+    float o = 0.f;
+    if (c < limit) {
+      const float yy = HalfTraits<T>::to_f(yr[c]);
+      o = scale * yy * (HalfTraits<T>::to_f(dyr[c]) - dot);
+    }
+    dxr[c] = HalfTraits<T>::from_f(o);
+  }
+}
+
+// =============================================================================================
+// embedding
+// =============================================================================================
+template <typename T>
+__global__ void embedding_fwd_kernel(const int64_t* __restrict__ tokens, const T* __restrict__ word,
+                                     const T* __restrict__ pos, T* __restrict__ out, int64_t ntok,
+                                     int seq, int hidden, int v0, int v1, int add_pos) {
+  const int nvec = hidden >> 3;
+  for (int64_t t = blockIdx.x; t < ntok; t += gridDim.x) {
+    const int64_t tok = tokens[t];
+    const bool mine = tok >= v0 && tok < v1;
+    const T* wr = word + (mine ? (tok - v0) : 0) * hidden;
+    const T* pr = pos + static_cast<int64_t>(t % seq) * hidden;
+    T* orow = out + t * hidden;
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      float w[8] = {0, 0, 0, 0, 0, 0, 0, 0}, pv[8];
+      if (mine) load8(wr + c * 8, w);
+      if (add_pos) {
+        load8(pr + c * 8, pv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] += pv[j];
+      }
+      store8(orow + c * 8, w);
+    }
+  }
+}
+template <typename G>
+__device__ __forceinline__ void atomic_add_g(G* p, float v) {
+  if constexpr (sizeof(G) == 4) atomicAdd(p, v);
+  else atomicAdd(p, HalfTraits<G>::from_f(v));
+}
+template <typename T, typename G>
+__global__ void embedding_bwd_kernel(const int64_t* __restrict__ tokens, const T* __restrict__ dout,
+                                     G* __restrict__ dword, G* __restrict__ dpos, int64_t ntok,
+                                     int seq, int hidden, int v0, int v1, int add_pos) {
+  for (int64_t t = blockIdx.x; t < ntok; t += gridDim.x) {
+    const int64_t tok = tokens[t];
+    const bool mine = tok >= v0 && tok < v1;
+    const T* drow = dout + t * hidden;
+    G* wr = dword + (mine ? (tok - v0) : 0) * hidden;
+    G* pr = dpos ? dpos + static_cast<int64_t>(t % seq) * hidden : nullptr;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float d = HalfTraits<T>::to_f(drow[c]);
+      if (mine) atomic_add_g(wr + c, d);
+      if (add_pos && pr) atomic_add_g(pr + c, d);
+    }
+  }
+}
+
+// =============================================================================================
+// vocab-parallel cross entropy
+// =============================================================================================
+template <typename T>
+__global__ void ce_stats_kernel(const T* __restrict__ logits, const int64_t* __restrict__ targets,
+                                float* __restrict__ stats, int64_t rows, int vl, int64_t ld,
+                                int v0) {
+  __shared__ float red[32];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* lr = logits + row * ld;
+    const int nvec = vl >> 3;
+    // online (max, sum) per thread, merged across the block
+    float mx = -INFINITY, sum = 0.f;
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      float v[8];
+      load8(lr + c * 8, v);
+      float m8 = v[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) m8 = fmaxf(m8, v[j]);
+      const float nm = fmaxf(mx, m8);
+      float s8 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s8 += __expf(v[j] - nm);
+      sum = sum * __expf(mx - nm) + s8;
+      mx = nm;
+    }
+    const float gm = block_max(mx, red);
+    const float contrib = (mx == -INFINITY) ? 0.f : sum * __expf(mx - gm);
+    const float gs = block_sum(contrib, red);
+    if (threadIdx.x == 0) {
+      const int64_t t = targets[row] - v0;
+      const float tl = (t >= 0 && t < vl) ? HalfTraits<T>::to_f(lr[t]) : 0.f;
+      stats[row * 3 + 0] = gm;
+      stats[row * 3 + 1] = gs;
+      stats[row * 3 + 2] = tl;
+    }
+    __syncthreads();
+  }
+}
+__global__ void ce_combine_kernel(const float* __restrict__ all, float* __restrict__ loss,
+                                  float* __restrict__ gmax, float* __restrict__ gsum, int64_t rows,
+                                  int world) {
+  const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (r >= rows) return;
+  float m = -INFINITY;
+  for (int w = 0; w < world; ++w) m = fmaxf(m, all[(w * rows + r) * 3]);
+  float s = 0.f, t = 0.f;
+  for (int w = 0; w < world; ++w) {
+    const float* p = all + (w * rows + r) * 3;
+    s += p[1] * __expf(p[0] - m);
+    t += p[2];
+  }
+  gmax[r] = m;
+  gsum[r] = s;
+  loss[r] = __logf(s) + m - t;
+}
+template <typename T>
+__global__ void ce_bwd_kernel(T* __restrict__ logits, const int64_t* __restrict__ targets,
+                              const float* __restrict__ gmax, const float* __restrict__ gsum,
+                              const float* __restrict__ dloss, int64_t rows, int vl, int64_t ld,
+                              int v0) {
+  const int nvec = vl >> 3;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    T* lr = logits + row * ld;
+    const float m = gmax[row], inv = 1.0f / gsum[row], g = dloss[row];
+    const int64_t t = targets[row] - v0;
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      float v[8];
+      load8(lr + c * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float sm = __expf(v[j] - m) * inv;
+        if (c * 8 + j == t) sm -= 1.0f;
+        v[j] = sm * g;
+      }
+      store8(lr + c * 8, v);
+    }
+  }
+}
+
+// =============================================================================================
+// optimizer
+// =============================================================================================
+template <typename G>
+__global__ void grad_norm_kernel(const G* __restrict__ g, int64_t n, float inv_scale,
+                                 float* __restrict__ acc) {
+  __shared__ float red[32];
+  float s = 0.f;
+  bool bad = false;
+  const int64_t nvec = n >> 3;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float v[8];
+    load8(g + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float u = v[j] * inv_scale;
+      bad |= !isfinite(u);
+      s += u * u;
+    }
+  }
+  for (int64_t i = (nvec << 3) + blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float u = HalfTraits<G>::to_f(g[i]) * inv_scale;
+    bad |= !isfinite(u);
+    s += u * u;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(acc, s);
+  if (bad) acc[1] = 1.0f;
+}
+
+template <typename P, typename G>
+__global__ void adam_kernel(AdamArgs a) {
+  const float found_inf = a.ctrl ? a.ctrl[1] : 0.f;
+  if (found_inf != 0.f) return;  // overflow: the whole step is skipped on every rank
+  float clip = 1.0f;
+  if (a.ctrl && a.max_norm > 0.f) {
+    const float norm = sqrtf(a.ctrl[0]);
+    clip = fminf(1.0f, a.max_norm / (norm + 1.0e-6f));
+  }
+  const float gscale = a.inv_scale * clip;
+  P* param = reinterpret_cast<P*>(a.param);
+  const G* grad = reinterpret_cast<const G*>(a.grad);
+  const float step = a.lr / a.bias_correction1;
+  const float inv_bc2 = 1.0f / sqrtf(a.bias_correction2);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < a.n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float g = HalfTraits<G>::to_f(grad[i]) * gscale;
+    float p = a.master[i];
+    if (!a.adamw) g += a.weight_decay * p;
+    const float m = a.beta1 * a.exp_avg[i] + (1.0f - a.beta1) * g;
+    const float v = a.beta2 * a.exp_avg_sq[i] + (1.0f - a.beta2) * g * g;
+    a.exp_avg[i] = m;
+    a.exp_avg_sq[i] = v;
+    const float denom = sqrtf(v) * inv_bc2 + a.eps;
+    if (a.adamw) p *= (1.0f - a.lr * a.weight_decay);
+    p -= step * (m / denom);
+    a.master[i] = p;
+    if (reinterpret_cast<void*>(param) != reinterpret_cast<void*>(a.master))
+      param[i] = HalfTraits<P>::from_f(p);
+  }
+}
+
+template <typename S, typename D>
+__global__ void strided_copy_kernel(const CopySegment* __restrict__ segs, float scale) {
+  const CopySegment s = segs[blockIdx.y];
+  const int64_t total = s.rows * s.run;
+  const S* src = reinterpret_cast<const S*>(s.src);
+  D* dst = reinterpret_cast<D*>(s.dst);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / s.run, c = i - r * s.run;
+    dst[r * s.dst_stride + c] =
+        HalfTraits<D>::from_f(HalfTraits<S>::to_f(src[r * s.src_stride + c]) * scale);
+  }
+}
+template <typename T>
+__global__ void scale_kernel(T* __restrict__ x, int64_t n, float scale) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    x[i] = HalfTraits<T>::from_f(HalfTraits<T>::to_f(x[i]) * scale);
+}
+
+__global__ void synthetic_batch_kernel(int64_t* __restrict__ tokens, int64_t* __restrict__ labels,
+                                       float* __restrict__ loss_mask,
+                                       const int64_t* __restrict__ sample_ids, int nsamples,
+                                       int seq, int vocab) {
+  const int64_t n = static_cast<int64_t>(nsamples) * seq;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t s = sample_ids[i / seq], pos = i % seq;
+    int64_t t = (s * 1103515245LL + pos * 12345LL) % vocab;
+    if (t < 0) t += vocab;
+    tokens[i] = t;
+    if (labels) {
+      int64_t l = (s * 1103515245LL + (pos + 1) * 12345LL) % vocab;
+      if (l < 0) l += vocab;
+      labels[i] = l;
+    }
+    loss_mask[i] = ((s + pos) % 4 != 0) ? 1.0f : 0.0f;
+  }
+}
+
+inline int grid_for(int64_t work_items, int threads, int per_sm = 8) {
+  int64_t blocks = (work_items + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(kSMs) * per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+// (iterations, threads) so that iterations * threads * 8 >= hidden with <= 512 threads when possible
+inline void ln_shape(int hidden, int& iters, int& threads) {
+  const int nvec = hidden / 8;
+  iters = nvec <= 512 ? 1 : (nvec <= 1024 ? 2 : 4);
+  threads = ((nvec + iters - 1) / iters + 31) / 32 * 32;
+  if (threads < 32) threads = 32;
+}
+#define ETHB_LN_ITERS(iters, I, ...)                  \
+  do {                                                 \
+    if ((iters) == 1) { constexpr int I = 1; __VA_ARGS__; }      \
+    else if ((iters) == 2) { constexpr int I = 2; __VA_ARGS__; } \
+    else { constexpr int I = 4; __VA_ARGS__; }                   \
+  } while (0)
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------
+cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
+                          float* mean, float* rstd, int rows, int hidden, float eps, int dtype,
+                          cudaStream_t st) {
+  if (hidden % 8 != 0 || hidden / 8 > 4 * 1024) return cudaErrorInvalidValue;
+  int iters, threads;
+  ln_shape(hidden, iters, threads);
+  const int grid = rows < kSMs * 16 ? rows : kSMs * 16;
+  ETHB_DISPATCH(dtype, T, ETHB_LN_ITERS(iters, I,
+                (ln_fwd_kernel<T, I><<<grid, threads, 0, st>>>(
+                    (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, hidden,
+                    eps))));
+  count_launch();
+  return cudaGetLastError();
+}
+
+int ln_bwd_parts(int rows) { return rows < kSMs * 4 ? rows : kSMs * 4; }
+
+cudaError_t layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
+                          const float* rstd, void* dx, void* dgamma, void* dbeta, float* ws,
+                          int rows, int hidden, int dtype, int grad_dtype, int accumulate,
+                          cudaStream_t st) {
+  if (hidden % 8 != 0 || hidden / 8 > 4 * 1024) return cudaErrorInvalidValue;
+  int iters, threads;
+  ln_shape(hidden, iters, threads);
+  const int parts = ln_bwd_parts(rows);
+  ETHB_DISPATCH(dtype, T, ETHB_LN_ITERS(iters, I,
+                (ln_bwd_kernel<T, I><<<parts, threads, 0, st>>>((const T*)dy, (const T*)x,
+                                                                 (const T*)gamma, mean, rstd,
+                                                                 (T*)dx, ws, rows, hidden))));
+  const int rthreads = 128;
+  ETHB_DISPATCH(grad_dtype, G,
+                (reduce_parts_kernel<G><<<(hidden + rthreads - 1) / rthreads, rthreads, 0, st>>>(
+                    ws, (G*)dgamma, (G*)dbeta, parts, hidden, accumulate)));
+  count_launch(2);
+  return cudaGetLastError();
+}
+
+cudaError_t bias_gelu_fwd(const void* x, const void* bias, void* y, int64_t rows, int cols,
+                          int dtype, cudaStream_t st) {
+  if (cols % 8) return cudaErrorInvalidValue;
+  const int64_t nvec = rows * cols / 8;
+  ETHB_DISPATCH(dtype, T,
+                (bias_gelu_fwd_kernel<T><<<grid_for(nvec, 256), 256, 0, st>>>(
+                    (const T*)x, (const T*)bias, (T*)y, nvec, cols / 8)));
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t bias_gelu_bwd(const void* dy, const void* x, const void* bias, void* dx, int64_t rows,
+                          int cols, int dtype, cudaStream_t st) {
+  if (cols % 8) return cudaErrorInvalidValue;
+  const int64_t nvec = rows * cols / 8;
+  ETHB_DISPATCH(dtype, T,
+                (bias_gelu_bwd_kernel<T><<<grid_for(nvec, 256), 256, 0, st>>>(
+                    (const T*)dy, (const T*)x, (const T*)bias, (T*)dx, nvec, cols / 8)));
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t bias_dropout_add_fwd(const void* x, const void* bias, const void* residual, void* out,
+                                 int64_t rows, int cols, float p, uint64_t seed, uint64_t offset,
+                                 int dtype, cudaStream_t st) {
+  if (cols % 8) return cudaErrorInvalidValue;
+  const int64_t nvec = rows * cols / 8;
+  ETHB_DISPATCH(dtype, T,
+                (bias_dropout_add_kernel<T><<<grid_for(nvec, 256), 256, 0, st>>>(
+                    (const T*)x, (const T*)bias, (const T*)residual, (T*)out, nvec, cols / 8, p,
+                    seed, offset)));
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t dropout_bwd(const void* dy, void* dx, int64_t rows, int cols, float p, uint64_t seed,
+                        uint64_t offset, int dtype, cudaStream_t st) {
+  if (cols % 8) return cudaErrorInvalidValue;
+  const int64_t nvec = rows * cols / 8;
+  ETHB_DISPATCH(dtype, T,
+                (dropout_bwd_kernel<T><<<grid_for(nvec, 256), 256, 0, st>>>((const T*)dy, (T*)dx,
+                                                                            nvec, p, seed, offset)));
+  count_launch();
+  return cudaGetLastError();
+}
+
+int colsum_parts(int64_t rows) {
+  int64_t p = (rows + 63) / 64;
+  if (p > 64) p = 64;
+  if (p < 1) p = 1;
+  return static_cast<int>(p);
+}
+cudaError_t colsum(const void* x, void* out, float* ws, int64_t rows, int cols, int dtype,
+                   int out_dtype, int accumulate, cudaStream_t st) {
+  if (cols % 8) return cudaErrorInvalidValue;
+  const int parts = colsum_parts(rows);
+  dim3 grid((cols + 255) / 256, parts), block(32, 8);
+  ETHB_DISPATCH(dtype, T,
+                (colsum_partial_kernel<T><<<grid, block, 0, st>>>((const T*)x, ws, rows, cols)));
+  ETHB_DISPATCH(out_dtype, G,
+                (reduce_parts_kernel<G><<<(cols + 127) / 128, 128, 0, st>>>(
+                    ws, (G*)out, (G*)nullptr, parts, cols, accumulate)));
+  count_launch(2);
+  return cudaGetLastError();
+}
+
+cudaError_t softmax_fwd(const void* x, const uint8_t* mask, void* y, int64_t batches, int heads,
+                        int sq, int sk, float scale, int mode, int mask_batch, int dtype,
+                        cudaStream_t st) {
+  const int64_t rows = batches * heads * sq;
+  if (rows <= 0 || rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+  ETHB_DISPATCH(dtype, T,
+                (softmax_fwd_kernel<T><<<static_cast<unsigned>(rows), 128, 0, st>>>(
+                    (const T*)x, mask, (T*)y, heads, sq, sk, scale, mode, mask_batch)));
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t softmax_bwd(const void* dy, const void* y, void* dx, int64_t rows, int sq, int sk,
+                        float scale, int mode, int dtype, cudaStream_t st) {
+  if (rows <= 0 || rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+  ETHB_DISPATCH(dtype, T,
+                (softmax_bwd_kernel<T><<<static_cast<unsigned>(rows), 128, 0, st>>>(
+                    (const T*)dy, (const T*)y, (T*)dx, sq, sk, scale, mode)));
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t embedding_fwd(const int64_t* tokens, const void* word, const void* pos, void* out,
+                          int64_t ntok, int seq, int hidden, int vocab_start, int vocab_end,
+                          int add_pos, int dtype, cudaStream_t st) {
+  if (hidden % 8) return cudaErrorInvalidValue;
+  const int grid = ntok < kSMs * 16 ? static_cast<int>(ntok) : kSMs * 16;
+  ETHB_DISPATCH(dtype, T,
+                (embedding_fwd_kernel<T><<<grid, 128, 0, st>>>(tokens, (const T*)word,
+                                                               (const T*)pos, (T*)out, ntok, seq,
+                                                               hidden, vocab_start, vocab_end,
+                                                               add_pos)));
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t embedding_bwd(const int64_t* tokens, const void* dout, void* dword, void* dpos,
+                          int64_t ntok, int seq, int hidden, int vocab_start, int vocab_end,
+                          int add_pos, int dtype, int grad_dtype, cudaStream_t st) {
+  const int grid = ntok < kSMs * 16 ? static_cast<int>(ntok) : kSMs * 16;
+  ETHB_DISPATCH(dtype, T, ETHB_DISPATCH(grad_dtype, G,
+                (embedding_bwd_kernel<T, G><<<grid, 256, 0, st>>>(tokens, (const T*)dout, (G*)dword,
+                                                                  (G*)dpos, ntok, seq, hidden,
+                                                                  vocab_start, vocab_end,
+                                                                  add_pos))));
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t ce_local_stats(const void* logits, const int64_t* targets, float* stats, int64_t rows,
+                           int vocab_local, int64_t ld, int vocab_start, int dtype,
+                           cudaStream_t st) {
+  if (vocab_local % 8 || ld % 8) return cudaErrorInvalidValue;
+  const int grid = rows < kSMs * 8 ? static_cast<int>(rows) : kSMs * 8;
+  ETHB_DISPATCH(dtype, T,
+                (ce_stats_kernel<T><<<grid, 256, 0, st>>>((const T*)logits, targets, stats, rows,
+                                                          vocab_local, ld, vocab_start)));
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t ce_combine(const float* stats_all, float* loss, float* gmax, float* gsum, int64_t rows,
+                       int world, cudaStream_t st) {
+  ce_combine_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, st>>>(stats_all, loss, gmax,
+                                                                              gsum, rows, world);
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t ce_bwd(void* logits, const int64_t* targets, const float* gmax, const float* gsum,
+                   const float* dloss, int64_t rows, int vocab_local, int64_t ld, int vocab_start,
+                   int dtype, cudaStream_t st) {
+  if (vocab_local % 8 || ld % 8) return cudaErrorInvalidValue;
+  const int grid = rows < kSMs * 8 ? static_cast<int>(rows) : kSMs * 8;
+  ETHB_DISPATCH(dtype, T,
+                (ce_bwd_kernel<T><<<grid, 256, 0, st>>>((T*)logits, targets, gmax, gsum, dloss, rows,
+                                                        vocab_local, ld, vocab_start)));
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t grad_norm_sq(const void* grad, int64_t n, int grad_dtype, float inv_scale, float* acc,
+                         cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  ETHB_DISPATCH(grad_dtype, G,
+                (grad_norm_kernel<G><<<grid_for(n / 8 + 1, 256, 4), 256, 0, st>>>((const G*)grad, n,
+                                                                                  inv_scale, acc)));
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t fused_adam(const AdamArgs& a, cudaStream_t st) {
+  if (a.n <= 0) return cudaSuccess;
+  const int grid = grid_for(a.n, 256, 8);
+  ETHB_DISPATCH(a.param_dtype, P, ETHB_DISPATCH(a.grad_dtype, G,
+                (adam_kernel<P, G><<<grid, 256, 0, st>>>(a))));
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t strided_copy_scale(const CopySegment* segs_dev, int nsegs, int64_t max_elems,
+                               float scale, int src_dtype, int dst_dtype, cudaStream_t st) {
+  if (nsegs <= 0) return cudaSuccess;
+  int gx = grid_for(max_elems, 256, 4);
+  dim3 grid(gx, nsegs);
+  ETHB_DISPATCH(src_dtype, S, ETHB_DISPATCH(dst_dtype, D,
+                (strided_copy_kernel<S, D><<<grid, 256, 0, st>>>(segs_dev, scale))));
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t scale_inplace(void* x, int64_t n, float scale, int dtype, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  ETHB_DISPATCH(dtype, T,
+                (scale_kernel<T><<<grid_for(n, 256, 8), 256, 0, st>>>((T*)x, n, scale)));
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t synthetic_batch(int64_t* tokens, int64_t* labels, float* loss_mask,
+                            const int64_t* sample_ids, int nsamples, int seq, int vocab,
+                            cudaStream_t st) {
+  const int64_t n = static_cast<int64_t>(nsamples) * seq;
+  synthetic_batch_kernel<<<grid_for(n, 256, 4), 256, 0, st>>>(tokens, labels, loss_mask, sample_ids,
+                                                              nsamples, seq, vocab);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace ethb

@@ -1,0 +1,431 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   D[M,N] = epilogue( alpha * sum_k A(m,k) * B(n,k) )
+//
+// One CTA per SM walks a static list of 128 x BN output tiles. Inside a CTA:
+//   warp 0   : TMA producer  - streams 128x64 / BNx64 operand tiles through a ring of shared
+//              memory stages (128-byte swizzle), signalling `full[stage]` by transaction count.
+//   warp 1   : MMA issuer    - one elected lane issues tcgen05.mma (M=128, N=BN, K=16) four times
+//              per stage into one of two TMEM accumulators, then tcgen05.commit releases the
+//              stage (`empty[stage]`) and, after the last k-block, publishes the accumulator
+//              (`tmem_full[acc]`).
+//   warps 2-5: epilogue      - tcgen05.ld the accumulator (lane == output row), apply
+//              bias / residual / GeLU / GeLU-grad / accumulate, convert and store. While they
+//              drain accumulator `acc`, the MMA warp already fills `acc ^ 1`.
+//
+// Both operands may be K-major ([rows, K]) or MN-major ([K, rows]); that covers the three GEMMs
+// of a linear layer (forward, data-gradient, weight-gradient) without materialising transposes.
+// With `comm.world > 1` the epilogue additionally all-reduces the output tiles across the GPUs
+// of a tensor-parallel group through peer memory (see the GemmComm notes in gemm_sm100.cuh).
+#include "gemm_sm100.cuh"
+#include "sm100_common.cuh"
+
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+
+namespace ethb {
+
+static std::atomic<int64_t> g_launches{0};
+int64_t launch_count() { return g_launches.load(); }
+void count_launch(int n) { g_launches.fetch_add(n); }
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;          // 6 warps
+constexpr int kEpiThreads = 128;
+constexpr int kGroupM = 16;            // band height (in tiles) of the L2-friendly rasterisation
+
+template <int BN> struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct Barriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_band = kGroupM * tiles_n;
+  const int band = tile / per_band;
+  const int r = tile - band * per_band;
+  const int rows = min(kGroupM, tiles_m - band * kGroupM);
+  tn = r / rows;
+  tm = band * kGroupM + (r - tn * rows);
+}
+
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+                    const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kStages * C::kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], kEpiThreads);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tma_a);
+    prefetch_tmap(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, C::kTmemCols);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          mbar_expect_tx(&bars->full[stage], C::kStageBytes);
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tma_a, &bars->full[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * 8192, &tma_a, &bars->full[stage], m0 + j * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tma_b, &bars->full[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, &tma_b, &bars->full[stage], n0 + j * 64, kb * BK);
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc =
+          make_idesc_f16(p.ab_dtype == kBF16 ? 1 : 0, p.a_mn, p.b_mn, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase, p.status, kStatusTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = p.a_mn ? make_smem_desc_sw128(sa + k * 2048, 8192, 1024)
+                                       : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = p.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
+                                       : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            tc_mma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&bars->empty[stage]);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        tc_commit(&bars->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    const int out_is_f32 = (p.d_dtype == kF32);
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (ok && !mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull))
+        ok = false;
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = tn * BN + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (p.bias != nullptr) {
+          const uint4* bp = reinterpret_cast<const uint4*>(
+              reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (col0 + q * 8 < p.N) {
+              uint4 b = __ldg(bp + q);
+              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 f = unpack2(bw[e], p.ab_dtype);
+                v[q * 8 + e * 2] += f.x;
+                v[q * 8 + e * 2 + 1] += f.y;
+              }
+            }
+          }
+        }
+        if (row_ok) {
+          if (p.aux_mode != kAuxNone) {
+            const uint4* ap = reinterpret_cast<const uint4*>(
+                reinterpret_cast<const uint16_t*>(p.aux) + static_cast<int64_t>(row) * p.ldaux +
+                col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col0 + q * 8 < p.N) {
+                uint4 a = __ldg(ap + q);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float2 f = unpack2(aw[e], p.ab_dtype);
+                  if (p.aux_mode == kAuxAdd) {
+                    v[q * 8 + e * 2] += f.x;
+                    v[q * 8 + e * 2 + 1] += f.y;
+                  } else {
+                    v[q * 8 + e * 2] *= gelu_tanh_grad(f.x);
+                    v[q * 8 + e * 2 + 1] *= gelu_tanh_grad(f.y);
+                  }
+                }
+              }
+            }
+          }
+          if (out_is_f32) {
+            float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.D) +
+                                                   static_cast<int64_t>(row) * p.ldd + col0);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              if (col0 + q * 4 < p.N) {
+                float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                if (p.accumulate) {
+                  float4 old = dp[q];
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                dp[q] = o;
+              }
+            }
+          } else {
+            uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.D) +
+                                                 static_cast<int64_t>(row) * p.ldd + col0);
+            uint4* d2p = p.D2 ? reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.D2) +
+                                                         static_cast<int64_t>(row) * p.ldd + col0)
+                              : nullptr;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col0 + q * 8 < p.N) {
+                if (p.accumulate) {
+                  uint4 old = dp[q];
+                  const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    float2 f = unpack2(ow[e], p.d_dtype);
+                    v[q * 8 + e * 2] += f.x;
+                    v[q * 8 + e * 2 + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack2(v[q * 8 + 0], v[q * 8 + 1], p.d_dtype);
+                o.y = pack2(v[q * 8 + 2], v[q * 8 + 3], p.d_dtype);
+                o.z = pack2(v[q * 8 + 4], v[q * 8 + 5], p.d_dtype);
+                o.w = pack2(v[q * 8 + 6], v[q * 8 + 7], p.d_dtype);
+                dp[q] = o;
+                if (d2p) {
+                  uint4 g;
+                  g.x = pack2(gelu_tanh(v[q * 8 + 0]), gelu_tanh(v[q * 8 + 1]), p.ab_dtype);
+                  g.y = pack2(gelu_tanh(v[q * 8 + 2]), gelu_tanh(v[q * 8 + 3]), p.ab_dtype);
+                  g.z = pack2(gelu_tanh(v[q * 8 + 4]), gelu_tanh(v[q * 8 + 5]), p.ab_dtype);
+                  g.w = pack2(gelu_tanh(v[q * 8 + 6]), gelu_tanh(v[q * 8 + 7]), p.ab_dtype);
+                  d2p[q] = g;
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+
+}  // namespace
+
+// 2-D tensor map over a 16-bit matrix: `inner` contiguous elements, `outer` rows of stride `ld`
+// elements, box {box_inner, box_outer}, 128-byte swizzle, zero fill outside the tensor.
+cudaError_t make_tmap_2d_16bit(CUtensorMap* map, const void* base, int dtype, uint64_t inner,
+                               uint64_t outer, uint64_t ld, uint32_t box_inner,
+                               uint32_t box_outer) {
+  EncodeFn fn = get_encode_fn();
+  if (!fn) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0)
+    return cudaErrorMisalignedAddress;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+namespace {
+
+int device_sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
+template <int BN>
+cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  CUtensorMap ta, tb;
+  cudaError_t e;
+  if (!a.a_mn)
+    e = make_tmap_2d_16bit(&ta, a.A, a.ab_dtype, a.K, a.M, a.lda, BK, BM);
+  else
+    e = make_tmap_2d_16bit(&ta, a.A, a.ab_dtype, a.M, a.K, a.lda, 64, BK);
+  if (e != cudaSuccess) return e;
+  if (!a.b_mn)
+    e = make_tmap_2d_16bit(&tb, a.B, a.ab_dtype, a.K, a.N, a.ldb, BK, BN);
+  else
+    e = make_tmap_2d_16bit(&tb, a.B, a.ab_dtype, a.N, a.K, a.ldb, 64, BK);
+  if (e != cudaSuccess) return e;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_tcgen05_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t gemm_tcgen05(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
+  if (a.N % 8 != 0 || a.ldd % 8 != 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a.D) & 15) != 0) return cudaErrorMisalignedAddress;
+  if (a.ab_dtype != kF16 && a.ab_dtype != kBF16) return cudaErrorInvalidValue;
+  // Pick the tile width that minimises (waves x cost per wave).
+  const int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
+  const int tm = (a.M + BM - 1) / BM;
+  const long t256 = static_cast<long>(tm) * ((a.N + 255) / 256);
+  const long t128 = static_cast<long>(tm) * ((a.N + 127) / 128);
+  const double c256 = static_cast<double>((t256 + sms - 1) / sms) * 2.0;
+  const double c128 = static_cast<double>((t128 + sms - 1) / sms) * 1.08;
+  if (a.N > 128 && c256 <= c128) return launch<256>(a, stream);
+  return launch<128>(a, stream);
+}
+
+}  // namespace ethb

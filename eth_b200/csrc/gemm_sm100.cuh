@@ -1,0 +1,42 @@
+// C ABI of the tcgen05 GEMM family (see gemm_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ethb {
+
+// Epilogue of D = alpha * (A x B^T) [+ bias] [op aux] [+ D]:
+enum GemmAuxMode : int {
+  kAuxNone = 0,
+  kAuxAdd = 1,       // value += aux[row, col]                 (residual add)
+  kAuxGeluGrad = 2,  // value *= gelu'(aux[row, col])          (dgrad of GEMM-2 fused with dGeLU)
+};
+
+struct GemmArgs {
+  // problem: D[M,N] = sum_k A(m,k) * B(n,k)
+  int M, N, K;
+  // operand layouts in global memory (16-bit elements, fp16 or bf16):
+  //   a_mn == 0: A is [M, K] with K contiguous, row stride lda.   a_mn == 1: A is [K, M], M contiguous.
+  //   b_mn == 0: B is [N, K] with K contiguous, row stride ldb.   b_mn == 1: B is [K, N], N contiguous.
+  const void* A; int64_t lda; int a_mn;
+  const void* B; int64_t ldb; int b_mn;
+  int ab_dtype;  // kF16 or kBF16
+  // outputs
+  void* D; int64_t ldd; int d_dtype;  // kF32 / kF16 / kBF16
+  void* D2;                          // optional gelu(value) output, same ld and dtype as A/B
+  const void* bias;                  // optional [N], ab_dtype
+  const void* aux; int64_t ldaux; int aux_mode;  // optional [M,N], ab_dtype
+  int accumulate;                    // D += value instead of D = value
+  float alpha;
+  int* status;                       // device status word (0 == ok)
+  int sm_count;                      // CTAs to launch at most (0 = all SMs)
+};
+
+// Returns cudaSuccess or the launch/encode error. Never allocates.
+cudaError_t gemm_tcgen05(const GemmArgs& args, cudaStream_t stream);
+
+// Number of kernel launches made by this library since load (for bench accounting).
+int64_t launch_count();
+void count_launch(int n = 1);
+
+}  // namespace ethb

@@ -1,0 +1,283 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+
+from eth_b200 import ops
+from eth_b200.ops import functional as Fn
+from eth_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    native.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 1024, 512), (100, 136, 72),
+                                   (1024, 2048, 1024), (4096, 6144, 2048)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_layouts(dtype, shape, a_mn, b_mn):
+    M, N, K = shape
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need 16-byte aligned rows")
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=dtype)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=dtype)
+    out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    assert _rel_err(out, ref) < 5e-3
+    native.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_epilogues(dtype):
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 256
+    a = torch.randn(M, K, device=DEV, dtype=dtype)
+    b = torch.randn(N, K, device=DEV, dtype=dtype) * 0.1
+    bias = torch.randn(N, device=DEV, dtype=dtype)
+    res = torch.randn(M, N, device=DEV, dtype=dtype)
+    base = a.float() @ b.float().t()
+    # bias + gelu second output
+    pre = torch.empty(M, N, device=DEV, dtype=dtype)
+    act = torch.empty_like(pre)
+    ops.gemm(a, b, out=pre, bias=bias, gelu_out=act)
+    assert _rel_err(pre, base + bias.float()) < 5e-3
+    assert _rel_err(act, torch.nn.functional.gelu(base + bias.float(), approximate="tanh")) < 1e-2
+    # residual add
+    out = ops.gemm(a, b, aux=res, aux_mode=Fn.AUX_ADD)
+    assert _rel_err(out, base + res.float()) < 5e-3
+    # gelu-grad epilogue
+    out = ops.gemm(a, b, aux=res, aux_mode=Fn.AUX_GELU_GRAD)
+    assert _rel_err(out, base * Fn.gelu_tanh_grad_ref(res.float())) < 1e-2
+    # fp32 accumulate output with alpha
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    ref = acc + 0.5 * base
+    ops.gemm(a, b, out=acc, accumulate=True, alpha=0.5)
+    assert _rel_err(acc, ref) < 2e-3
+    # 16-bit accumulate
+    acc16 = torch.randn(M, N, device=DEV, dtype=dtype)
+    ref = acc16.float() + base
+    ops.gemm(a, b, out=acc16, accumulate=True)
+    assert _rel_err(acc16, ref) < 1e-2
+
+
+def test_gemm_strided_views():
+    torch.manual_seed(2)
+    big = torch.randn(512, 3 * 256, device=DEV, dtype=torch.bfloat16)
+    a = big[:, 256:512]  # row stride 768, inner contiguous
+    w = torch.randn(384, 256, device=DEV, dtype=torch.bfloat16)
+    out = ops.gemm(a, w)
+    assert _rel_err(out, a.float() @ w.float().t()) < 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hidden", [64, 2048, 4096, 5120])
+def test_layernorm(dtype, hidden):
+    torch.manual_seed(3)
+    rows = 777
+    x = torch.randn(rows, hidden, device=DEV, dtype=dtype, requires_grad=True)
+    g = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(dtype).requires_grad_(True)
+    b = (0.1 * torch.randn(hidden, device=DEV)).to(dtype).requires_grad_(True)
+    y = ops.layer_norm(x, g, b, 1e-5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, gr, br = (t.detach().float().requires_grad_(True) for t in (x, g, b))
+    yr = torch.nn.functional.layer_norm(xr, (hidden,), gr, br, 1e-5)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(g.grad, gr.grad) < 2e-2
+    assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+def test_layernorm_main_grad_accumulates():
+    hidden, rows = 256, 300
+    x = torch.randn(rows, hidden, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.ones(hidden, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.zeros(hidden, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g.main_grad = torch.full((hidden,), 2.0, device=DEV)
+    b.main_grad = torch.full((hidden,), 3.0, device=DEV)
+    y = ops.layer_norm(x, g, b, 1e-5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert g.grad is None and b.grad is None
+    assert _rel_err(b.main_grad, 3.0 + dy.float().sum(0)) < 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_bias_gelu(dtype):
+    x = torch.randn(500, 1024, device=DEV, dtype=dtype, requires_grad=True)
+    b = torch.randn(1024, device=DEV, dtype=dtype, requires_grad=True)
+    y = ops.bias_gelu(x, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, br = x.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.gelu(xr + br, approximate="tanh")
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("p", [0.0, 0.1])
+def test_bias_dropout_add(p):
+    dtype = torch.bfloat16
+    x = torch.randn(300, 512, device=DEV, dtype=dtype, requires_grad=True)
+    b = torch.randn(512, device=DEV, dtype=dtype, requires_grad=True)
+    r = torch.randn(300, 512, device=DEV, dtype=dtype, requires_grad=True)
+    out = ops.bias_dropout_add(x, b, r, p, seed=1234, offset=7)
+    keep = Fn._keep_mask_ref(x.shape, p, 1234, 7, "cpu").to(DEV) if p > 0 else torch.ones_like(x, dtype=torch.bool)
+    ref = r.float() + torch.where(keep, (x.float() + b.float()) / (1 - p), torch.zeros_like(x.float()))
+    assert _rel_err(out, ref) < 1e-2
+    if p > 0:
+        frac = keep.float().mean().item()
+        assert abs(frac - (1 - p)) < 0.01
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    dxr = torch.where(keep, dy.float() / (1 - p), torch.zeros_like(dy.float()))
+    assert _rel_err(x.grad, dxr) < 1e-2
+    assert _rel_err(r.grad, dy) < 1e-6
+    assert _rel_err(b.grad, dxr.sum(0)) < 2e-2
+
+
+def test_softmax_family():
+    dtype = torch.float16
+    x = torch.randn(6, 128, 128, device=DEV, dtype=dtype, requires_grad=True)
+    y = ops.scaled_upper_triang_masked_softmax(x, 0.5)
+    tri = torch.triu(torch.ones(128, 128, dtype=torch.bool, device=DEV), 1)
+    xr = x.detach().float().requires_grad_(True)
+    yr = torch.softmax((xr * 0.5).masked_fill(tri, float("-inf")), -1)
+    assert _rel_err(y, yr) < 5e-3
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    yr.backward(dy.float())
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    # explicit mask
+    x4 = torch.randn(2, 3, 64, 96, device=DEV, dtype=dtype)
+    mask = torch.rand(2, 1, 64, 96, device=DEV) < 0.3
+    y4 = ops.scaled_masked_softmax(x4, mask, 2.0)
+    ref = torch.softmax((x4.float() * 2.0).masked_fill(mask, -10000.0), -1)
+    assert _rel_err(y4, ref) < 5e-3
+    y0 = ops.scaled_softmax(x4, 1.5)
+    assert _rel_err(y0, torch.softmax(x4.float() * 1.5, -1)) < 5e-3
+
+
+def test_embedding_fwd_bwd():
+    dtype = torch.bfloat16
+    V, H, S, B = 1000, 256, 64, 4
+    word = torch.randn(500, H, device=DEV, dtype=dtype, requires_grad=True)  # shard [250, 750)
+    pos = torch.randn(S, H, device=DEV, dtype=dtype, requires_grad=True)
+    tok = torch.randint(0, V, (B, S), device=DEV)
+    out = ops.embedding(tok, word, pos, S, vocab_start=250, add_pos=True)
+    t = tok.reshape(-1) - 250
+    mine = (t >= 0) & (t < 500)
+    ref = word.float()[t.clamp(0, 499)] * mine[:, None] + pos.float().repeat(B, 1)
+    assert _rel_err(out, ref) < 1e-2
+    word.main_grad = torch.zeros(500, H, device=DEV)
+    pos.main_grad = torch.zeros(S, H, device=DEV)
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    refw = torch.zeros(500, H, device=DEV).index_add_(0, t[mine], dy.float()[mine])
+    assert _rel_err(word.main_grad, refw) < 1e-3
+    assert _rel_err(pos.main_grad, dy.float().view(B, S, H).sum(0)) < 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy(dtype):
+    rows, V = 333, 4096
+    logits = (torch.randn(rows, V, device=DEV) * 3).to(dtype)
+    tgt = torch.randint(0, V, (rows,), device=DEV)
+    lref = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lref, tgt, reduction="none")
+    w = torch.rand(rows, device=DEV)
+    (ref * w).sum().backward()
+    l2 = logits.clone().requires_grad_(True)
+    loss = ops.vocab_parallel_cross_entropy(l2, tgt)
+    assert _rel_err(loss, ref) < 2e-3
+    (loss * w).sum().backward()
+    assert _rel_err(l2.grad, lref.grad) < 2e-2
+    # two vocab shards combined through the gather hook
+    halves = [logits[:, : V // 2].contiguous(), logits[:, V // 2:].contiguous()]
+    stats = []
+    for i, h in enumerate(halves):
+        st = torch.empty(rows, 3, device=DEV)
+        native.lib().ce_local_stats(h, tgt, st, i * (V // 2))
+        stats.append(st)
+    both = torch.stack(stats)
+    loss2 = ops.vocab_parallel_cross_entropy(halves[0], tgt, 0, gather_fn=lambda s: both)
+    assert _rel_err(loss2, ref) < 2e-3
+
+
+def test_adam_and_norm():
+    n = 100003
+    p16 = torch.randn(n, device=DEV).to(torch.bfloat16)
+    master = p16.float().clone()
+    g = torch.randn(n, device=DEV) * 64.0
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    ctrl = torch.zeros(2, device=DEV)
+    native.lib().grad_norm_sq(g, 1 / 64.0, ctrl)
+    assert abs(ctrl[0].item() - (g / 64).pow(2).sum().item()) / ctrl[0].item() < 1e-4
+    ref_p = master.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref_p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    clip = min(1.0, 1.0 / (ctrl[0].sqrt().item() + 1e-6))
+    for step in (1, 2):
+        ref_p.grad = (g / 64) * clip
+        opt.step()
+        native.lib().fused_adam(p16, master, g, m, v, ctrl, 1e-3, 0.9, 0.95, 1e-8, 0.01, step,
+                                1 / 64.0, 1.0, True)
+    assert _rel_err(master, ref_p.detach()) < 1e-5
+    assert _rel_err(p16, ref_p.detach()) < 1e-2
+    # overflow flag skips the update
+    ctrl[1] = 1.0
+    before = master.clone()
+    native.lib().fused_adam(p16, master, g, m, v, ctrl, 1e-3, 0.9, 0.95, 1e-8, 0.01, 3, 1 / 64.0, 1.0, True)
+    assert torch.equal(before, master)
+
+
+def test_linear_autograd_main_grad():
+    torch.manual_seed(5)
+    dtype = torch.bfloat16
+    x = torch.randn(512, 256, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(384, 256, device=DEV) * 0.05).to(dtype).requires_grad_(True)
+    b = torch.randn(384, device=DEV, dtype=dtype, requires_grad=True)
+    w.main_grad = torch.zeros(384, 256, device=DEV)
+    b.main_grad = torch.zeros(384, device=DEV)
+    for fn, ref_fn in ((ops.linear, lambda z: z), (ops.linear_gelu, lambda z: torch.nn.functional.gelu(z, approximate="tanh"))):
+        w.main_grad.zero_(); b.main_grad.zero_(); x.grad = None
+        y = fn(x, w, b)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+        yr = ref_fn(xr @ wr.t() + br)
+        yr.backward(dy.float())
+        assert _rel_err(y, yr) < 1e-2
+        assert _rel_err(x.grad, xr.grad) < 1.5e-2
+        assert _rel_err(w.main_grad, wr.grad) < 1.5e-2
+        assert _rel_err(b.main_grad, br.grad) < 2e-2
+        assert w.grad is None
+
+
+def test_synthetic_batch_matches_reference_formula():
+    ids = torch.tensor([0, 5, 123456], device=DEV)
+    S, V = 64, 50257
+    tok = torch.empty(3, S, dtype=torch.long, device=DEV)
+    lab = torch.empty_like(tok)
+    mask = torch.empty(3, S, device=DEV)
+    native.lib().synthetic_batch(tok, lab, mask, ids, S, V)
+    pos = torch.arange(S, device=DEV)
+    ref = (ids[:, None] * 1103515245 + pos[None] * 12345).remainder(V)
+    assert torch.equal(tok, ref)
+    assert torch.equal(mask, ((ids[:, None] + pos[None]) % 4 != 0).float())
