@@ -1,5 +1,970 @@
+// Causal flash attention for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+//
+// Forward. One CTA owns 256 query rows (two 128-row tiles) of one (batch, head) and streams the
+// key/value tiles once for both:
+//   warp 0      TMA producer: Q (once), then K_j / V_j tiles into a ring of shared-memory stages.
+//   warp 1      MMA issuer:   S_t = Q_t K_j^T  (operands in shared memory, accumulator in TMEM),
+//               O_t += P_t V_j (P_t read from TMEM, V_j from shared memory as an MN-major operand).
+//   warps 2-5   softmax of query tile 0, warps 6-9 softmax of query tile 1: one thread per query
+//               row; tcgen05.ld the scores, online softmax in the exp2 domain, write P back to
+//               TMEM as packed 16-bit (aliasing the score columns) and rescale the O accumulator
+//               only when the running maximum grew by more than 2^8 (exact after the final
+//               normalisation, and it keeps TMEM read-modify-write traffic rare).
+// The two query tiles ping-pong: while one tile's softmax runs on the CUDA cores, the tensor
+// core executes the other tile's MMAs.
+//
+// TMEM map (512 columns): S_0/P_0 [0,128)  S_1/P_1 [128,256)  O_0 [256,256+D)  O_1 [384,384+D).
+//
+// Backward is two kernels (see the second half of this file): one per key/value tile that
+// produces dK and dV, one per query tile that produces dQ. Both recompute the scores.
 #include "attention_sm100.cuh"
+#include "gemm_sm100.cuh"
+#include "sm100_common.cuh"
+
+#include <cstdio>
+#include <mutex>
+
 namespace ethb {
-cudaError_t attention_fwd(const AttnArgs&, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t attention_bwd(const AttnArgs&, cudaStream_t) { return cudaErrorNotSupported; }
+
+cudaError_t make_tmap_2d_16bit(CUtensorMap* map, const void* base, int dtype, uint64_t inner,
+                               uint64_t outer, uint64_t ld, uint32_t box_inner,
+                               uint32_t box_outer);
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr int kTile = 128;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
+        "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+
+// 4-D map over a [batch, seq, heads, head_dim] view: dims {d, seq, heads, batch}, box {64, rows, 1, 1}.
+cudaError_t make_tmap_bshd(CUtensorMap* map, const void* base, int dtype, int d, int seq, int heads,
+                           int batch, const int64_t strides[3], int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return cudaErrorNotSupported;
+  ensure_thread_context();
+  if (reinterpret_cast<uintptr_t>(base) & 15) return cudaErrorMisalignedAddress;
+  for (int i = 0; i < 3; ++i)
+    if ((strides[i] * 2) % 16 != 0) return cudaErrorMisalignedAddress;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(seq),
+                        static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  // strides[] = (batch, seq, heads) element strides
+  cuuint64_t gstr[3] = {static_cast<cuuint64_t>(strides[1]) * 2,
+                        static_cast<cuuint64_t>(strides[2]) * 2,
+                        static_cast<cuuint64_t>(strides[0]) * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  4, const_cast<void*>(base), dims, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "[eth_b200] cuTensorMapEncodeTiled failed (%d): base=%p dims={%llu,%llu,%llu,%llu} "
+            "strides(bytes)={%llu,%llu,%llu} box_rows=%d\n", static_cast<int>(r), base,
+            (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+            (unsigned long long)dims[3], (unsigned long long)gstr[0], (unsigned long long)gstr[1],
+            (unsigned long long)gstr[2], box_rows);
+  ETHB_RETURN_IF(r != CUDA_SUCCESS, cudaErrorInvalidValue, "cuTensorMapEncodeTiled (4-D)");
+  return cudaSuccess;
+}
+
+__device__ __forceinline__ uint32_t pack_pair(float a, float b, int dtype) {
+  return pack2(a, b, dtype);
+}
+
+// ==============================================================================================
+// forward
+// ==============================================================================================
+template <int D> struct FwdCfg {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kQBytes = 2 * kHalves * 16384;       // two query tiles
+  static constexpr int kKBytes = kHalves * 16384;
+  static constexpr int kVBytes = kHalves * 16384;
+  static constexpr int kStageBytes = kKBytes + kVBytes;
+  static constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + 1024 + 256;
+  static constexpr int kThreads = 320;
+};
+
+struct FwdBarriers {
+  uint64_t q_full;
+  uint64_t kv_full[4];
+  uint64_t kv_empty[4];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_done[2];
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const AttnArgs p) {
+  using C = FwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + C::kQBytes;
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(sKV + C::kStages * C::kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  // heavy (late) query blocks first so the causal triangle balances across waves
+  const int qb = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int kv_tiles = (p.seq_k + kTile - 1) / kTile;
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt = 2 * qb + t;
+    if (qt * kTile >= p.seq_q) n_t[t] = 0;
+    else n_t[t] = p.causal ? min(qt + 1, kv_tiles) : kv_tiles;
+  }
+  const int n = max(n_t[0], n_t[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->o_done[t], 1);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tq);
+    prefetch_tmap(&tk);
+    prefetch_tmap(&tv);
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (elect_one()) {
+      mbar_expect_tx(&bars->q_full, C::kQBytes);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h)
+          tma_load_4d(sQ + (t * C::kHalves + h) * 16384, &tq, &bars->q_full, h * 64,
+                      (2 * qb + t) * kTile, head, batch);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < n; ++j) {
+        if (!mbar_wait(&bars->kv_empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
+        uint8_t* sk = sKV + stage * C::kStageBytes;
+        uint8_t* sv = sk + C::kKBytes;
+        mbar_expect_tx(&bars->kv_full[stage], C::kStageBytes);
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h) {
+          tma_load_4d(sk + h * 16384, &tk, &bars->kv_full[stage], h * 64, j * kTile, head, batch);
+          tma_load_4d(sv + h * 16384, &tv, &bars->kv_full[stage], h * 64, j * kTile, head, batch);
+        }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      const int fmt = p.dtype == kBF16 ? 1 : 0;
+      const uint32_t idesc_qk = make_idesc_f16(fmt, 0, 0, 128, 128);
+      const uint32_t idesc_pv = make_idesc_f16(fmt, 0, 1, 128, D);
+      bool ok = mbar_wait(&bars->q_full, 0, p.status, kStatusTimeoutFull);
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t sq = smem_u32(sQ + t * C::kHalves * 16384);
+        const uint32_t sk = smem_u32(sKV + stage * C::kStageBytes);
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f16(tmem_base + t * 128,
+                       make_smem_desc_sw128(sq + h * 16384 + k * 32, 16, 1024),
+                       make_smem_desc_sw128(sk + h * 16384 + k * 32, 16, 1024), idesc_qk,
+                       (h | k) != 0 ? 1u : 0u);
+        tc_commit(&bars->s_full[t]);
+      };
+      auto issue_pv = [&](int t, int stage, int j) {
+        const uint32_t sv = smem_u32(sKV + stage * C::kStageBytes + C::kKBytes);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          tc_mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+                        make_smem_desc_sw128(sv + k * 2048, 16384, 1024), idesc_pv,
+                        (j | k) != 0 ? 1u : 0u);
+        tc_commit(&bars->o_done[t]);
+      };
+      if (ok && n > 0) {
+        ok = mbar_wait(&bars->kv_full[0], 0, p.status, kStatusTimeoutFull);
+        tc_fence_after();
+        if (ok) {
+          if (n_t[0] > 0) issue_qk(0, 0);
+          if (n_t[1] > 0) issue_qk(1, 0);
+        }
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < n && ok; ++j) {
+        int nstage = stage + 1;
+        uint32_t nphase = phase;
+        if (nstage == C::kStages) { nstage = 0; nphase ^= 1; }
+        if (j < n_t[0]) {
+          ok = mbar_wait(&bars->p_full[0], j & 1, p.status, kStatusTimeoutTmemFull);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(0, stage, j);
+        }
+        if (j + 1 < n) {
+          ok = mbar_wait(&bars->kv_full[nstage], nphase, p.status, kStatusTimeoutFull);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (j + 1 < n_t[0]) issue_qk(0, nstage);
+        if (j < n_t[1]) {
+          ok = mbar_wait(&bars->p_full[1], j & 1, p.status, kStatusTimeoutTmemFull);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(1, stage, j);
+        }
+        tc_commit(&bars->kv_empty[stage]);
+        if (j + 1 < n_t[1]) issue_qk(1, nstage);
+        stage = nstage;
+        phase = nphase;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue
+    const int t = (warp - 2) >> 2;       // query tile of this warpgroup
+    const int quarter = warp & 3;        // TMEM lane quarter
+    const int r_local = quarter * 32 + lane;
+    const int qt = 2 * qb + t;
+    const int q_row = qt * kTile + r_local;
+    const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + t * 128 + lane_bits;
+    const uint32_t o_addr = tmem_base + 256 + t * 128 + lane_bits;
+    const float sl2 = p.scale * kLog2e;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    const int nt = n_t[t];
+    for (int j = 0; j < nt && ok; ++j) {
+      ok = mbar_wait(&bars->s_full[t], j & 1, p.status, kStatusTimeoutTmemFull);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diag = p.causal && (j == qt);
+      const bool tail = (j + 1) * kTile > p.seq_k;
+      const int col_limit_tail = p.seq_k - j * kTile;  // valid columns in a tail tile
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c * 32 + i;
+          float s = __uint_as_float(r[i]);
+          if ((diag && col > r_local) || (tail && col >= col_limit_tail)) s = -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx * sl2);
+      if (j == 0) {
+        m_run = m_new;
+      } else {
+        const bool need = m_new > m_run + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          const float m_upd = need ? m_new : m_run;
+          const float alpha = exp2f(m_run - m_upd);
+          l_run *= alpha;
+          m_run = m_upd;
+          // PV_{j-1} must have landed before O is touched
+          ok = mbar_wait(&bars->o_done[t], (j - 1) & 1, p.status, kStatusTimeoutTmemFull);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(o_addr + c * 16, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x16(o_addr + c * 16, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: P = exp2(s * scale_log2 - m), packed to 16 bit into the first 64 score columns
+      float lsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int col = c * 32 + 2 * i;
+          float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
+          float p0 = exp2f(s0 * sl2 - m_run), p1 = exp2f(s1 * sl2 - m_run);
+          if ((diag && col > r_local) || (tail && col >= col_limit_tail)) p0 = 0.f;
+          if ((diag && col + 1 > r_local) || (tail && col + 1 >= col_limit_tail)) p1 = 0.f;
+          lsum += p0 + p1;
+          pk[i] = pack_pair(p0, p1, p.dtype);
+        }
+        tmem_st_32x32b_x16(s_addr + c * 16, pk);
+      }
+      l_run += lsum;
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[t]);
+    }
+    if (ok && nt > 0) {
+      ok = mbar_wait(&bars->o_done[t], (nt - 1) & 1, p.status, kStatusTimeoutTmemFull);
+      tc_fence_after();
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && nt > 0) {
+      const float inv_l = 1.0f / l_run;
+      const bool row_ok = q_row < p.seq_q;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_strides[0] +
+                       static_cast<int64_t>(q_row) * p.o_strides[1] + head * p.o_strides[2];
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(o_addr + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l, p.dtype);
+            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l, p.dtype);
+            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l, p.dtype);
+            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l, p.dtype);
+            dst[q] = o;
+          }
+        }
+      }
+      if (row_ok)
+        p.lse[(static_cast<int64_t>(batch) * p.heads + head) * p.seq_q + q_row] =
+            (m_run + log2f(l_run)) * kLn2;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
+  using C = FwdCfg<D>;
+  CUtensorMap tq, tk, tv;
+  cudaError_t e;
+  e = make_tmap_bshd(&tq, a.q, a.dtype, D, a.seq_q, a.heads, a.batch, a.q_strides, kTile);
+  if (e != cudaSuccess) return e;
+  e = make_tmap_bshd(&tk, a.k, a.dtype, D, a.seq_k, a.heads, a.batch, a.k_strides, kTile);
+  if (e != cudaSuccess) return e;
+  e = make_tmap_bshd(&tv, a.v, a.dtype, D, a.seq_k, a.heads, a.batch, a.v_strides, kTile);
+  if (e != cudaSuccess) return e;
+  static bool attr = false;
+  if (!attr) {
+    e = cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  dim3 grid((a.seq_q + 2 * kTile - 1) / (2 * kTile), a.heads, a.batch);
+  attn_fwd_kernel<D><<<grid, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+
+// ==============================================================================================
+// backward
+// ==============================================================================================
+// Shared by both backward kernels: 2 resident 128-row tiles + a 2-stage ring of streamed tile
+// pairs, processed in 64-row/column sub-tiles that ping-pong between two TMEM score buffers:
+//   buffer b: S at columns [128b, 128b+64), dP at [128b+64, 128b+128); the 16-bit P / dS that
+//   feed the next MMAs alias the first 32 columns of S / dP. Accumulators start at column 256.
+template <int D> struct BwdCfg {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kTileBytes = kHalves * 16384;        // one 128-row tile
+  static constexpr int kResidentBytes = 2 * kTileBytes;
+  static constexpr int kStages = 2;
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kAuxBytes = 2 * 2 * 2 * 64 * 4;      // [wg][parity][lse|delta][64]
+  static constexpr int kSmemBytes = kResidentBytes + kStages * kStageBytes + kAuxBytes + 1024 + 256;
+  static constexpr int kThreads = 320;
+};
+
+struct BwdBarriers {
+  uint64_t res_full;
+  uint64_t st_full[2];
+  uint64_t st_empty[2];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t done;
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ void wg_bar_sync(int wg) {
+  asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
+}
+
+// delta[b,h,s] = sum_d dO * O ; one warp per (b, s, h) row
+__global__ void attn_delta_kernel(const AttnArgs p) {
+  const int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int64_t total = static_cast<int64_t>(p.batch) * p.seq_q * p.heads;
+  if (row >= total) return;
+  const int h = static_cast<int>(row % p.heads);
+  const int64_t bs = row / p.heads;
+  const int s = static_cast<int>(bs % p.seq_q);
+  const int b = static_cast<int>(bs / p.seq_q);
+  const uint16_t* o = reinterpret_cast<const uint16_t*>(p.o) + b * p.o_strides[0] +
+                      static_cast<int64_t>(s) * p.o_strides[1] + h * p.o_strides[2];
+  const uint16_t* g = reinterpret_cast<const uint16_t*>(p.d_o) + b * p.do_strides[0] +
+                      static_cast<int64_t>(s) * p.do_strides[1] + h * p.do_strides[2];
+  float acc = 0.f;
+  for (int c = lane * 2; c < p.head_dim; c += 64) {
+    const float2 a = unpack2(*reinterpret_cast<const uint32_t*>(o + c), p.dtype);
+    const float2 d = unpack2(*reinterpret_cast<const uint32_t*>(g + c), p.dtype);
+    acc += a.x * d.x + a.y * d.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) p.delta[(static_cast<int64_t>(b) * p.heads + h) * p.seq_q + s] = acc;
+}
+
+// ---- dK / dV: one CTA per (key/value tile, head, batch) ---------------------------------------
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                     const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                     const AttnArgs p) {
+  using C = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + C::kTileBytes;
+  uint8_t* sStage = smem + C::kResidentBytes;  // stage: [Q tile | dO tile]
+  float* sAux = reinterpret_cast<float*>(sStage + C::kStages * C::kStageBytes);
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(reinterpret_cast<uint8_t*>(sAux) + C::kAuxBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int j = blockIdx.x;  // key/value tile
+  const int q_tiles = (p.seq_q + kTile - 1) / kTile;
+  const int i0 = p.causal ? j : 0;
+  const int nq = max(q_tiles - i0, 0);
+  const int U = 2 * nq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->res_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->st_full[s], 1);
+      mbar_init(&bars->st_empty[s], 1);
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->p_full[s], 128);
+    }
+    mbar_init(&bars->done, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv); prefetch_tmap(&tdo);
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(&bars->res_full, C::kResidentBytes);
+#pragma unroll
+      for (int h = 0; h < C::kHalves; ++h) {
+        tma_load_4d(sK + h * 16384, &tk, &bars->res_full, h * 64, j * kTile, head, batch);
+        tma_load_4d(sV + h * 16384, &tv, &bars->res_full, h * 64, j * kTile, head, batch);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = 0; t < nq; ++t) {
+        if (!mbar_wait(&bars->st_empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
+        uint8_t* sq = sStage + stage * C::kStageBytes;
+        uint8_t* sdo = sq + C::kTileBytes;
+        mbar_expect_tx(&bars->st_full[stage], C::kStageBytes);
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h) {
+          tma_load_4d(sq + h * 16384, &tq, &bars->st_full[stage], h * 64, (i0 + t) * kTile, head, batch);
+          tma_load_4d(sdo + h * 16384, &tdo, &bars->st_full[stage], h * 64, (i0 + t) * kTile, head, batch);
+        }
+        if (++stage == 2) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const int fmt = p.dtype == kBF16 ? 1 : 0;
+      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, 128, 64);
+      const uint32_t idesc_acc = make_idesc_f16(fmt, 0, 1, 128, D);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      auto issue_sdp = [&](int u) {
+        const int stage = (u >> 1) & 1, sub = u & 1, b = u & 1;
+        const uint32_t aQ = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
+        const uint32_t aDO = aQ + C::kTileBytes;
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f16(tmem_base + b * 128,
+                       make_smem_desc_sw128(aK + h * 16384 + k * 32, 16, 1024),
+                       make_smem_desc_sw128(aQ + h * 16384 + k * 32, 16, 1024), idesc_s,
+                       (h | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f16(tmem_base + b * 128 + 64,
+                       make_smem_desc_sw128(aV + h * 16384 + k * 32, 16, 1024),
+                       make_smem_desc_sw128(aDO + h * 16384 + k * 32, 16, 1024), idesc_s,
+                       (h | k) != 0 ? 1u : 0u);
+        tc_commit(&bars->s_full[b]);
+      };
+      bool ok = mbar_wait(&bars->res_full, 0, p.status, kStatusTimeoutFull);
+      if (ok && U > 0) {
+        ok = mbar_wait(&bars->st_full[0], 0, p.status, kStatusTimeoutFull);
+        tc_fence_after();
+        if (ok) { issue_sdp(0); issue_sdp(1); }
+      }
+      for (int u = 0; u < U && ok; ++u) {
+        const int b = u & 1, stage = (u >> 1) & 1, sub = u & 1;
+        ok = mbar_wait(&bars->p_full[b], (u >> 1) & 1, p.status, kStatusTimeoutTmemFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
+        const uint32_t aDO = aQ + C::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // dV += P^T dO
+          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + k * 8,
+                        make_smem_desc_sw128(aDO + k * 2048, 16384, 1024), idesc_acc,
+                        (u | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // dK += dS^T Q
+          tc_mma_f16_ts(tmem_base + 384, tmem_base + b * 128 + 64 + k * 8,
+                        make_smem_desc_sw128(aQ + k * 2048, 16384, 1024), idesc_acc,
+                        (u | k) != 0 ? 1u : 0u);
+        if (sub == 1) tc_commit(&bars->st_empty[stage]);
+        if (u + 2 < U) {
+          const int u2 = u + 2;
+          if ((u2 & 1) == 0) {
+            ok = mbar_wait(&bars->st_full[(u2 >> 1) & 1], (u2 >> 2) & 1, p.status, kStatusTimeoutFull);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_sdp(u2);
+        }
+      }
+      tc_commit(&bars->done);
+    }
+  } else {
+    const int wg = (warp - 2) >> 2;      // sub-tile parity handled by this warpgroup
+    const int quarter = warp & 3;
+    const int r_local = quarter * 32 + lane;     // key/value row inside the tile
+    const int wg_tid = threadIdx.x - 64 - wg * 128;
+    const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + wg * 128 + lane_bits;
+    const uint32_t dp_addr = s_addr + 64;
+    const float sl2 = p.scale * kLog2e;
+    const float* lse_bh = p.lse + (static_cast<int64_t>(batch) * p.heads + head) * p.seq_q;
+    const float* delta_bh = p.delta + (static_cast<int64_t>(batch) * p.heads + head) * p.seq_q;
+    bool ok = true;
+    for (int t = 0; t < nq && ok; ++t) {
+      const int i = i0 + t;
+      const int q0 = i * kTile + wg * 64;
+      float* a_lse = sAux + ((wg * 2 + (t & 1)) * 2 + 0) * 64;
+      float* a_del = a_lse + 64;
+      if (wg_tid < 64) {
+        const int qi = q0 + wg_tid;
+        const bool in = qi < p.seq_q;
+        a_lse[wg_tid] = in ? lse_bh[qi] * kLog2e : INFINITY;
+        a_del[wg_tid] = in ? delta_bh[qi] : 0.f;
+      }
+      wg_bar_sync(wg);
+      ok = mbar_wait(&bars->s_full[wg], t & 1, p.status, kStatusTimeoutTmemFull);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diag = p.causal && (i == j);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(s_addr + c * 32, rs);
+        tmem_ld_32x32b_x32(dp_addr + c * 32, rd);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const int col = c * 32 + 2 * x;          // query column inside this 64-wide sub-tile
+          const int ql = wg * 64 + col;            // query row inside the 128-row tile
+          float p0 = exp2f(__uint_as_float(rs[2 * x]) * sl2 - a_lse[col]);
+          float p1 = exp2f(__uint_as_float(rs[2 * x + 1]) * sl2 - a_lse[col + 1]);
+          if (diag && r_local > ql) p0 = 0.f;
+          if (diag && r_local > ql + 1) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(rd[2 * x]) - a_del[col]);
+          const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - a_del[col + 1]);
+          pk[x] = pack_pair(p0, p1, p.dtype);
+          dk[x] = pack_pair(d0, d1, p.dtype);
+        }
+        tmem_st_32x32b_x16(s_addr + c * 16, pk);
+        tmem_st_32x32b_x16(dp_addr + c * 16, dk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[wg]);
+    }
+    // epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK * scale
+    if (ok) ok = mbar_wait(&bars->done, 0, p.status, kStatusTimeoutTmemFull);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && U > 0) {
+      tc_fence_after();
+      const int kv_row = j * kTile + r_local;
+      const bool row_ok = kv_row < p.seq_k;
+      const int64_t* st = wg == 0 ? p.dv_strides : p.dk_strides;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(wg == 0 ? p.dv : p.dk) + batch * st[0] +
+                       static_cast<int64_t>(kv_row) * st[1] + head * st[2];
+      const float mul = wg == 0 ? 1.0f : p.scale;
+      const uint32_t acc_addr = tmem_base + 256 + wg * 128 + lane_bits;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(acc_addr + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul, p.dtype);
+            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul, p.dtype);
+            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul, p.dtype);
+            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul, p.dtype);
+            dst[q] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---- dQ: one CTA per (query tile, head, batch) ---------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                   const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                   const AttnArgs p) {
+  using C = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + C::kTileBytes;
+  uint8_t* sStage = smem + C::kResidentBytes;  // stage: [K tile | V tile]
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(sStage + C::kStages * C::kStageBytes + C::kAuxBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int i = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // query tile, heavy first
+  const int kv_tiles = (p.seq_k + kTile - 1) / kTile;
+  const int nkv = p.causal ? min(i + 1, kv_tiles) : kv_tiles;
+  const int U = 2 * nkv;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->res_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->st_full[s], 1);
+      mbar_init(&bars->st_empty[s], 1);
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->p_full[s], 128);
+    }
+    mbar_init(&bars->done, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv); prefetch_tmap(&tdo);
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(&bars->res_full, C::kResidentBytes);
+#pragma unroll
+      for (int h = 0; h < C::kHalves; ++h) {
+        tma_load_4d(sQ + h * 16384, &tq, &bars->res_full, h * 64, i * kTile, head, batch);
+        tma_load_4d(sDO + h * 16384, &tdo, &bars->res_full, h * 64, i * kTile, head, batch);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = 0; t < nkv; ++t) {
+        if (!mbar_wait(&bars->st_empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
+        uint8_t* sk = sStage + stage * C::kStageBytes;
+        uint8_t* sv = sk + C::kTileBytes;
+        mbar_expect_tx(&bars->st_full[stage], C::kStageBytes);
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h) {
+          tma_load_4d(sk + h * 16384, &tk, &bars->st_full[stage], h * 64, t * kTile, head, batch);
+          tma_load_4d(sv + h * 16384, &tv, &bars->st_full[stage], h * 64, t * kTile, head, batch);
+        }
+        if (++stage == 2) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const int fmt = p.dtype == kBF16 ? 1 : 0;
+      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, 128, 64);
+      const uint32_t idesc_acc = make_idesc_f16(fmt, 0, 1, 128, D);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      auto issue_sdp = [&](int u) {
+        const int stage = (u >> 1) & 1, sub = u & 1, b = u & 1;
+        const uint32_t aK = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
+        const uint32_t aV = aK + C::kTileBytes;
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f16(tmem_base + b * 128,
+                       make_smem_desc_sw128(aQ + h * 16384 + k * 32, 16, 1024),
+                       make_smem_desc_sw128(aK + h * 16384 + k * 32, 16, 1024), idesc_s,
+                       (h | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int h = 0; h < C::kHalves; ++h)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f16(tmem_base + b * 128 + 64,
+                       make_smem_desc_sw128(aDO + h * 16384 + k * 32, 16, 1024),
+                       make_smem_desc_sw128(aV + h * 16384 + k * 32, 16, 1024), idesc_s,
+                       (h | k) != 0 ? 1u : 0u);
+        tc_commit(&bars->s_full[b]);
+      };
+      bool ok = mbar_wait(&bars->res_full, 0, p.status, kStatusTimeoutFull);
+      if (ok && U > 0) {
+        ok = mbar_wait(&bars->st_full[0], 0, p.status, kStatusTimeoutFull);
+        tc_fence_after();
+        if (ok) { issue_sdp(0); issue_sdp(1); }
+      }
+      for (int u = 0; u < U && ok; ++u) {
+        const int b = u & 1, stage = (u >> 1) & 1, sub = u & 1;
+        ok = mbar_wait(&bars->p_full[b], (u >> 1) & 1, p.status, kStatusTimeoutTmemFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // dQ += dS K
+          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + 64 + k * 8,
+                        make_smem_desc_sw128(aK + k * 2048, 16384, 1024), idesc_acc,
+                        (u | k) != 0 ? 1u : 0u);
+        if (sub == 1) tc_commit(&bars->st_empty[stage]);
+        if (u + 2 < U) {
+          const int u2 = u + 2;
+          if ((u2 & 1) == 0) {
+            ok = mbar_wait(&bars->st_full[(u2 >> 1) & 1], (u2 >> 2) & 1, p.status, kStatusTimeoutFull);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_sdp(u2);
+        }
+      }
+      tc_commit(&bars->done);
+    }
+  } else {
+    const int wg = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int r_local = quarter * 32 + lane;     // query row inside the tile
+    const int q_row = i * kTile + r_local;
+    const bool row_ok = q_row < p.seq_q;
+    const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + wg * 128 + lane_bits;
+    const uint32_t dp_addr = s_addr + 64;
+    const float sl2 = p.scale * kLog2e;
+    const int64_t bh = (static_cast<int64_t>(batch) * p.heads + head) * p.seq_q;
+    const float lse2 = row_ok ? p.lse[bh + q_row] * kLog2e : INFINITY;
+    const float delta = row_ok ? p.delta[bh + q_row] : 0.f;
+    bool ok = true;
+    for (int t = 0; t < nkv && ok; ++t) {
+      ok = mbar_wait(&bars->s_full[wg], t & 1, p.status, kStatusTimeoutTmemFull);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diag = p.causal && (t == i);
+      const int kv0 = t * kTile + wg * 64;       // first key index of this sub-tile
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(s_addr + c * 32, rs);
+        tmem_ld_32x32b_x32(dp_addr + c * 32, rd);
+        tmem_ld_wait();
+        uint32_t dk[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const int col = c * 32 + 2 * x;
+          const int kl = wg * 64 + col;            // key row inside the 128-row tile
+          float p0 = exp2f(__uint_as_float(rs[2 * x]) * sl2 - lse2);
+          float p1 = exp2f(__uint_as_float(rs[2 * x + 1]) * sl2 - lse2);
+          if ((diag && kl > r_local) || (kv0 + col >= p.seq_k)) p0 = 0.f;
+          if ((diag && kl + 1 > r_local) || (kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(rd[2 * x]) - delta);
+          const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - delta);
+          dk[x] = pack_pair(d0, d1, p.dtype);
+        }
+        tmem_st_32x32b_x16(dp_addr + c * 16, dk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[wg]);
+    }
+    if (ok) ok = mbar_wait(&bars->done, 0, p.status, kStatusTimeoutTmemFull);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && U > 0) {
+      tc_fence_after();
+      // each warpgroup stores half of the head dimension
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.dq) + batch * p.dq_strides[0] +
+                       static_cast<int64_t>(q_row) * p.dq_strides[1] + head * p.dq_strides[2];
+      const uint32_t acc_addr = tmem_base + 256 + lane_bits;
+#pragma unroll 1
+      for (int c = wg * (D / 64); c < (wg + 1) * (D / 64); ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(acc_addr + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * p.scale, __uint_as_float(r[q * 8 + 1]) * p.scale, p.dtype);
+            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * p.scale, __uint_as_float(r[q * 8 + 3]) * p.scale, p.dtype);
+            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * p.scale, __uint_as_float(r[q * 8 + 5]) * p.scale, p.dtype);
+            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * p.scale, __uint_as_float(r[q * 8 + 7]) * p.scale, p.dtype);
+            dst[q] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
+  using C = BwdCfg<D>;
+  CUtensorMap tq, tk, tv, tdo;
+  ETHB_TRY(make_tmap_bshd(&tq, a.q, a.dtype, D, a.seq_q, a.heads, a.batch, a.q_strides, kTile), "bwd tensor map q");
+  ETHB_TRY(make_tmap_bshd(&tk, a.k, a.dtype, D, a.seq_k, a.heads, a.batch, a.k_strides, kTile), "bwd tensor map k");
+  ETHB_TRY(make_tmap_bshd(&tv, a.v, a.dtype, D, a.seq_k, a.heads, a.batch, a.v_strides, kTile), "bwd tensor map v");
+  ETHB_TRY(make_tmap_bshd(&tdo, a.d_o, a.dtype, D, a.seq_q, a.heads, a.batch, a.do_strides, kTile), "bwd tensor map dO");
+  static bool attr = false;
+  if (!attr) {
+    ETHB_TRY(cudaFuncSetAttribute(attn_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  C::kSmemBytes), "bwd smem attribute dkdv");
+    ETHB_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  C::kSmemBytes), "bwd smem attribute dq");
+    attr = true;
+  }
+  const int64_t rows = static_cast<int64_t>(a.batch) * a.seq_q * a.heads;
+  attn_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(a);
+  dim3 gkv((a.seq_k + kTile - 1) / kTile, a.heads, a.batch);
+  attn_bwd_dkdv_kernel<D><<<gkv, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+  dim3 gq((a.seq_q + kTile - 1) / kTile, a.heads, a.batch);
+  attn_bwd_dq_kernel<D><<<gq, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+  count_launch(3);
+  ETHB_TRY(cudaGetLastError(), "bwd kernel launch");
+  return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t st) {
+  if (a.dtype != kF16 && a.dtype != kBF16) return cudaErrorInvalidValue;
+  if (a.causal && a.seq_q != a.seq_k) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a.o) & 15) || a.o_strides[1] % 8 || a.o_strides[2] % 8 ||
+      a.o_strides[0] % 8)
+    return cudaErrorMisalignedAddress;
+  if (a.head_dim == 128) return launch_fwd<128>(a, st);
+  if (a.head_dim == 64) return launch_fwd<64>(a, st);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t attention_bwd(const AttnArgs& a, cudaStream_t st) {
+  ETHB_RETURN_IF(a.dtype != kF16 && a.dtype != kBF16, cudaErrorInvalidValue, "attention dtype");
+  ETHB_RETURN_IF(a.causal && a.seq_q != a.seq_k, cudaErrorInvalidValue, "causal needs seq_q == seq_k");
+  const void* outs[3] = {a.dq, a.dk, a.dv};
+  const int64_t* strs[3] = {a.dq_strides, a.dk_strides, a.dv_strides};
+  for (int i = 0; i < 3; ++i) {
+    if (reinterpret_cast<uintptr_t>(outs[i]) & 15) return cudaErrorMisalignedAddress;
+    for (int k = 0; k < 3; ++k)
+      if (strs[i][k] % 8) return cudaErrorMisalignedAddress;
+  }
+  if (a.head_dim == 128) return launch_bwd<128>(a, st);
+  if (a.head_dim == 64) return launch_bwd<64>(a, st);
+  ETHB_RETURN_IF(true, cudaErrorInvalidValue, "head_dim must be 64 or 128");
+}
+
 }  // namespace ethb

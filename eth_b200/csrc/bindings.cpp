@@ -25,7 +25,7 @@ int dtype_code(const Tensor& t) {
 }
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 void check(cudaError_t e, const char* what) {
-  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e), " [", ethb::last_error_detail(), "]");
 }
 const void* optptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 void need_cuda(const Tensor& t, const char* name) {

@@ -29,6 +29,18 @@ namespace ethb {
 static std::atomic<int64_t> g_launches{0};
 int64_t launch_count() { return g_launches.load(); }
 void count_launch(int n) { g_launches.fetch_add(n); }
+static thread_local const char* g_error_detail = "";
+const char* last_error_detail() { return g_error_detail; }
+void set_error_detail(const char* where) { g_error_detail = where; }
+// Driver entry points (cuTensorMapEncodeTiled) need a context bound to the calling thread; a
+// fresh thread (e.g. the autograd engine's) has none until its first runtime call.
+void ensure_thread_context() {
+  static thread_local bool ready = false;
+  if (!ready) {
+    cudaFree(nullptr);
+    ready = true;
+  }
+}
 
 namespace {
 
@@ -353,6 +365,7 @@ cudaError_t make_tmap_2d_16bit(CUtensorMap* map, const void* base, int dtype, ui
                                uint32_t box_outer) {
   EncodeFn fn = get_encode_fn();
   if (!fn) return cudaErrorNotSupported;
+  ensure_thread_context();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0)
     return cudaErrorMisalignedAddress;
   cuuint64_t dims[2] = {inner, outer};

@@ -35,6 +35,15 @@ struct GemmArgs {
 // Returns cudaSuccess or the launch/encode error. Never allocates.
 cudaError_t gemm_tcgen05(const GemmArgs& args, cudaStream_t stream);
 
+// Where the last failing launcher of this thread gave up (empty if none).
+void ensure_thread_context();
+const char* last_error_detail();
+void set_error_detail(const char* where);
+#define ETHB_RETURN_IF(cond, err, where) \
+  do { if (cond) { ::ethb::set_error_detail(where); return (err); } } while (0)
+#define ETHB_TRY(expr, where) \
+  do { cudaError_t e__ = (expr); if (e__ != cudaSuccess) { ::ethb::set_error_detail(where); return e__; } } while (0)
+
 // Number of kernel launches made by this library since load (for bench accounting).
 int64_t launch_count();
 void count_launch(int n = 1);
