@@ -219,7 +219,7 @@ void grad_norm_sq(const Tensor& grad, double inv_scale, Tensor& acc) {
 void fused_adam(Tensor& param, Tensor& master, const Tensor& grad, Tensor& exp_avg,
                 Tensor& exp_avg_sq, const OptTensor& ctrl, double lr, double beta1, double beta2,
                 double eps, double weight_decay, int64_t step, double inv_scale, double max_norm,
-                bool adamw) {
+                bool adamw, bool scale_from_ctrl) {
   c10::cuda::CUDAGuard guard(param.device());
   ethb::AdamArgs a{};
   a.param = param.data_ptr();
@@ -238,6 +238,7 @@ void fused_adam(Tensor& param, Tensor& master, const Tensor& grad, Tensor& exp_a
   a.bias_correction2 = static_cast<float>(1.0 - std::pow(beta2, static_cast<double>(step)));
   a.ctrl = ctrl.has_value() ? ctrl->data_ptr<float>() : nullptr;
   a.inv_scale = static_cast<float>(inv_scale);
+  a.scale_from_ctrl = scale_from_ctrl;
   a.max_norm = static_cast<float>(max_norm);
   a.adamw = adamw;
   check(ethb::fused_adam(a, cur_stream()), "fused_adam");

@@ -578,12 +578,16 @@ template <typename P, typename G>
 __global__ void adam_kernel(AdamArgs a) {
   const float found_inf = a.ctrl ? a.ctrl[1] : 0.f;
   if (found_inf != 0.f) return;  // overflow: the whole step is skipped on every rank
+  // ctrl[0] holds the sum of squares of the raw (loss-scaled, not yet normalised) gradients;
+  // ctrl[2], when used, the factor that turns a raw gradient into the true one
+  // (loss normalisation / loss scale), so neither value ever has to visit the host.
+  const float inv_scale = (a.ctrl && a.scale_from_ctrl) ? a.ctrl[2] : a.inv_scale;
   float clip = 1.0f;
   if (a.ctrl && a.max_norm > 0.f) {
-    const float norm = sqrtf(a.ctrl[0]);
+    const float norm = sqrtf(a.ctrl[0]) * inv_scale;
     clip = fminf(1.0f, a.max_norm / (norm + 1.0e-6f));
   }
-  const float gscale = a.inv_scale * clip;
+  const float gscale = inv_scale * clip;
   P* param = reinterpret_cast<P*>(a.param);
   const G* grad = reinterpret_cast<const G*>(a.grad);
   const float step = a.lr / a.bias_correction1;

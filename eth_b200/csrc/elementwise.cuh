@@ -71,7 +71,7 @@ cudaError_t ce_bwd(void* logits, const int64_t* targets, const float* gmax, cons
                    int dtype, cudaStream_t st);
 
 // ---- optimizer -----------------------------------------------------------------------------------
-// acc[0] += sum(g^2) (g scaled by inv_scale), acc[1] = 1 if any non-finite value was seen.
+// acc[0] += sum((g * inv_scale)^2), acc[1] = 1 if any non-finite value was seen.
 cudaError_t grad_norm_sq(const void* grad, int64_t n, int grad_dtype, float inv_scale, float* acc,
                          cudaStream_t st);
 struct AdamArgs {
@@ -85,9 +85,11 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay;
   float bias_correction1, bias_correction2;
   // Device scalars so no host synchronisation is needed:
-  //   ctrl[0] = sum of squared (unscaled) gradients over the whole model, ctrl[1] = found-inf flag
+  //   ctrl[0] = sum of squares of the (still loss-scaled) gradients over the whole model,
+  //   ctrl[1] = found-inf flag, ctrl[2] = raw-to-true gradient factor (read when scale_from_ctrl != 0)
   const float* ctrl;
-  float inv_scale;      // 1 / loss scale
+  int scale_from_ctrl;
+  float inv_scale;      // raw-to-true gradient factor from the host (used when scale_from_ctrl == 0)
   float max_norm;       // <= 0 disables clipping
   int adamw;            // decoupled weight decay
 };

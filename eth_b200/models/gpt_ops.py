@@ -1,0 +1,496 @@
+"""The GPT op graph: one class per manifest op, each with an explicit forward and backward.
+
+A GPT model is the flat op list `[encoder-embedding] + 10 ops * L + [final-layernorm,
+gpt-post-process]` (reference: eth/runtime/megatron/model/flex_gpt.py:23-43); a pipeline stage owns
+a contiguous op range, so a stage cut may fall inside a layer. Ops exchange *named* tensors through
+an environment dict (reference: the dict-of-tensors boundary of model/flex_model.py:171-240):
+
+    hidden_states      main stream, [tokens, features] (tokens = batch*seq, batch-major)
+    hidden_states_1/2  residual saved by the 1st / 2nd LayerNorm, consumed by the dropout-add op
+    qkv                packed per-head [q|k|v], [tokens, 3*hidden/tp]
+    output_bias        bias of a row-parallel GEMM, added after the tensor-parallel reduction
+
+Differences from the reference that are deliberate B200 design:
+  * no autograd graph: `fwd` stores what `bwd` needs in a per-micro-batch context;
+  * biases, GeLU, GeLU-gradient and the gradient accumulation into `main_grad` run in GEMM epilogues;
+  * activations stay token-major, so every GEMM / attention operand is TMA-addressable in place.
+"""
+from __future__ import annotations
+
+import hashlib
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..contract.config import FIRST_OP, LAYER_OPS, TAIL_OPS
+from ..ops import raw
+
+
+# ------------------------------------------------------------------------------------------
+# configuration and parameter specs
+# ------------------------------------------------------------------------------------------
+@dataclass
+class GPTModelConfig:
+    num_layers: int
+    hidden_size: int
+    num_attention_heads: int
+    seq_length: int
+    max_position_embeddings: int
+    padded_vocab_size: int
+    hidden_dropout: float = 0.0
+    layernorm_epsilon: float = 1e-5
+    init_method_std: float = 0.02
+    params_dtype: torch.dtype = torch.bfloat16
+    grad_dtype: torch.dtype = torch.float32
+    seed: int = 1234
+    canonical_init: bool = False     # U(-0.02, 0.02) seeded by sha256(logical id), CPU generator
+    zero_labels: bool = False        # the reference's synthetic labels are all zero
+
+    @property
+    def ffn_hidden_size(self) -> int:
+        return 4 * self.hidden_size
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+
+@dataclass
+class ParamSpec:
+    """One parameter of one op: its logical identity and how this rank's piece is cut from it."""
+    local_name: str                   # attribute name inside the op
+    logical_id: str                   # topology-independent identity, e.g. gpt.layers.3.mlp.dense_h_to_4h.weight
+    full_shape: Tuple[int, ...]
+    partition_dim: int                # -1: replicated across TP
+    partition_stride: int = 1
+    init: str = "normal"              # normal | scaled_normal | ones | zeros
+    weight_decay: bool = True
+    shared_with: Optional[str] = None  # logical id this parameter is tied to (same storage if same stage)
+
+    def local_shape(self, tp: int) -> Tuple[int, ...]:
+        if self.partition_dim < 0:
+            return tuple(self.full_shape)
+        s = list(self.full_shape)
+        s[self.partition_dim] //= tp
+        return tuple(s)
+
+
+class TPComm:
+    """Tensor-parallel communication of one stage. `size == 1` makes every call a no-op."""
+
+    def __init__(self, size: int = 1, rank: int = 0, group=None, backend=None):
+        self.size, self.rank, self.group, self.backend = size, rank, group, backend
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size > 1:
+            if self.backend is not None:
+                return self.backend.all_reduce_(t)
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    def gather_stats(self, stats: torch.Tensor) -> torch.Tensor:
+        """[rows, 3] -> [tp, rows, 3] (cross-entropy statistics)."""
+        if self.size == 1:
+            return stats.unsqueeze(0)
+        out = torch.empty((self.size,) + tuple(stats.shape), dtype=stats.dtype, device=stats.device)
+        torch.distributed.all_gather_into_tensor(out.view(-1), stats.contiguous().view(-1), group=self.group)
+        return out
+
+
+def _seed_for(logical_id: str, base: int) -> int:
+    h = hashlib.sha256(f"{base}:{logical_id}".encode()).digest()
+    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
+
+
+def init_full_tensor(spec: ParamSpec, cfg: GPTModelConfig, device) -> torch.Tensor:
+    """The full logical tensor in fp32; a rank slices its shard from it, so the initial weights do
+    not depend on the parallel layout (reference evidence init: grad_sync/evidence.py:12-126)."""
+    if spec.init == "ones":
+        return torch.ones(spec.full_shape, dtype=torch.float32, device=device)
+    if spec.init == "zeros":
+        return torch.zeros(spec.full_shape, dtype=torch.float32, device=device)
+    if cfg.canonical_init:
+        g = torch.Generator(device="cpu")
+        g.manual_seed(int.from_bytes(hashlib.sha256(spec.logical_id.encode()).digest()[:8], "little") & ((1 << 63) - 1))
+        full = (torch.rand(spec.full_shape, generator=g, dtype=torch.float32) * 2 - 1) * 0.02
+        return full.to(device)
+    g = torch.Generator(device=device)
+    g.manual_seed(_seed_for(spec.shared_with or spec.logical_id, cfg.seed))
+    std = cfg.init_method_std
+    if spec.init == "scaled_normal":
+        std = std / math.sqrt(2.0 * cfg.num_layers)
+    return torch.randn(spec.full_shape, generator=g, dtype=torch.float32, device=device) * std
+
+
+def shard_of(full: torch.Tensor, spec: ParamSpec, tp: int, tp_rank: int) -> torch.Tensor:
+    if spec.partition_dim < 0 or tp == 1:
+        return full
+    n = full.shape[spec.partition_dim]
+    chunk = n // (tp * spec.partition_stride)
+    parts = [full.narrow(spec.partition_dim, (b * tp + tp_rank) * chunk, chunk) for b in range(spec.partition_stride)]
+    return parts[0] if len(parts) == 1 else torch.cat(parts, spec.partition_dim)
+
+
+# ------------------------------------------------------------------------------------------
+# op base
+# ------------------------------------------------------------------------------------------
+class Op:
+    """Base of all stage-program ops. Subclasses define `specs`, `fwd`, `bwd`, `reads`, `writes`."""
+    reads: Tuple[str, ...] = ("hidden_states",)
+    writes: Tuple[str, ...] = ("hidden_states",)
+    consumes: Tuple[str, ...] = ()     # names removed from the environment by this op
+
+    def __init__(self, name: str, op_index: int, layer_index: Optional[int], cfg: GPTModelConfig, tp: TPComm):
+        self.name, self.op_index, self.layer_index, self.cfg, self.tp = name, op_index, layer_index, cfg, tp
+        self.params: Dict[str, torch.Tensor] = {}
+        self.fuse_next = False   # set by the stage builder when the following op is fused into this one
+        self.fuse_prev = False
+
+    def specs(self) -> List[ParamSpec]:
+        return []
+
+    def _lid(self, suffix: str) -> str:
+        return f"gpt.layers.{self.layer_index}.{suffix}"
+
+    def p(self, name: str) -> torch.Tensor:
+        return self.params[name]
+
+    def fwd(self, env: dict, ctx: dict, mb) -> None:
+        raise NotImplementedError
+
+    def bwd(self, genv: dict, ctx: dict, mb) -> None:
+        raise NotImplementedError
+
+    def dropout_offset(self, mb) -> int:
+        """Philox offset: distinct per optimizer step, micro-batch and data-parallel replica, equal
+        across the tensor-parallel ranks of a replica (they must draw the same mask)."""
+        return ((int(getattr(mb, "global_step", 0)) << 24) + (int(getattr(mb, "index", 0)) << 8)
+                + int(getattr(mb, "dp_rank", 0)))
+
+    def __repr__(self):
+        return f"{type(self).__name__}({self.op_index}:{self.name})"
+
+
+def _take(genv: dict, name: str):
+    g = genv.pop(name, None)
+    if g is None:
+        raise RuntimeError(f"missing gradient for {name}")
+    return g
+
+
+def _acc(genv: dict, name: str, g: torch.Tensor) -> None:
+    old = genv.get(name)
+    if old is None:
+        genv[name] = g
+    else:
+        old.add_(g)
+
+
+# ------------------------------------------------------------------------------------------
+# embedding
+# ------------------------------------------------------------------------------------------
+class EmbeddingOp(Op):
+    """Vocab-parallel word embedding + position embedding (+ dropout). TP ranks hold vocab shards;
+    partial rows are summed over the TP group (reference: mpu/layers.py:136-205)."""
+    reads = ("enc_input_ids",)
+    writes = ("hidden_states",)
+
+    def specs(self):
+        c = self.cfg
+        return [ParamSpec("word", "gpt.word_embeddings.weight", (c.padded_vocab_size, c.hidden_size), 0),
+                ParamSpec("pos", "gpt.position_embeddings.weight", (c.max_position_embeddings, c.hidden_size), -1)]
+
+    def fwd(self, env, ctx, mb):
+        tokens = env["enc_input_ids"]
+        seq = tokens.shape[-1]
+        vstart = self.tp.rank * (self.cfg.padded_vocab_size // self.tp.size)
+        out = raw.embedding_fwd(tokens, self.p("word"), self.p("pos"), seq, vstart, self.tp.rank == 0)
+        self.tp.all_reduce_(out)
+        p = self.cfg.hidden_dropout
+        if p > 0:
+            ctx["drop"] = (p, self.cfg.seed + self.op_index, self.dropout_offset(mb))
+            out = raw.bias_dropout_add_fwd(out, None, None, *ctx["drop"])
+        ctx["tokens"], ctx["seq"], ctx["vstart"] = tokens, seq, vstart
+        env["hidden_states"] = out
+
+    def bwd(self, genv, ctx, mb):
+        d = _take(genv, "hidden_states")
+        if "drop" in ctx:
+            d = raw.dropout_bwd(d, *ctx["drop"])
+        # position embeddings are replicated: every TP rank accumulates the full gradient
+        raw.embedding_bwd(ctx["tokens"], d, self.p("word"), self.p("pos"), ctx["seq"], ctx["vstart"], True)
+
+
+# ------------------------------------------------------------------------------------------
+# transformer layer ops
+# ------------------------------------------------------------------------------------------
+class LayerNormOp(Op):
+    """LayerNorm that also publishes its input as the residual of the following sub-block."""
+
+    def __init__(self, *a, residual_name: Optional[str], prefix: str, **k):
+        super().__init__(*a, **k)
+        self.residual_name, self.prefix = residual_name, prefix
+        self.writes = ("hidden_states",) + ((residual_name,) if residual_name else ())
+
+    def specs(self):
+        h = self.cfg.hidden_size
+        base = self._lid(self.prefix) if self.layer_index is not None else "gpt.final_layernorm"
+        return [ParamSpec("weight", base + ".weight", (h,), -1, init="ones", weight_decay=False),
+                ParamSpec("bias", base + ".bias", (h,), -1, init="zeros", weight_decay=False)]
+
+    def fwd(self, env, ctx, mb):
+        x = env["hidden_states"]
+        y, mean, rstd = raw.ln_fwd(x, self.p("weight"), self.p("bias"), self.cfg.layernorm_epsilon)
+        ctx["x"], ctx["mean"], ctx["rstd"] = x, mean, rstd
+        if self.residual_name:
+            env[self.residual_name] = x
+        env["hidden_states"] = y
+
+    def bwd(self, genv, ctx, mb):
+        dy = _take(genv, "hidden_states")
+        dx = raw.ln_bwd(dy, ctx["x"], self.p("weight"), self.p("bias"), ctx["mean"], ctx["rstd"])
+        if self.residual_name:
+            res = genv.pop(self.residual_name, None)
+            if res is not None:
+                dx.add_(res)
+        genv["hidden_states"] = dx
+
+
+class ColumnLinearOp(Op):
+    """Column-parallel GEMM: weight [out/tp, in]; forward needs no communication, the data gradient
+    is summed over the TP group (reference: mpu/layers.py:282-370, mappings.py:84-97)."""
+
+    def __init__(self, *a, in_features: int, out_features: int, suffix: str, out_name: str = "hidden_states", **k):
+        super().__init__(*a, **k)
+        self.in_features, self.out_features, self.suffix, self.out_name = in_features, out_features, suffix, out_name
+        self.writes = (out_name,)
+        self.consumes = ("hidden_states",) if out_name != "hidden_states" else ()
+
+    def specs(self):
+        return [ParamSpec("weight", self._lid(self.suffix + ".weight"), (self.out_features, self.in_features), 0),
+                ParamSpec("bias", self._lid(self.suffix + ".bias"), (self.out_features,), 0, init="zeros",
+                          weight_decay=False)]
+
+    def fwd(self, env, ctx, mb):
+        x = env.pop("hidden_states")
+        ctx["x"] = x
+        if self.fuse_next:   # GeLU in the GEMM epilogue
+            pre, act = raw.linear_fwd(x, self.p("weight"), self.p("bias"), gelu=True)
+            env[self.out_name] = pre
+            env["_gelu_out"] = act
+        else:
+            env[self.out_name] = raw.linear_fwd(x, self.p("weight"), self.p("bias"))
+
+    def bwd(self, genv, ctx, mb):
+        dy = _take(genv, self.out_name)
+        dx = raw.linear_dgrad(dy, self.p("weight"))
+        self.tp.all_reduce_(dx)
+        raw.linear_wgrad(dy, ctx["x"], self.p("weight"), self.p("bias"))
+        genv["hidden_states"] = dx
+
+
+class RowLinearOp(Op):
+    """Row-parallel GEMM: weight [out, in/tp]; partial outputs are summed over the TP group, the
+    bias travels separately (`output_bias`) and is added by the following dropout-add op
+    (reference: mpu/layers.py:373-468, model/flex_ops.py:1600-1632)."""
+    writes = ("hidden_states", "output_bias")
+
+    def __init__(self, *a, in_features: int, out_features: int, suffix: str, **k):
+        super().__init__(*a, **k)
+        self.in_features, self.out_features, self.suffix = in_features, out_features, suffix
+
+    def specs(self):
+        return [ParamSpec("weight", self._lid(self.suffix + ".weight"), (self.out_features, self.in_features), 1,
+                          init="scaled_normal"),
+                ParamSpec("bias", self._lid(self.suffix + ".bias"), (self.out_features,), -1, init="zeros",
+                          weight_decay=False)]
+
+    def fwd(self, env, ctx, mb):
+        x = env["hidden_states"]
+        ctx["x"] = x
+        y = raw.linear_fwd(x, self.p("weight"))
+        self.tp.all_reduce_(y)
+        env["hidden_states"] = y
+        env["output_bias"] = self.p("bias")
+
+    def bwd(self, genv, ctx, mb):
+        dy = _take(genv, "hidden_states")
+        db = genv.pop("output_bias", None)
+        if db is not None:
+            self.p("bias").main_grad.view(-1).add_(db.to(self.p("bias").main_grad.dtype).view(-1))
+        gelu_pre = mb.ctxs[self.op_index - 1]["pre"] if self.fuse_prev else None
+        genv["hidden_states"] = raw.linear_dgrad(dy, self.p("weight"), gelu_pre=gelu_pre)
+        if gelu_pre is not None:
+            genv["_gelu_grad_done"] = True
+        raw.linear_wgrad(dy, ctx["x"], self.p("weight"))
+
+
+class FlashAttentionOp(Op):
+    """Causal self-attention over this rank's heads; consumes the packed qkv tensor
+    (reference: model/flex_ops.py:1377-1426 + F.scaled_dot_product_attention :66-96)."""
+    reads = ("qkv",)
+    writes = ("hidden_states",)
+    consumes = ("qkv",)
+
+    def fwd(self, env, ctx, mb):
+        qkv = env.pop("qkv")
+        heads = self.cfg.num_attention_heads // self.tp.size
+        out, lse = raw.attention_fwd(qkv, mb.batch, mb.seq, heads, self.cfg.head_dim)
+        ctx["qkv"], ctx["out"], ctx["lse"], ctx["shape"] = qkv, out, lse, (mb.batch, mb.seq, heads)
+        env["hidden_states"] = out
+
+    def bwd(self, genv, ctx, mb):
+        d = _take(genv, "hidden_states")
+        b, s, heads = ctx["shape"]
+        genv["qkv"] = raw.attention_bwd(d.contiguous(), ctx["qkv"], ctx["out"], ctx["lse"], b, s, heads,
+                                        self.cfg.head_dim)
+
+
+class BiasDropoutAddOp(Op):
+    """hidden = residual + dropout(hidden + output_bias) (reference: model/flex_ops.py:104-134)."""
+
+    def __init__(self, *a, residual_name: str, **k):
+        super().__init__(*a, **k)
+        self.residual_name = residual_name
+        self.reads = ("hidden_states", "output_bias", residual_name)
+        self.consumes = ("output_bias", residual_name)
+
+    def fwd(self, env, ctx, mb):
+        x, bias, res = env["hidden_states"], env.pop("output_bias"), env.pop(self.residual_name)
+        p = self.cfg.hidden_dropout
+        ctx["drop"] = (p, self.cfg.seed + self.op_index, self.dropout_offset(mb))
+        env["hidden_states"] = raw.bias_dropout_add_fwd(x, bias, res, *ctx["drop"])
+
+    def bwd(self, genv, ctx, mb):
+        dout = _take(genv, "hidden_states")
+        dx = raw.dropout_bwd(dout, *ctx["drop"])
+        genv["hidden_states"] = dx
+        genv[self.residual_name] = dout
+        genv["output_bias"] = raw.colsum(dx, out_dtype=torch.float32)
+
+
+class GeluOp(Op):
+    """tanh-GeLU. When the preceding GEMM already produced it in its epilogue, forward is free;
+    when the following row-parallel GEMM multiplies by gelu' in its data-gradient epilogue,
+    backward is free as well."""
+
+    def fwd(self, env, ctx, mb):
+        pre = env["hidden_states"]
+        ctx["pre"] = pre
+        act = env.pop("_gelu_out", None)
+        if act is None:
+            act = raw.gelu_fwd(pre)
+        env["hidden_states"] = act
+
+    def bwd(self, genv, ctx, mb):
+        if genv.pop("_gelu_grad_done", False):
+            return
+        dy = _take(genv, "hidden_states")
+        genv["hidden_states"] = raw.gelu_bwd(dy, ctx["pre"])
+
+
+class PostProcessOp(Op):
+    """Tied LM head (logits = h E^T over this rank's vocab shard) + vocab-parallel cross entropy.
+    Output: per-token losses (reference: model/flex_ops.py:1908-1985, mpu/cross_entropy.py:33-118)."""
+    writes = ("output",)
+    consumes = ("hidden_states",)
+
+    def specs(self):
+        c = self.cfg
+        return [ParamSpec("word", "gpt.word_embeddings.weight", (c.padded_vocab_size, c.hidden_size), 0,
+                          shared_with="gpt.word_embeddings.weight")]
+
+    def fwd(self, env, ctx, mb):
+        x = env.pop("hidden_states")
+        w = self.p("word")
+        logits = raw.linear_fwd(x, w)
+        vstart = self.tp.rank * (self.cfg.padded_vocab_size // self.tp.size)
+        labels = env["labels"]
+        loss, gmax, gsum = raw.ce_fwd(logits, labels, vstart, self.tp.gather_stats if self.tp.size > 1 else None)
+        ctx.update(x=x, logits=logits, labels=labels, gmax=gmax, gsum=gsum, vstart=vstart)
+        env["output"] = loss
+
+    def bwd(self, genv, ctx, mb):
+        dloss = _take(genv, "output")
+        dlogits = raw.ce_bwd_(ctx["logits"], ctx["labels"], ctx["gmax"], ctx["gsum"], dloss, ctx["vstart"])
+        w = self.p("word")
+        dx = raw.linear_dgrad(dlogits, w)
+        self.tp.all_reduce_(dx)
+        raw.linear_wgrad(dlogits, ctx["x"], w)
+        ctx.pop("logits")
+        genv["hidden_states"] = dx
+
+
+# ------------------------------------------------------------------------------------------
+# manifest -> ops
+# ------------------------------------------------------------------------------------------
+def build_op_descriptors(num_layers: int) -> List[dict]:
+    """Runtime op list in manifest order: [{op_index, name, layer_index, prev_name}]."""
+    names: List[Tuple[str, Optional[int]]] = [(FIRST_OP, None)]
+    for layer in range(num_layers):
+        names += [(n, layer) for n in LAYER_OPS]
+    names += [(n, None) for n in TAIL_OPS]
+    out = []
+    for i, (n, layer) in enumerate(names):
+        out.append({"op_index": i, "name": n, "layer_index": layer, "prev_name": names[i - 1][0] if i else None})
+    return out
+
+
+def make_op(desc: dict, cfg: GPTModelConfig, tp: TPComm) -> Op:
+    n, i, layer = desc["name"], desc["op_index"], desc["layer_index"]
+    h, f = cfg.hidden_size, cfg.ffn_hidden_size
+    a = (n, i, layer, cfg, tp)
+    if n == FIRST_OP:
+        return EmbeddingOp(*a)
+    if n == "enc-1st-layernorm":
+        return LayerNormOp(*a, residual_name="hidden_states_1", prefix="input_layernorm")
+    if n == "enc-attention-qkv":
+        return ColumnLinearOp(*a, in_features=h, out_features=3 * h, suffix="attention.query_key_value", out_name="qkv")
+    if n == "enc-flash-attention":
+        return FlashAttentionOp(*a)
+    if n == "enc-attention-dense":
+        return RowLinearOp(*a, in_features=h, out_features=h, suffix="attention.dense")
+    if n == "enc-post-attention-dropout":
+        return BiasDropoutAddOp(*a, residual_name="hidden_states_1")
+    if n == "enc-2nd-layernorm":
+        return LayerNormOp(*a, residual_name="hidden_states_2", prefix="post_attention_layernorm")
+    if n == "enc-MLP-GEMM-1":
+        return ColumnLinearOp(*a, in_features=h, out_features=f, suffix="mlp.dense_h_to_4h")
+    if n == "enc-MLP-gelu":
+        return GeluOp(*a)
+    if n == "enc-MLP-GEMM-2":
+        return RowLinearOp(*a, in_features=f, out_features=h, suffix="mlp.dense_4h_to_h")
+    if n == "enc-post-MLP-dropout":
+        return BiasDropoutAddOp(*a, residual_name="hidden_states_2")
+    if n == "final-layernorm":
+        return LayerNormOp(*a, residual_name=None, prefix="final_layernorm")
+    if n == "gpt-post-process":
+        return PostProcessOp(*a)
+    raise ValueError(f"unknown op {n!r}")
+
+
+# Named tensors alive right after each op, i.e. what crosses a stage boundary placed there:
+# name -> (features, tp_sharded, per_token). `features` is a multiple of hidden_size; a TP-sharded
+# tensor holds features/tp columns per rank; per_token tensors have one row per token (dim 0 is
+# batch-major, so data-parallel ranks own contiguous row blocks), others are [features] vectors.
+_H = ("hidden_states", 1, False, True)
+_R1 = ("hidden_states_1", 1, False, True)
+_R2 = ("hidden_states_2", 1, False, True)
+_B = ("output_bias", 1, False, False)
+LIVE_AFTER = {
+    "encoder-embedding": (_H,),
+    "enc-1st-layernorm": (_H, _R1),
+    "enc-attention-qkv": (("qkv", 3, True, True), _R1),
+    "enc-flash-attention": (("hidden_states", 1, True, True), _R1),
+    "enc-attention-dense": (_H, _B, _R1),
+    "enc-post-attention-dropout": (_H,),
+    "enc-2nd-layernorm": (_H, _R2),
+    "enc-MLP-GEMM-1": (("hidden_states", 4, True, True), _R2),
+    "enc-MLP-gelu": (("hidden_states", 4, True, True), _R2),
+    "enc-MLP-GEMM-2": (_H, _B, _R2),
+    "enc-post-MLP-dropout": (_H,),
+    "final-layernorm": (_H,),
+    "gpt-post-process": (),
+}

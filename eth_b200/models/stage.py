@@ -1,0 +1,203 @@
+"""One pipeline stage of the GPT op graph: parameters, flat buffers, and the explicit
+forward / backward interpreter with op-granular activation recomputation.
+
+Memory layout (B200-first): every parameter of the stage is a view into ONE flat 16-bit buffer,
+its persistent gradient (`main_grad`, the LocalDDP contract of
+eth/runtime/megatron/model/distributed.py:68-123) a view into ONE flat gradient buffer, and the
+fp32 master copy and Adam moments views into flat fp32 buffers with the same element order
+(weight-decayed parameters first). The optimizer, the gradient norm and zeroing then are a
+handful of launches over contiguous memory instead of one per tensor.
+
+Recomputation follows the reference contract (model/flex_model.py:564-588): `recompute_ops` is a
+0/1 list over the stage's ops; every maximal run of 1s (broken at `enc-1st-layernorm`) is executed
+in forward without keeping its op contexts -- only the environment at the run's entry is kept --
+and is re-executed right before its backward. Dropout masks are functions of (seed, offset), so the
+replay is exact without capturing RNG state.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from types import SimpleNamespace
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .gpt_ops import (LIVE_AFTER, GPTModelConfig, Op, ParamSpec, TPComm, build_op_descriptors, init_full_tensor,
+                      make_op, shard_of)
+
+
+@dataclass
+class ParamEntry:
+    op: Op
+    spec: ParamSpec
+    param: torch.Tensor        # view into the flat parameter buffer (carries .main_grad)
+    offset: int                # element offset inside the flat buffers
+    numel: int
+    tied_alias: bool = False   # second use of a tensor that already has an entry (same-stage tying)
+
+
+class MicroBatch(SimpleNamespace):
+    """Per-micro-batch record: index, local batch, seq, global_step, dp_rank, op contexts."""
+
+
+def _align(n: int, a: int = 128) -> int:
+    return (n + a - 1) // a * a
+
+
+class GPTStage:
+    def __init__(self, cfg: GPTModelConfig, op_begin: int, op_end: int, tp: Optional[TPComm] = None,
+                 device="cpu", recompute_ops: Optional[Sequence[int]] = None, fuse: bool = True):
+        self.cfg = cfg
+        self.tp = tp or TPComm()
+        self.device = torch.device(device)
+        self.descriptors = build_op_descriptors(cfg.num_layers)
+        self.op_begin, self.op_end = op_begin, op_end
+        self.ops: List[Op] = [make_op(d, cfg, self.tp) for d in self.descriptors[op_begin:op_end]]
+        self.is_first = op_begin == 0
+        self.is_last = op_end == len(self.descriptors)
+        self.recompute = list(recompute_ops) if recompute_ops is not None else [0] * len(self.ops)
+        if len(self.recompute) != len(self.ops):
+            raise ValueError("recompute_ops length must equal the stage's op count")
+        self._build_params()
+        if fuse:
+            self._mark_fusions()
+        self._segments = self._plan_segments()
+        self._contexts: Dict[int, dict] = {}
+        prev = self.descriptors[op_begin - 1]["name"] if op_begin > 0 else None
+        self.input_spec = LIVE_AFTER[prev] if prev else ()
+        self.output_spec = LIVE_AFTER[self.descriptors[op_end - 1]["name"]]
+
+    # ------------------------------------------------------------------ parameters
+    def _build_params(self):
+        cfg, tp = self.cfg, self.tp
+        entries: List[Tuple[Op, ParamSpec]] = [(op, s) for op in self.ops for s in op.specs()]
+        # a tied parameter that appears twice in one stage gets one storage
+        uniq: List[Tuple[Op, ParamSpec]] = []
+        seen: Dict[str, int] = {}
+        alias: List[Tuple[Op, ParamSpec, int]] = []
+        for op, s in entries:
+            if s.logical_id in seen:
+                alias.append((op, s, seen[s.logical_id]))
+            else:
+                seen[s.logical_id] = len(uniq)
+                uniq.append((op, s))
+        order = sorted(range(len(uniq)), key=lambda i: (0 if uniq[i][1].weight_decay else 1, i))
+        offsets, cursor = {}, 0
+        self.decay_numel = 0
+        for i in order:
+            n = 1
+            for d in uniq[i][1].local_shape(tp.size):
+                n *= d
+            offsets[i] = (cursor, n)
+            cursor += _align(n)
+            if uniq[i][1].weight_decay:
+                self.decay_numel = cursor   # decayed parameters come first, so this ends their region
+        total = max(cursor, 1)
+        dev = self.device
+        self.param_buf = torch.zeros(total, dtype=cfg.params_dtype, device=dev)
+        self.grad_buf = torch.zeros(total, dtype=cfg.grad_dtype, device=dev)
+        self.total_numel = total
+        self.entries: List[ParamEntry] = []
+        by_uniq: Dict[int, ParamEntry] = {}
+        for i, (op, spec) in enumerate(uniq):
+            off, n = offsets[i]
+            shape = spec.local_shape(tp.size)
+            p = self.param_buf[off:off + n].view(shape)
+            full = init_full_tensor(spec, cfg, dev)
+            p.copy_(shard_of(full, spec, tp.size, tp.rank).to(cfg.params_dtype))
+            del full
+            p.main_grad = self.grad_buf[off:off + n].view(shape)
+            p.requires_grad = False
+            op.params[spec.local_name] = p
+            e = ParamEntry(op, spec, p, off, n)
+            self.entries.append(e)
+            by_uniq[i] = e
+        for op, spec, i in alias:
+            op.params[spec.local_name] = by_uniq[i].param
+            self.entries.append(ParamEntry(op, spec, by_uniq[i].param, by_uniq[i].offset, by_uniq[i].numel, True))
+
+    def unique_entries(self) -> List[ParamEntry]:
+        return [e for e in self.entries if not e.tied_alias]
+
+    def named_parameters(self):
+        for e in self.unique_entries():
+            yield e.spec.logical_id, e.param
+
+    def zero_grad_buffer(self):
+        self.grad_buf.zero_()
+
+    def _mark_fusions(self):
+        for a, b in zip(self.ops, self.ops[1:]):
+            if a.name == "enc-MLP-GEMM-1" and b.name == "enc-MLP-gelu":
+                a.fuse_next = True
+            if a.name == "enc-MLP-gelu" and b.name == "enc-MLP-GEMM-2":
+                b.fuse_prev = True
+
+    # ------------------------------------------------------------------ recompute segments
+    def _plan_segments(self) -> List[Tuple[int, int, bool]]:
+        """Maximal runs [i, j) of equal recompute flag; recompute runs break at enc-1st-layernorm."""
+        segs, i, n = [], 0, len(self.ops)
+        while i < n:
+            flag = bool(self.recompute[i])
+            j = i + 1
+            while j < n and bool(self.recompute[j]) == flag and not (flag and self.ops[j].name == "enc-1st-layernorm"):
+                j += 1
+            segs.append((i, j, flag))
+            i = j
+        return segs
+
+    # ------------------------------------------------------------------ execution
+    def forward(self, mb: MicroBatch, inputs: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        env = dict(inputs)
+        ctxs: Dict[int, dict] = {}
+        mb.ctxs = ctxs
+        saved_envs: Dict[int, dict] = {}
+        for (i, j, recompute) in self._segments:
+            if recompute:
+                saved_envs[i] = dict(env)
+                scratch: Dict[int, dict] = {}
+                mb.ctxs = scratch
+                for op in self.ops[i:j]:
+                    scratch[op.op_index] = {}
+                    op.fwd(env, scratch[op.op_index], mb)
+                mb.ctxs = ctxs
+            else:
+                for op in self.ops[i:j]:
+                    ctxs[op.op_index] = {}
+                    op.fwd(env, ctxs[op.op_index], mb)
+        self._contexts[mb.index] = {"ctxs": ctxs, "envs": saved_envs, "mb": mb}
+        keep = {name for name, *_ in self.output_spec} | ({"output"} if self.is_last else set())
+        return {k: v for k, v in env.items() if k in keep}
+
+    def backward(self, mb_index: int, grad_outputs: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        rec = self._contexts.pop(mb_index)
+        ctxs, saved_envs, mb = rec["ctxs"], rec["envs"], rec["mb"]
+        mb.ctxs = ctxs
+        genv = dict(grad_outputs)
+        for (i, j, recompute) in reversed(self._segments):
+            if recompute:
+                env = saved_envs.pop(i)
+                for op in self.ops[i:j]:
+                    ctxs[op.op_index] = {}
+                    op.fwd(env, ctxs[op.op_index], mb)
+            for op in reversed(self.ops[i:j]):
+                op.bwd(genv, ctxs.pop(op.op_index), mb)
+        keep = {name for name, *_ in self.input_spec}
+        return {k: v for k, v in genv.items() if k in keep and isinstance(v, torch.Tensor)}
+
+    def drop_context(self, mb_index: int) -> None:
+        self._contexts.pop(mb_index, None)
+
+    # ------------------------------------------------------------------ boundary shapes
+    def boundary_shapes(self, spec, tokens: int) -> Dict[str, Tuple[int, ...]]:
+        out = {}
+        h = self.cfg.hidden_size
+        for name, mult, tp_sharded, per_token in spec:
+            feat = mult * h // (self.tp.size if tp_sharded else 1)
+            out[name] = (tokens, feat) if per_token else (feat,)
+        return out
+
+
+def build_full_model(cfg: GPTModelConfig, device="cpu", tp: Optional[TPComm] = None, **kw) -> GPTStage:
+    """The whole op list as a single stage (PP = 1)."""
+    return GPTStage(cfg, 0, 3 + 10 * cfg.num_layers, tp=tp, device=device, **kw)

@@ -1,0 +1,248 @@
+"""Forward / backward primitives without autograd, used by the explicit stage program.
+
+The training runtime does not build an autograd graph: every op of the stage program has a
+hand-written forward and backward that call these primitives, so the host cost per op is one
+Python call into the native library and buffers can be reused deterministically. CUDA tensors
+run the sm_100a kernels; CPU tensors run a PyTorch restatement (tests, validation).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .functional import (AUX_ADD, AUX_GELU_GRAD, AUX_NONE, _keep_mask_ref, _workspace, attention_ref,  # noqa: F401
+                         colsum, gelu_tanh_grad_ref, gemm)
+
+
+def _grad_of(p):
+    mg = getattr(p, "main_grad", None)
+    if mg is None:
+        raise RuntimeError("parameter has no main_grad buffer")
+    return mg
+
+
+# ---------------------------------------------------------------------------------- LayerNorm
+def ln_fwd(x, gamma, beta, eps):
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    if native.use_native(x):
+        y = torch.empty_like(x)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        native.lib().layernorm_fwd(x, gamma, beta, y, mean, rstd, eps)
+        return y, mean, rstd
+    xf = x.float().reshape(rows, hidden)
+    mean = xf.mean(1)
+    rstd = torch.rsqrt(xf.var(1, unbiased=False) + eps)
+    y = ((xf - mean[:, None]) * rstd[:, None] * gamma.float() + beta.float()).to(x.dtype).reshape(x.shape)
+    return y, mean, rstd
+
+
+def ln_bwd(dy, x, gamma, beta, mean, rstd):
+    """Returns dx; accumulates dgamma / dbeta into the parameters' main_grad."""
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    dg, db = _grad_of(gamma).view(-1), _grad_of(beta).view(-1)
+    if native.use_native(x):
+        dx = torch.empty_like(x)
+        parts = native.lib().ln_bwd_parts(rows)
+        native.lib().layernorm_bwd(dy, x, gamma, mean, rstd, dx, dg, db,
+                                   _workspace(x.device, 2 * parts * hidden), True)
+        return dx
+    xf, dyf = x.float().reshape(rows, hidden), dy.float().reshape(rows, hidden)
+    xh = (xf - mean[:, None]) * rstd[:, None]
+    wdy = dyf * gamma.float()
+    m1 = wdy.mean(1, keepdim=True)
+    m2 = (wdy * xh).mean(1, keepdim=True)
+    dg.add_((dyf * xh).sum(0).to(dg.dtype))
+    db.add_(dyf.sum(0).to(db.dtype))
+    return ((wdy - m1 - xh * m2) * rstd[:, None]).to(x.dtype).reshape(x.shape)
+
+
+# ---------------------------------------------------------------------------------- linear
+def linear_fwd(x, weight, bias=None, gelu=False, residual=None):
+    """x W^T (+bias) (+residual). With gelu=True returns (pre_activation, gelu(pre_activation))."""
+    if gelu:
+        pre = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        act = torch.empty_like(pre)
+        gemm(x, weight, out=pre, bias=bias, gelu_out=act)
+        return pre, act
+    if residual is not None:
+        return gemm(x, weight, bias=bias, aux=residual, aux_mode=AUX_ADD)
+    return gemm(x, weight, bias=bias)
+
+
+def linear_dgrad(dy, weight, gelu_pre=None):
+    """dx = dy W, optionally multiplied by gelu'(gelu_pre) in the GEMM epilogue."""
+    if gelu_pre is not None:
+        return gemm(dy, weight, b_mn=True, aux=gelu_pre, aux_mode=AUX_GELU_GRAD)
+    return gemm(dy, weight, b_mn=True)
+
+
+def linear_wgrad(dy, x, weight, bias=None):
+    """main_grad(W) += dy^T x ; main_grad(b) += colsum(dy)."""
+    gemm(dy, x, a_mn=True, b_mn=True, out=_grad_of(weight).view(weight.shape), accumulate=True)
+    if bias is not None:
+        colsum(dy, out=_grad_of(bias).view(-1), accumulate=True)
+
+
+# ---------------------------------------------------------------------------------- GeLU / dropout
+def gelu_fwd(x, bias=None):
+    if native.use_native(x):
+        y = torch.empty_like(x)
+        native.lib().bias_gelu_fwd(x, bias, y)
+        return y
+    return F.gelu(x.float() + (bias.float() if bias is not None else 0.0), approximate="tanh").to(x.dtype)
+
+
+def gelu_bwd(dy, x, bias=None):
+    if native.use_native(x):
+        dx = torch.empty_like(x)
+        native.lib().bias_gelu_bwd(dy, x, bias, dx)
+        return dx
+    v = x.float() + (bias.float() if bias is not None else 0.0)
+    return (dy.float() * gelu_tanh_grad_ref(v)).to(x.dtype)
+
+
+def bias_dropout_add_fwd(x, bias, residual, p, seed, offset):
+    if native.use_native(x):
+        out = torch.empty_like(x)
+        native.lib().bias_dropout_add_fwd(x, bias, residual, out, float(p), int(seed), int(offset))
+        return out
+    v = x.float() + (bias.float() if bias is not None else 0.0)
+    if p > 0:
+        keep = _keep_mask_ref(x.shape, p, seed, offset, x.device)
+        v = torch.where(keep, v / (1.0 - p), torch.zeros_like(v))
+    if residual is not None:
+        v = v + residual.float()
+    return v.to(x.dtype)
+
+
+def dropout_bwd(dy, p, seed, offset):
+    if p <= 0:
+        return dy
+    if native.use_native(dy):
+        dx = torch.empty_like(dy)
+        native.lib().dropout_bwd(dy, dx, float(p), int(seed), int(offset))
+        return dx
+    keep = _keep_mask_ref(dy.shape, p, seed, offset, dy.device)
+    return torch.where(keep, dy.float() / (1.0 - p), torch.zeros_like(dy.float())).to(dy.dtype)
+
+
+def add_(a, b):
+    """a += b for gradient accumulation of residual branches."""
+    return a.add_(b)
+
+
+# ---------------------------------------------------------------------------------- embedding
+def embedding_fwd(tokens, word, pos, seq, vocab_start, add_pos):
+    ntok, hidden = tokens.numel(), word.shape[1]
+    if native.use_native(word):
+        out = torch.empty((ntok, hidden), dtype=word.dtype, device=word.device)
+        native.lib().embedding_fwd(tokens.contiguous(), word, pos, out, seq, vocab_start, add_pos)
+        return out
+    t = tokens.reshape(-1) - vocab_start
+    mine = (t >= 0) & (t < word.shape[0])
+    out = word[t.clamp(0, word.shape[0] - 1)].float() * mine[:, None]
+    if add_pos:
+        out = out + pos[torch.arange(ntok, device=tokens.device) % seq].float()
+    return out.to(word.dtype)
+
+
+def embedding_bwd(tokens, dout, word, pos, seq, vocab_start, add_pos):
+    dword = _grad_of(word).view(word.shape)
+    dpos = _grad_of(pos).view(pos.shape) if add_pos else None
+    if native.use_native(dout):
+        native.lib().embedding_bwd(tokens.contiguous(), dout, dword, dpos, seq, vocab_start, add_pos)
+        return
+    t = tokens.reshape(-1) - vocab_start
+    mine = (t >= 0) & (t < word.shape[0])
+    acc = torch.zeros(word.shape, dtype=torch.float32, device=dout.device)
+    acc.index_add_(0, t[mine], dout.float()[mine])
+    dword.add_(acc.to(dword.dtype))
+    if dpos is not None:
+        accp = torch.zeros(pos.shape, dtype=torch.float32, device=dout.device)
+        accp.index_add_(0, torch.arange(tokens.numel(), device=tokens.device) % seq, dout.float())
+        dpos.add_(accp.to(dpos.dtype))
+
+
+# ---------------------------------------------------------------------------------- cross entropy
+def ce_fwd(logits, targets, vocab_start, gather_fn=None):
+    """Per-token loss; returns (loss, gmax, gsum) with the global softmax statistics for backward."""
+    rows = logits.shape[0]
+    targets = targets.reshape(-1).contiguous()
+    if native.use_native(logits):
+        stats = torch.empty((rows, 3), dtype=torch.float32, device=logits.device)
+        native.lib().ce_local_stats(logits, targets, stats, vocab_start)
+        all_stats = gather_fn(stats) if gather_fn is not None else stats.unsqueeze(0)
+        loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        gmax, gsum = torch.empty_like(loss), torch.empty_like(loss)
+        native.lib().ce_combine(all_stats.contiguous(), loss, gmax, gsum, all_stats.shape[0])
+        return loss, gmax, gsum
+    lf = logits.float()
+    lmax = lf.max(1).values
+    lsum = torch.exp(lf - lmax[:, None]).sum(1)
+    t = targets - vocab_start
+    mine = (t >= 0) & (t < logits.shape[1])
+    tl = lf.gather(1, t.clamp(0, logits.shape[1] - 1)[:, None])[:, 0] * mine
+    stats = torch.stack([lmax, lsum, tl], 1)
+    all_stats = gather_fn(stats) if gather_fn is not None else stats.unsqueeze(0)
+    gmax = all_stats[:, :, 0].max(0).values
+    gsum = (all_stats[:, :, 1] * torch.exp(all_stats[:, :, 0] - gmax)).sum(0)
+    return torch.log(gsum) + gmax - all_stats[:, :, 2].sum(0), gmax, gsum
+
+
+def ce_bwd_(logits, targets, gmax, gsum, dloss, vocab_start):
+    """Overwrites `logits` with d loss / d logits scaled by dloss[row]; returns it."""
+    targets = targets.reshape(-1).contiguous()
+    if native.use_native(logits):
+        native.lib().ce_bwd(logits, targets, gmax, gsum, dloss.float().contiguous(), vocab_start)
+        return logits
+    sm = torch.exp(logits.float() - gmax[:, None]) / gsum[:, None]
+    t = targets - vocab_start
+    mine = (t >= 0) & (t < logits.shape[1])
+    onehot = torch.zeros_like(sm)
+    onehot[mine, t[mine]] = 1.0
+    logits.copy_(((sm - onehot) * dloss.float()[:, None]).to(logits.dtype))
+    return logits
+
+
+# ---------------------------------------------------------------------------------- attention
+def attention_fwd(qkv, batch, seq, heads, head_dim, scale=None, causal=True):
+    """qkv: [batch*seq, heads*3*head_dim] with per-head [q | k | v] blocks. Returns (out[T, heads*d], lse)."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    v5 = qkv.view(batch, seq, heads, 3, head_dim)
+    q, k, v = v5[:, :, :, 0], v5[:, :, :, 1], v5[:, :, :, 2]
+    if native.use_native(qkv):
+        o = torch.empty((batch, seq, heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((batch, heads, seq), dtype=torch.float32, device=qkv.device)
+        native.lib().attn_fwd(q, k, v, o, lse, float(scale), bool(causal), native.status(qkv.device))
+        return o.view(batch * seq, heads * head_dim), lse
+    o = attention_ref(q, k, v, scale, causal).to(qkv.dtype).contiguous()
+    return o.view(batch * seq, heads * head_dim), None
+
+
+def attention_bwd(d_out, qkv, out, lse, batch, seq, heads, head_dim, scale=None, causal=True):
+    """Returns dqkv in the same packed layout as qkv."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    v5 = qkv.view(batch, seq, heads, 3, head_dim)
+    q, k, v = v5[:, :, :, 0], v5[:, :, :, 1], v5[:, :, :, 2]
+    if native.use_native(qkv):
+        dqkv = torch.empty_like(qkv)
+        d5 = dqkv.view(batch, seq, heads, 3, head_dim)
+        delta = torch.empty((batch, heads, seq), dtype=torch.float32, device=qkv.device)
+        native.lib().attn_bwd(q, k, v, out.view(batch, seq, heads, head_dim),
+                              d_out.view(batch, seq, heads, head_dim), lse, d5[:, :, :, 0], d5[:, :, :, 1],
+                              d5[:, :, :, 2], delta, delta, float(scale), bool(causal),
+                              native.status(qkv.device))
+        return dqkv
+    with torch.enable_grad():
+        qd, kd, vd = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+        ref = attention_ref(qd, kd, vd, scale, causal)
+        gq, gk, gv = torch.autograd.grad(ref, (qd, kd, vd), d_out.view(batch, seq, heads, head_dim).float())
+    return torch.stack([gq, gk, gv], 3).to(qkv.dtype).reshape(qkv.shape)

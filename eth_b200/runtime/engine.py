@@ -1,0 +1,285 @@
+"""Training engine of one rank: stage program, pipeline schedule, loss contract, canonical
+gradient sync and the optimizer step.
+
+One iteration (reference call stack: eth/runtime/megatron/training.py:904-1034):
+    zero the gradient buffer
+    forward/backward over this pipeline's micro-batches (no-pipeline or 1F1B schedule)
+    all-reduce [loss_sum, loss_weight] over the world  -> normalisation = nominal / weight
+    canonical gradient sync (bucketed reductions across pipelines and DP replicas)
+    optimizer: norm + overflow agreement over the world, clip, AdamW, refresh 16-bit weights
+    learning-rate schedule and clock advance on success
+The normalisation and the loss scale never go through the host: they are folded into one device
+scalar that the optimizer kernels read.
+"""
+from __future__ import annotations
+
+import math
+import time
+from types import SimpleNamespace
+from typing import Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.gpt_ops import GPTModelConfig, TPComm
+from ..models.stage import GPTStage, MicroBatch
+from ..optim.grad_scaler import ConstantGradScaler, DynamicGradScaler
+from ..optim.lr import AnnealingLR
+from ..optim.optimizer import FlatMixedPrecisionAdam, coalesce_ranges
+from ..parallel.grad_sync.gpt_adapter import collect_gpt_gradient_metadata
+from ..parallel.grad_sync.loss import TrainingClock, local_sample_slots, synthetic_gpt_batch
+from ..parallel.grad_sync.manager import dump_gradient_sync_plan, initialize_gradient_sync
+from ..parallel.p2p import PipelineComm
+from ..parallel.state import ParallelState
+from . import schedules
+from .timers import Timers
+
+
+class _SingleRank:
+    """Stand-in for the process group of a single rank (collectives over it are no-ops)."""
+
+    def __repr__(self):
+        return "<single-rank group>"
+
+
+SINGLE = _SingleRank()
+
+
+class Collectives:
+    """torch.distributed calls used by the engine, gathered in one place so tests can fake them.
+    `group=None` means the world; groups of one rank are the `SINGLE` sentinel."""
+
+    def __init__(self, world_size: int):
+        self.world_size = world_size
+        self.enabled = world_size > 1 and dist.is_available() and dist.is_initialized()
+
+    def create_group(self, ranks):
+        if len(ranks) <= 1:
+            return SINGLE
+        return dist.new_group(list(ranks)) if self.enabled else None
+
+    def all_reduce_sum(self, t, group=None):
+        if self.enabled and group is not SINGLE:
+            dist.all_reduce(t, group=group)
+
+    def all_reduce_max(self, t, group=None):
+        if self.enabled and group is not SINGLE:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+
+    def all_gather_object(self, out_list, obj, group=None):
+        if self.enabled and group is not SINGLE:
+            dist.all_gather_object(out_list, obj, group=group)
+        else:
+            out_list[0] = obj
+
+    def broadcast(self, t, src, group=None):
+        if self.enabled and group is not SINGLE:
+            dist.broadcast(t, src, group=group)
+
+    def barrier(self):
+        if self.enabled:
+            dist.barrier()
+
+
+class TrainEngine:
+    def __init__(self, args, device=None, collectives: Optional[Collectives] = None,
+                 data_provider: Optional[Callable] = None):
+        self.args = args
+        self.device = torch.device(device if device is not None else
+                                   ("cuda:%d" % torch.cuda.current_device() if torch.cuda.is_available() else "cpu"))
+        self.coll = collectives or Collectives(args.world_size)
+        self.timers = Timers()
+        cfg = args.normalized_config
+        self.pstate = ParallelState(cfg, args.rank, self.coll.create_group, topology=args.canonical_topology)
+        ps = self.pstate
+        self.model_cfg = GPTModelConfig(
+            num_layers=cfg["num_layers"], hidden_size=cfg["hidden_size"],
+            num_attention_heads=cfg["num_attention_heads"], seq_length=cfg["seq_length"],
+            max_position_embeddings=cfg.get("max_position_embeddings", cfg["seq_length"]),
+            padded_vocab_size=args.padded_vocab_size, hidden_dropout=args.hidden_dropout,
+            layernorm_epsilon=args.layernorm_epsilon, init_method_std=args.init_method_std,
+            params_dtype=args.params_dtype, grad_dtype=args.grad_dtype, seed=args.seed,
+            canonical_init=getattr(args, "grad_sync_evidence_canonical_init", False),
+            zero_labels=getattr(args, "reference_zero_labels", False))
+        self.tp = self._make_tp_comm()
+        begin, end = ps.op_range
+        self.stage = GPTStage(self.model_cfg, begin, end, tp=self.tp, device=self.device,
+                              recompute_ops=ps.recompute_ops)
+        self.seq_len = cfg["seq_length"]
+        self.comm = PipelineComm(ps, cfg["hidden_size"], self.seq_len, self.stage.input_spec, self.stage.output_spec,
+                                 args.params_dtype, self.device) if ps.num_stages > 1 else None
+        self.data_provider = data_provider
+        self.clock = TrainingClock(total_gbs=args.total_gbs)
+        self.iteration = 0
+        self._setup_grad_sync()
+        self._setup_optimizer()
+        self.loss_acc = torch.zeros(2, dtype=torch.float32, device=self.device)
+        self.last_stats: Dict[str, object] = {}
+
+    # ------------------------------------------------------------------ set-up
+    def _make_tp_comm(self) -> TPComm:
+        ps = self.pstate
+        if ps.tp_size == 1:
+            return TPComm()
+        backend = None
+        mode = getattr(self.args, "tp_comm", "auto")
+        if mode in ("auto", "fused") and self.device.type == "cuda":
+            try:
+                from ..parallel.fused_tp import FusedTPBackend
+                backend = FusedTPBackend.create(ps, self.coll, self.device, self.args)
+            except Exception:
+                if mode == "fused":
+                    raise
+                backend = None
+        return TPComm(ps.tp_size, ps.tp_rank, ps.tp_group, backend)
+
+    def _setup_grad_sync(self):
+        args, ps = self.args, self.pstate
+        topo = ps.topology
+        descriptors, bindings = collect_gpt_gradient_metadata(self.stage, ps, args.normalized_config)
+        self.descriptors, self.bindings = descriptors, bindings
+        peer_factory = None
+        backend = getattr(args, "grad_sync_backend", "auto")
+        if backend in ("auto", "peer") and self.device.type == "cuda" and self.coll.enabled:
+            try:
+                from ..parallel.grad_sync.peer_backend import PeerReduceBackend
+                peer_factory = lambda plan, rank: PeerReduceBackend(plan, rank, self.coll, self.device)  # noqa: E731
+            except Exception:
+                if backend == "peer":
+                    raise
+
+        def group_gather(out, obj, handle):
+            self.coll.all_gather_object(out, obj, group=handle)
+
+        self.grad_sync = initialize_gradient_sync(
+            local_descriptors=descriptors, local_runtime_bindings=bindings, topology=topo,
+            model_impl=args.normalized_config["model_impl"], manifest_hash=args.manifest_hash,
+            sync_mode=args.grad_sync_mode, bucket_cap_bytes=args.grad_sync_bucket_size_mb * 1024 * 1024,
+            global_rank=args.rank, all_gather_object=lambda out, obj: self.coll.all_gather_object(out, obj),
+            all_gather_group_object=group_gather, create_group=self.coll.create_group,
+            all_reduce_sum=lambda t, handle: self.coll.all_reduce_sum(t, group=handle),
+            control_device=self.device, runtime_evidence_dir=args.grad_sync_runtime_evidence_dir,
+            peer_backend_factory=peer_factory)
+        if args.grad_sync_dump_plan and args.rank == 0:
+            dump_gradient_sync_plan(self.grad_sync.plan, args.grad_sync_dump_plan)
+        # parameters of one logical fragment start equal on all holders
+        self.grad_sync.synchronize_parameters(lambda t, src, handle: self.coll.broadcast(t, src, group=handle))
+        groups = {g.process_group_id: g for g in self.grad_sync.plan.process_groups}
+        self._needs_reduction = any(len(groups[b.process_group_id].ranks) > 1 for b in self.grad_sync.executor.buckets)
+
+    def _owned_ranges(self):
+        """(offset, numel) ranges of the flat gradient buffer whose norm this rank is responsible for."""
+        sem = self.grad_sync.optimizer_semantics
+        base = self.stage.grad_buf.data_ptr()
+        esize = self.stage.grad_buf.element_size()
+        ranges = []
+        for v in sem.owned_gradient_views():
+            if v.is_contiguous():
+                ranges.append(((v.data_ptr() - base) // esize, v.numel()))
+            else:
+                # a column slice of a row-parallel weight: one range per row
+                flat = v.reshape(-1, v.shape[-1]) if v.dim() > 2 else v
+                for r in range(flat.shape[0]):
+                    row = flat[r]
+                    ranges.append(((row.data_ptr() - base) // esize, row.numel()))
+        return coalesce_ranges(ranges)
+
+    def _setup_optimizer(self):
+        a = self.args
+        if a.fp16:
+            if a.loss_scale:
+                self.scaler = ConstantGradScaler(a.loss_scale, self.device)
+            else:
+                self.scaler = DynamicGradScaler(a.initial_loss_scale, a.min_loss_scale, 2.0, 0.5,
+                                                int(a.loss_scale_window), a.hysteresis, self.device)
+        else:
+            self.scaler = None
+        world_ar = (lambda t: self.coll.all_reduce_sum(t)) if self.coll.enabled else None
+        self.optimizer = FlatMixedPrecisionAdam(
+            self.stage, lr=a.lr, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_eps, weight_decay=a.weight_decay,
+            clip_grad=a.clip_grad, grad_scaler=self.scaler, owned_ranges=self._owned_ranges(),
+            world_all_reduce=world_ar)
+        decay_samples = a.lr_decay_iters * a.total_gbs
+        self.lr_scheduler = AnnealingLR(self.optimizer, a.lr, a.min_lr, a.lr_warmup_samples, decay_samples,
+                                        a.lr_decay_style, a.use_checkpoint_lr_scheduler, a.override_lr_scheduler)
+
+    # ------------------------------------------------------------------ data
+    def _sample_ids(self, mb_index: int):
+        a, ps = self.args, self.pstate
+        return local_sample_slots(ps.pipeline_id, mb_index, ps.dp_size, ps.dp_rank, a.mbs_seq,
+                                  a.pipeline_sample_offsets, self.clock.global_data_cursor)
+
+    def get_batch(self, mb_index: int):
+        ids = self._sample_ids(mb_index)
+        seq = self.args.mbs_seq[self.pstate.pipeline_id][mb_index][1]
+        if self.data_provider is not None:
+            return self.data_provider(ids, seq, self.device)
+        tokens, mask, _pos, _attn, labels = synthetic_gpt_batch(ids, seq, self.args.vocab_size, self.device,
+                                                                with_labels=True)
+        if self.model_cfg.zero_labels:
+            labels = torch.zeros_like(labels)
+        return tokens, labels, mask
+
+    # ------------------------------------------------------------------ steps used by the schedules
+    def forward_step(self, mb_index: int, inputs: Optional[Dict[str, torch.Tensor]]):
+        ps = self.pstate
+        seq = self.args.mbs_seq[ps.pipeline_id][mb_index][1]
+        mb = MicroBatch(index=mb_index, batch=ps.local_micro_batch, seq=seq, global_step=self.iteration,
+                        dp_rank=ps.dp_rank)
+        env = dict(inputs) if inputs else {}
+        if ps.is_first_stage or ps.is_last_stage:
+            tokens, labels, mask = self.get_batch(mb_index)
+            if ps.is_first_stage:
+                env["enc_input_ids"] = tokens
+            if ps.is_last_stage:
+                env["labels"] = labels
+                mb.loss_mask = mask.reshape(-1)
+        out = self.stage.forward(mb, env)
+        if ps.is_last_stage:
+            losses = out.pop("output")
+            if ps.tp_rank == 0:   # TP peers hold identical losses; count them once
+                self.loss_acc[0] += torch.dot(losses, mb.loss_mask)
+                self.loss_acc[1] += mb.loss_mask.sum()
+        return out
+
+    def backward_step(self, mb_index: int, grad_outputs: Optional[Dict[str, torch.Tensor]]):
+        ps = self.pstate
+        if ps.is_last_stage:
+            rec = self.stage._contexts[mb_index]["mb"]
+            scale = self.scaler.value() if self.scaler is not None else 1.0
+            grad_outputs = {"output": rec.loss_mask * (scale / self.args.nominal_global_loss_scale)}
+        return self.stage.backward(mb_index, grad_outputs or {})
+
+    # ------------------------------------------------------------------ one iteration
+    def train_step(self, sync: Optional[bool] = None) -> Dict[str, object]:
+        a = self.args
+        if sync is None:
+            sync = not getattr(a, "async_optimizer", False)
+        self.optimizer.zero_grad()
+        self.loss_acc.zero_()
+        n_mb = self.pstate.num_microbatches
+        if self.pstate.num_stages == 1:
+            schedules.forward_backward_no_pipelining(self, n_mb)
+        else:
+            schedules.forward_backward_1f1b(self, n_mb)
+        # global loss weight -> normalisation factor (device scalar)
+        self.coll.all_reduce_sum(self.loss_acc)
+        normalization = a.nominal_global_loss_scale / self.loss_acc[1]
+        if self._needs_reduction:
+            self.grad_sync.execute(1.0)
+        self.optimizer.set_grad_factor(normalization)
+        ok, grad_norm, _ = self.optimizer.step(sync=sync)
+        increment = self.clock.after_attempt(ok)
+        if ok:
+            self.lr_scheduler.step(increment)
+        self.iteration += 1
+        stats = {"iteration": self.iteration, "update_successful": ok, "grad_norm": grad_norm,
+                 "loss_scale": self.scaler.value() if self.scaler is not None else 1.0, "lr": self.optimizer.lr,
+                 "loss_acc": self.loss_acc}
+        self.last_stats = stats
+        return stats
+
+    def reduced_loss(self) -> float:
+        """Mean masked LM loss of the last iteration (synchronises)."""
+        s, w = self.loss_acc.tolist()
+        return s / w if w > 0 else float("nan")

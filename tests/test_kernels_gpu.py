@@ -228,22 +228,22 @@ def test_adam_and_norm():
     m = torch.zeros(n, device=DEV)
     v = torch.zeros(n, device=DEV)
     ctrl = torch.zeros(2, device=DEV)
-    native.lib().grad_norm_sq(g, 1 / 64.0, ctrl)
-    assert abs(ctrl[0].item() - (g / 64).pow(2).sum().item()) / ctrl[0].item() < 1e-4
+    native.lib().grad_norm_sq(g, 1.0, ctrl)
+    assert abs(ctrl[0].item() - g.pow(2).sum().item()) / ctrl[0].item() < 1e-4
     ref_p = master.clone().requires_grad_(True)
     opt = torch.optim.AdamW([ref_p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
-    clip = min(1.0, 1.0 / (ctrl[0].sqrt().item() + 1e-6))
+    clip = min(1.0, 1.0 / (ctrl[0].sqrt().item() / 64 + 1e-6))
     for step in (1, 2):
         ref_p.grad = (g / 64) * clip
         opt.step()
         native.lib().fused_adam(p16, master, g, m, v, ctrl, 1e-3, 0.9, 0.95, 1e-8, 0.01, step,
-                                1 / 64.0, 1.0, True)
+                                1 / 64.0, 1.0, True, False)
     assert _rel_err(master, ref_p.detach()) < 1e-5
     assert _rel_err(p16, ref_p.detach()) < 1e-2
     # overflow flag skips the update
     ctrl[1] = 1.0
     before = master.clone()
-    native.lib().fused_adam(p16, master, g, m, v, ctrl, 1e-3, 0.9, 0.95, 1e-8, 0.01, 3, 1 / 64.0, 1.0, True)
+    native.lib().fused_adam(p16, master, g, m, v, ctrl, 1e-3, 0.9, 0.95, 1e-8, 0.01, 3, 1 / 64.0, 1.0, True, False)
     assert torch.equal(before, master)
 
 
