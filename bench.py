@@ -1,0 +1,248 @@
+"""Headline benchmark: GPT training throughput (tokens/s, whole job) on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 4 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 4 --warmup 3
+    python bench.py --impl reference --gpus 1 ...      (the unmodified reference, if installed)
+
+Model and layout follow the GPT-1.3B fp16 training config (24 layers, hidden 2048, 16 heads,
+seq 2048, vocab 50257, micro-batch 4, block-wise gradient sync with 32 MiB buckets):
+    8 GPUs: PP2 x TP2 x DP2, global batch 512
+    4 GPUs: TP2 x DP2, global batch 256      2 GPUs: TP2, global batch 128      1 GPU: global batch 64
+so the work per GPU is constant (weak scaling). Data is synthetic (closed-form token ids), weights
+are random-init.
+
+Two numbers are measured, both with CUDA events around exactly K steps, bracketed by a barrier and
+a device synchronize, max over ranks:
+  value : steps whose batches are generated on the device (kernel-side throughput);
+  e2e   : the same steps through the public `TrainEngine.train_step()` API with every step's
+          token ids / labels / loss mask built on the host, copied from pinned memory, and the
+          step's loss read back to the host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+MODEL = dict(model_size="1_3B", num_layers=24, hidden_size=2048, num_attention_heads=16, seq_length=2048,
+             max_position_embeddings=2048)
+VOCAB = 50257
+MICRO_BATCH = 4
+SAMPLES_PER_GPU = 64
+LAYOUTS = {1: (1, 1, 1), 2: (1, 2, 1), 4: (1, 2, 2), 8: (2, 2, 2)}  # N -> (pp, tp, dp)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_config(n_gpus: int):
+    from eth_b200.contract.config import uniform_config
+    pp, tp, dp = LAYOUTS[n_gpus]
+    gbs = SAMPLES_PER_GPU * n_gpus
+    return uniform_config(MODEL, pp=pp, tp=tp, dp=dp, gbs=gbs, mbs=MICRO_BATCH), (pp, tp, dp), gbs
+
+
+def host_batch_provider(vocab: int):
+    """Builds each micro-batch on the host (numpy), stages it in pinned memory and copies it to the
+    device. Returns (provider, byte counter)."""
+    import numpy as np
+    import torch
+    counter = {"h2d": 0}
+    ring, events, cursor = {}, {}, {"i": 0}
+    RING = 4
+
+    def provider(sample_ids, seq, device):
+        ids = np.asarray(sample_ids, dtype=np.int64)[:, None]
+        pos = np.arange(seq, dtype=np.int64)[None, :]
+        tokens = (ids * 1103515245 + pos * 12345) % vocab
+        labels = (ids * 1103515245 + (pos + 1) * 12345) % vocab
+        mask = ((ids + pos) % 4 != 0).astype(np.float32)
+        slot = (len(sample_ids), seq, cursor["i"] % RING)
+        cursor["i"] += 1
+        if slot not in ring:
+            shape = slot[:2]
+            ring[slot] = (torch.empty(shape, dtype=torch.long).pin_memory(),
+                          torch.empty(shape, dtype=torch.long).pin_memory(),
+                          torch.empty(shape, dtype=torch.float32).pin_memory())
+        else:
+            events[slot].synchronize()   # the copies that last used this pinned slot have finished
+        pt, pl, pm = ring[slot]
+        pt.copy_(torch.from_numpy(tokens))
+        pl.copy_(torch.from_numpy(labels))
+        pm.copy_(torch.from_numpy(mask))
+        out = (pt.to(device, non_blocking=True), pl.to(device, non_blocking=True), pm.to(device, non_blocking=True))
+        ev = torch.cuda.Event()
+        ev.record()
+        events[slot] = ev
+        counter["h2d"] += pt.numel() * 8 + pl.numel() * 8 + pm.numel() * 4
+        return out
+
+    return provider, counter
+
+
+def run_ours(opts):
+    import torch
+    import torch.distributed as dist
+    from eth_b200.ops import native
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != opts.gpus:
+        raise SystemExit(f"--gpus {opts.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    config, (pp, tp, dp), gbs = build_config(opts.gpus)
+    argv = ["--fp16", "--loss-scale", "4096", "--hidden-dropout", "0.1", "--grad-sync-mode", "block",
+            "--grad-sync-bucket-size-mb", "32", "--train-iters", str(opts.steps + opts.warmup),
+            "--vocab-size", str(VOCAB)]
+    if opts.bf16:
+        argv = ["--bf16"] + argv[3:]
+    args = parse_args(argv, config=config, rank=rank, world_size=world, local_rank=local_rank)
+    engine = TrainEngine(args)
+
+    def barrier_sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(k, e2e):
+        losses = []
+        barrier_sync()
+        l0 = native.launch_count()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(k):
+            engine.train_step()
+            if e2e:
+                losses.append(engine.reduced_loss())   # device -> host read of the step's result
+        e.record()
+        barrier_sync()
+        ms = s.elapsed_time(e)
+        t = torch.tensor([ms], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), native.launch_count() - l0, losses
+
+    for _ in range(opts.warmup):
+        engine.train_step()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms, launches, _ = timed(opts.steps, e2e=False)
+    clocks = sampler.stop() if sampler else None
+    tokens = gbs * MODEL["seq_length"] * opts.steps
+    value = tokens / (ms / 1e3)
+
+    # end-to-end arm: host-built batches from pinned memory + loss read-back every step
+    provider, counter = host_batch_provider(VOCAB)
+    engine.data_provider = provider
+    engine.train_step()
+    counter["h2d"] = 0
+    ms_e2e, _, losses = timed(opts.steps, e2e=True)
+    e2e_value = tokens / (ms_e2e / 1e3)
+    native.check_status()
+    if rank == 0:
+        out = {
+            "metric": "GPT training throughput (tokens/s, device-timed, max over ranks)",
+            "value": value, "unit": "tokens/s", "n_gpus": opts.gpus, "steps": opts.steps, "warmup": opts.warmup,
+            "ms_per_step": ms / opts.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if opts.bf16 else "fp16", "data": "synthetic token ids, random-init weights",
+            "impl": "eth_b200",
+            "config": {"model": "GPT-1.3B (24 layers, hidden 2048, 16 heads)", "global_batch": gbs,
+                       "seq_len": MODEL["seq_length"], "micro_batch": MICRO_BATCH,
+                       "parallelism": f"pp{pp}tp{tp}dp{dp}", "grad_sync": "block, 32 MiB buckets",
+                       "l2": "inputs larger than L2 (each step streams several GB of weights and activations)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / opts.steps,
+                    "h2d_bytes_per_step": counter["h2d"] // opts.steps, "d2h_bytes_per_step": 8,
+                    "final_loss": losses[-1] if losses else None},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(opts):
+    from baseline.reference_arm import run as run_ref
+    run_ref(opts, MODEL, LAYOUTS, SAMPLES_PER_GPU, MICRO_BATCH, VOCAB)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bf16", action="store_true", help="bf16 instead of the config's fp16")
+    opts = ap.parse_args()
+    if opts.gpus not in LAYOUTS:
+        raise SystemExit(f"--gpus must be one of {sorted(LAYOUTS)}")
+    if opts.impl == "reference":
+        run_reference(opts)
+    else:
+        run_ours(opts)
+
+
+if __name__ == "__main__":
+    main()
