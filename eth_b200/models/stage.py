@@ -63,6 +63,7 @@ class GPTStage:
             self._mark_fusions()
         self._segments = self._plan_segments()
         self._contexts: Dict[int, dict] = {}
+        self.op_events = None   # set to a list to record (op name, phase, start event, end event)
         prev = self.descriptors[op_begin - 1]["name"] if op_begin > 0 else None
         self.input_spec = LIVE_AFTER[prev] if prev else ()
         self.output_spec = LIVE_AFTER[self.descriptors[op_end - 1]["name"]]
@@ -147,6 +148,25 @@ class GPTStage:
         return segs
 
     # ------------------------------------------------------------------ execution
+    def _run(self, op, phase, fn, *a):
+        """Run one op step; when `op_events` is a list, bracket it with CUDA events."""
+        if self.op_events is None:
+            return fn(*a)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        out = fn(*a)
+        e.record()
+        self.op_events.append((op.name, phase, s, e))
+        return out
+
+    def op_time_table(self):
+        """{(op name, phase): total ms} from the recorded events (synchronises)."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, phase, s, e in self.op_events or []:
+            out[(name, phase)] = out.get((name, phase), 0.0) + s.elapsed_time(e)
+        return out
+
     def forward(self, mb: MicroBatch, inputs: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         env = dict(inputs)
         ctxs: Dict[int, dict] = {}
@@ -159,12 +179,12 @@ class GPTStage:
                 mb.ctxs = scratch
                 for op in self.ops[i:j]:
                     scratch[op.op_index] = {}
-                    op.fwd(env, scratch[op.op_index], mb)
+                    self._run(op, "fwd", op.fwd, env, scratch[op.op_index], mb)
                 mb.ctxs = ctxs
             else:
                 for op in self.ops[i:j]:
                     ctxs[op.op_index] = {}
-                    op.fwd(env, ctxs[op.op_index], mb)
+                    self._run(op, "fwd", op.fwd, env, ctxs[op.op_index], mb)
         self._contexts[mb.index] = {"ctxs": ctxs, "envs": saved_envs, "mb": mb}
         keep = {name for name, *_ in self.output_spec} | ({"output"} if self.is_last else set())
         return {k: v for k, v in env.items() if k in keep}
@@ -179,9 +199,9 @@ class GPTStage:
                 env = saved_envs.pop(i)
                 for op in self.ops[i:j]:
                     ctxs[op.op_index] = {}
-                    op.fwd(env, ctxs[op.op_index], mb)
+                    self._run(op, "refwd", op.fwd, env, ctxs[op.op_index], mb)
             for op in reversed(self.ops[i:j]):
-                op.bwd(genv, ctxs.pop(op.op_index), mb)
+                self._run(op, "bwd", op.bwd, genv, ctxs.pop(op.op_index), mb)
         keep = {name for name, *_ in self.input_spec}
         return {k: v for k, v in genv.items() if k in keep and isinstance(v, torch.Tensor)}
 

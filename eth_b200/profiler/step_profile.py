@@ -1,0 +1,73 @@
+"""Per-op time table of one training step (CUDA events around every op's forward and backward).
+
+    python -m eth_b200.profiler.step_profile --size 1_3B --layers 24 --mbs 4 --microbatches 2 [--bf16]
+
+Prints one JSON line per (op, phase) with its share of the step, then host-side totals: wall time of
+the step, device time between first and last event, and native launch count. The gap between the
+sum of op times and the device time of the step is launch/host overhead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import time
+
+import torch
+
+
+def main(argv=None):
+    from eth_b200.contract.config import GPT_SIZES, make_config, make_pipe, manifest_size
+    from eth_b200.ops import native
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--size", default="1_3B")
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--heads", type=int, default=None)
+    ap.add_argument("--mbs", type=int, default=4)
+    ap.add_argument("--microbatches", type=int, default=2)
+    ap.add_argument("--bf16", action="store_true")
+    ap.add_argument("--steps", type=int, default=1)
+    o = ap.parse_args(argv)
+    m = dict(GPT_SIZES[o.size])
+    if o.layers:
+        m["num_layers"] = o.layers
+    if o.heads:
+        m["num_attention_heads"] = o.heads
+    cfg = make_config([make_pipe([manifest_size(m["num_layers"])], [1], [1], gbs=o.mbs * o.microbatches, mbs=o.mbs)],
+                      num_layers=m["num_layers"], hidden_size=m["hidden_size"],
+                      num_attention_heads=m["num_attention_heads"], seq_length=m["seq_length"])
+    argv2 = ["--bf16"] if o.bf16 else ["--fp16", "--loss-scale", "4096"]
+    args = parse_args(argv2 + ["--hidden-dropout", "0.1"], config=cfg, rank=0, world_size=1)
+    eng = TrainEngine(args)
+    for _ in range(2):
+        eng.train_step()
+    torch.cuda.synchronize()
+    # un-instrumented step
+    l0 = native.launch_count()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    s.record()
+    for _ in range(o.steps):
+        eng.train_step(sync=False)
+    e.record()
+    host_ms = (time.perf_counter() - t0) * 1e3
+    torch.cuda.synchronize()
+    dev_ms = s.elapsed_time(e) / o.steps
+    launches = (native.launch_count() - l0) // o.steps
+    # instrumented step
+    eng.stage.op_events = []
+    eng.train_step(sync=False)
+    table = eng.stage.op_time_table()
+    eng.stage.op_events = None
+    total = sum(table.values())
+    for (name, phase), ms in sorted(table.items(), key=lambda kv: -kv[1]):
+        print(json.dumps({"op": name, "phase": phase, "ms": round(ms, 3), "share": round(ms / total, 4)}))
+    print(json.dumps({"summary": True, "step_device_ms": dev_ms, "host_enqueue_ms": host_ms / o.steps,
+                      "sum_op_ms": total, "native_launches_per_step": launches,
+                      "tokens_per_s": o.mbs * o.microbatches * m["seq_length"] / dev_ms * 1e3}))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,57 @@
+"""Spawn N CPU ranks over Gloo on localhost, run `fn(rank, world, *args)` in each, collect results."""
+import os
+import socket
+import tempfile
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, fn, args, outdir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        result = fn(rank, world, *args)
+        torch.save({"ok": True, "result": result}, os.path.join(outdir, f"rank{rank}.pt"))
+    except Exception:
+        torch.save({"ok": False, "error": traceback.format_exc()}, os.path.join(outdir, f"rank{rank}.pt"))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run_ranks(world, fn, *args, timeout=240):
+    port = _free_port()
+    with tempfile.TemporaryDirectory() as outdir:
+        ctx = mp.get_context("spawn")
+        procs = [ctx.Process(target=_worker, args=(r, world, port, fn, args, outdir)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout)
+        hung = [p for p in procs if p.is_alive()]
+        for p in hung:
+            p.terminate()
+        if hung:
+            raise RuntimeError(f"{len(hung)} rank(s) did not finish within {timeout}s (deadlock watchdog)")
+        out = []
+        for r in range(world):
+            path = os.path.join(outdir, f"rank{r}.pt")
+            if not os.path.exists(path):
+                raise RuntimeError(f"rank {r} produced no result (exit code {procs[r].exitcode})")
+            rec = torch.load(path, weights_only=False)
+            if not rec["ok"]:
+                raise RuntimeError(f"rank {r} failed:\n{rec['error']}")
+            out.append(rec["result"])
+        return out

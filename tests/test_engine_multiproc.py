@@ -1,0 +1,101 @@
+"""Topology independence: after N optimizer steps every parallel layout holds the same logical
+parameters as a single-rank run over the same global batch (the evidence protocol of the
+reference, tools/validation/compare_numerical_evidence.py, run here on CPU ranks over Gloo)."""
+import pytest
+import torch
+
+from eth_b200.contract.config import make_config, make_pipe, manifest_size
+from tests.helpers.multiproc import run_ranks
+
+LAYERS, HIDDEN, HEADS, SEQ, VOCAB = 2, 32, 4, 16, 96
+N_OPS = manifest_size(LAYERS)
+
+
+def _config(pipes):
+    return make_config(pipes, num_layers=LAYERS, hidden_size=HIDDEN, num_attention_heads=HEADS, seq_length=SEQ)
+
+
+def _train(rank, world, config, steps, mode):
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+    argv = ["--hidden-dropout", "0.0", "--device", "cpu", "--vocab-size", str(VOCAB),
+            "--make-vocab-size-divisible-by", "8", "--lr", "1e-2", "--lr-warmup-fraction", "0.0",
+            "--lr-decay-style", "constant", "--grad-sync-mode", mode, "--grad-sync-bucket-size-mb", "1",
+            "--distributed-backend", "gloo"]
+    args = parse_args(argv, config=config, rank=rank, world_size=world)
+    # identical vocabulary padding in every layout so logical shapes agree
+    eng = TrainEngine(args, device="cpu")
+    losses, norms = [], []
+    for _ in range(steps):
+        st = eng.train_step()
+        losses.append(eng.reduced_loss())
+        norms.append(st["grad_norm"])
+    shards = []
+    for e in eng.stage.unique_entries():
+        shards.append((e.spec.logical_id, e.spec.full_shape, e.spec.partition_dim, eng.pstate.tp_size,
+                       eng.pstate.tp_rank, eng.pstate.pipeline_id, eng.pstate.dp_rank, e.param.detach().clone()))
+    return {"losses": losses, "norms": norms, "shards": shards,
+            "collectives": eng.grad_sync.executor.collectives_issued}
+
+
+def _logical(results, pipeline=0, dp=0):
+    """Reassemble full logical tensors from one (pipeline, dp) replica."""
+    parts = {}
+    for res in results:
+        for lid, full, pdim, tp, tpr, pid, dpr, t in res["shards"]:
+            if pid == pipeline and dpr == dp:
+                parts.setdefault(lid, {})[tpr] = (pdim, tp, t)
+    out = {}
+    for lid, by in parts.items():
+        pdim, tp, _ = next(iter(by.values()))
+        if pdim < 0 or tp == 1:
+            out[lid] = by[min(by)][2]
+        else:
+            out[lid] = torch.cat([by[r][2] for r in range(tp)], pdim)
+    return out
+
+
+LAYOUTS = {
+    "tp2": (2, [make_pipe([N_OPS], [2], [1], gbs=8, mbs=4)]),
+    "dp2": (2, [make_pipe([N_OPS], [1], [2], gbs=8, mbs=4)]),
+    "pp2": (2, [make_pipe([11, N_OPS - 11], [1, 1], [1, 1], gbs=8, mbs=4)]),
+    "pp2-midlayer-cut": (2, [make_pipe([6, N_OPS - 6], [1, 1], [1, 1], gbs=8, mbs=4)]),
+    "pp2-tp2-to-dp2": (4, [make_pipe([11, N_OPS - 11], [2, 1], [1, 2], gbs=8, mbs=4)]),
+    "two-pipelines-hetero": (3, [make_pipe([N_OPS], [2], [1], gbs=4, mbs=4), make_pipe([N_OPS], [1], [1], gbs=4, mbs=2)]),
+    "pp3-1f1b": (3, [make_pipe([11, 10, N_OPS - 21], [1, 1, 1], [1, 1, 1], gbs=8, mbs=2)]),
+}
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    cfg = _config([make_pipe([N_OPS], [1], [1], gbs=8, mbs=4)])
+    return run_ranks(1, _train, cfg, 2, "block")
+
+
+@pytest.mark.parametrize("name", sorted(LAYOUTS))
+def test_layout_matches_single_rank(name, oracle):
+    world, pipes = LAYOUTS[name]
+    results = run_ranks(world, _train, _config(pipes), 2, "block")
+    ref = _logical(oracle)
+    merged = {}
+    for res in results:
+        for lid, full, pdim, tp, tpr, pid, dpr, t in res["shards"]:
+            merged.setdefault((lid, pid, dpr), {})[tpr] = (pdim, tp, t)
+    for (lid, pid, dpr), by in merged.items():
+        pdim, tp, _ = next(iter(by.values()))
+        full = by[min(by)][2] if (pdim < 0 or tp == 1) else torch.cat([by[r][2] for r in range(tp)], pdim)
+        err = (full - ref[lid]).norm() / (ref[lid].norm() + 1e-12)
+        assert err < 2e-4, (name, lid, pid, dpr, float(err))
+    for a, b in zip(results[-1]["losses"], oracle[0]["losses"]):
+        assert abs(a - b) < 1e-4
+    for a, b in zip(results[0]["norms"], oracle[0]["norms"]):
+        assert abs(a - b) / b < 1e-3
+
+
+def test_block_mode_issues_fewer_collectives_than_tensor_mode():
+    world, pipes = LAYOUTS["dp2"]
+    block = run_ranks(world, _train, _config(pipes), 1, "block")
+    tensor = run_ranks(world, _train, _config(pipes), 1, "tensor")
+    assert block[0]["collectives"] < tensor[0]["collectives"]
+    for (a, b) in zip(block[0]["shards"], tensor[0]["shards"]):
+        assert torch.allclose(a[-1], b[-1], atol=1e-6)
