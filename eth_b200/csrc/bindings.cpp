@@ -73,6 +73,50 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& d, con
   check(ethb::gemm_tcgen05(g, cur_stream()), "gemm_tcgen05");
 }
 
+// GEMM fused with the tensor-parallel all-reduce. The result lands in every rank's `out` buffer
+// (`out_ptrs[rank]` is this rank's, M x N with row stride ldd).
+void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, const OptTensor& bias,
+                    const OptTensor& aux, double alpha, const OptTensor& status,
+                    const std::vector<int64_t>& stage_ptrs, const std::vector<int64_t>& out_ptrs,
+                    const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, int64_t max_tiles,
+                    int64_t stage_elems, int64_t ldd) {
+  need_cuda(a, "a"); need_cuda(b, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1);
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a/b dtype mismatch");
+  c10::cuda::CUDAGuard guard(a.device());
+  ethb::GemmArgs g{};
+  g.M = static_cast<int>(a_mn ? a.size(1) : a.size(0));
+  g.K = static_cast<int>(a_mn ? a.size(0) : a.size(1));
+  g.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == g.K, "reduction dims differ");
+  g.A = a.data_ptr(); g.lda = a.stride(0); g.a_mn = a_mn;
+  g.B = b.data_ptr(); g.ldb = b.stride(0); g.b_mn = b_mn;
+  g.ab_dtype = dtype_code(a);
+  g.d_dtype = g.ab_dtype;
+  const size_t w = stage_ptrs.size();
+  TORCH_CHECK(w >= 2 && w <= ethb::kGemmMaxPeers && out_ptrs.size() == w && flag_ptrs.size() == w);
+  g.D = reinterpret_cast<void*>(out_ptrs[rank]);
+  g.ldd = ldd;
+  g.bias = optptr(bias);
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == a.scalar_type() && bias->numel() == g.N);
+  g.aux = optptr(aux);
+  g.ldaux = aux.has_value() ? aux->stride(0) : 0;
+  g.aux_mode = aux.has_value() ? 1 : 0;
+  g.alpha = static_cast<float>(alpha);
+  g.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  g.comm.world = static_cast<int>(w);
+  g.comm.rank = static_cast<int>(rank);
+  g.comm.epoch = static_cast<int>(epoch);
+  g.comm.max_tiles = static_cast<int>(max_tiles);
+  g.comm.stage_elems = stage_elems;
+  for (size_t i = 0; i < w; ++i) {
+    g.comm.stage[i] = reinterpret_cast<void*>(stage_ptrs[i]);
+    g.comm.out[i] = reinterpret_cast<void*>(out_ptrs[i]);
+    g.comm.flags[i] = reinterpret_cast<int*>(flag_ptrs[i]);
+  }
+  check(ethb::gemm_tcgen05(g, cur_stream()), "gemm_allreduce");
+}
+
 void layernorm_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Tensor& y,
                    Tensor& mean, Tensor& rstd, double eps) {
   need_cuda(x, "x");
@@ -378,6 +422,7 @@ void peer_allreduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_allreduce", &gemm_allreduce);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("ln_bwd_parts", &ln_bwd_parts);
   m.def("layernorm_bwd", &layernorm_bwd);

@@ -81,6 +81,118 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_flag_ge(const int* p, int target, int* status) {
+  if (ld_acquire_sys(p) >= target) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_sys(p) < target) {
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > ETHB_WAIT_NS) {
+      if (status) atomicCAS(status, 0, kStatusTimeoutPeerFlag);
+      return false;
+    }
+  }
+  return true;
+}
+
+// Sum the `world` staged partials of one owned tile, add bias / residual, and write the result
+// into every rank's output. Called by the 128 epilogue threads (thread == tile row).
+template <int BN>
+__device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, int tiles_m, int tiles_n,
+                                                 int slots, int row_in_tile, int tid_e) {
+  const GemmComm& cm = p.comm;
+  int tm, tn;
+  tile_coords(tile, tiles_m, tiles_n, tm, tn);
+  const int slot = tile / cm.world;
+  const int row = tm * BM + row_in_tile;
+  const bool row_ok = row < p.M;
+  const uint16_t* base = reinterpret_cast<const uint16_t*>(cm.stage[cm.rank]) +
+                         static_cast<int64_t>(slot) * (BM * BN) + row_in_tile * BN;
+  const int64_t src_stride = static_cast<int64_t>(slots) * (BM * BN);
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    const int col0 = tn * BN + c * 32;
+    if (col0 >= p.N) break;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    for (int s = 0; s < cm.world; ++s) {
+      const uint4* sp = reinterpret_cast<const uint4*>(base + s * src_stride + c * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 u = __ldcg(sp + q);   // L2 only: peers write these lines through NVLink
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack2(w[e], p.ab_dtype);
+          v[q * 8 + e * 2] += f.x;
+          v[q * 8 + e * 2 + 1] += f.y;
+        }
+      }
+    }
+    if (p.bias != nullptr) {
+      const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (col0 + q * 8 < p.N) {
+          const uint4 b = __ldg(bp + q);
+          const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack2(bw[e], p.ab_dtype);
+            v[q * 8 + e * 2] += f.x;
+            v[q * 8 + e * 2 + 1] += f.y;
+          }
+        }
+      }
+    }
+    if (row_ok) {
+      if (p.aux_mode == kAuxAdd) {
+        const uint4* ap = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const uint16_t*>(p.aux) + static_cast<int64_t>(row) * p.ldaux + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (col0 + q * 8 < p.N) {
+            const uint4 a = __ldg(ap + q);
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack2(aw[e], p.ab_dtype);
+              v[q * 8 + e * 2] += f.x;
+              v[q * 8 + e * 2 + 1] += f.y;
+            }
+          }
+        }
+      }
+      uint4 o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        o[q].x = pack2(v[q * 8 + 0], v[q * 8 + 1], p.ab_dtype);
+        o[q].y = pack2(v[q * 8 + 2], v[q * 8 + 3], p.ab_dtype);
+        o[q].z = pack2(v[q * 8 + 4], v[q * 8 + 5], p.ab_dtype);
+        o[q].w = pack2(v[q * 8 + 6], v[q * 8 + 7], p.ab_dtype);
+      }
+      for (int dst = 0; dst < cm.world; ++dst) {
+        uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[dst]) +
+                                             static_cast<int64_t>(row) * p.ldd + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          if (col0 + q * 8 < p.N) dp[q] = o[q];
+      }
+    }
+  }
+  __threadfence_system();
+  epi_bar_sync();
+  if (tid_e < cm.world && tid_e != cm.rank)
+    st_release_sys(cm.flags[tid_e] + cm.max_tiles * kGemmMaxPeers + tile, cm.epoch);
+}
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -197,6 +309,89 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
         tc_commit(&bars->tmem_full[acc]);
       }
+    }
+  } else if (p.comm.world > 1) {
+    // ---------------------------------------------- epilogue fused with the TP all-reduce
+    const GemmComm& cm = p.comm;
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int tid_e = threadIdx.x - 64;
+    const int W = cm.world, me = cm.rank;
+    const int slots = (num_tiles + W - 1) / W;
+    int* my_flags = cm.flags[me];
+    __shared__ int s_ready;
+    const int n_my = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    int red = 0;   // next entry of this CTA's tile list to consider for reduction
+    bool ok = true;
+    for (int it = 0; it < n_my && ok; ++it) {
+      const int tile = blockIdx.x + it * gridDim.x;
+      const int owner = tile % W, slot = tile / W;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // phase A: this rank's partial tile -> the owner's staging area (a peer store unless owned)
+      uint16_t* dst = reinterpret_cast<uint16_t*>(cm.stage[owner]) +
+                      (static_cast<int64_t>(me) * slots + slot) * (BM * BN) + row_in_tile * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          o.x = pack2(__uint_as_float(r[q * 8 + 0]) * p.alpha, __uint_as_float(r[q * 8 + 1]) * p.alpha, p.ab_dtype);
+          o.y = pack2(__uint_as_float(r[q * 8 + 2]) * p.alpha, __uint_as_float(r[q * 8 + 3]) * p.alpha, p.ab_dtype);
+          o.z = pack2(__uint_as_float(r[q * 8 + 4]) * p.alpha, __uint_as_float(r[q * 8 + 5]) * p.alpha, p.ab_dtype);
+          o.w = pack2(__uint_as_float(r[q * 8 + 6]) * p.alpha, __uint_as_float(r[q * 8 + 7]) * p.alpha, p.ab_dtype);
+          d4[q] = o;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->tmem_empty[acc]);
+      __threadfence_system();
+      epi_bar_sync();
+      if (tid_e == 0 && owner != me) st_release_sys(cm.flags[owner] + tile * kGemmMaxPeers + me, cm.epoch);
+      // phase B (opportunistic): reduce owned tiles whose peer partials have all arrived
+      while (red <= it) {
+        const int t2 = blockIdx.x + red * gridDim.x;
+        if (t2 % W != me) { ++red; continue; }
+        if (tid_e == 0) {
+          int ready = 1;
+          for (int s = 0; s < W; ++s)
+            if (s != me && ld_acquire_sys(my_flags + t2 * kGemmMaxPeers + s) < cm.epoch) ready = 0;
+          s_ready = ready;
+        }
+        epi_bar_sync();
+        const int ready = s_ready;
+        epi_bar_sync();
+        if (!ready) break;
+        comm_reduce_tile<BN>(p, t2, tiles_m, tiles_n, slots, row_in_tile, tid_e);
+        ++red;
+      }
+    }
+    // drain: remaining owned tiles, now with (bounded) blocking waits
+    while (red < n_my) {
+      const int t2 = blockIdx.x + red * gridDim.x;
+      if (t2 % W == me) {
+        if (tid_e < W && tid_e != me)
+          wait_flag_ge(my_flags + t2 * kGemmMaxPeers + tid_e, cm.epoch, p.status);
+        epi_bar_sync();
+        comm_reduce_tile<BN>(p, t2, tiles_m, tiles_n, slots, row_in_tile, tid_e);
+      }
+      ++red;
+    }
+    // the tiles owned by peers must have landed in this rank's output before the kernel ends
+    for (int i = tid_e; i < n_my; i += kEpiThreads) {
+      const int t = blockIdx.x + i * gridDim.x;
+      if (t % W != me) wait_flag_ge(my_flags + cm.max_tiles * kGemmMaxPeers + t, cm.epoch, p.status);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -416,6 +611,12 @@ cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
     attr_set = true;
   }
   const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  if (a.comm.world > 1) {
+    const int64_t slots = (tiles + a.comm.world - 1) / a.comm.world;
+    ETHB_RETURN_IF(tiles > a.comm.max_tiles, cudaErrorInvalidValue, "fused all-reduce: more tiles than flags");
+    ETHB_RETURN_IF(slots * a.comm.world * BM * BN > a.comm.stage_elems, cudaErrorInvalidValue,
+                   "fused all-reduce: staging area too small");
+  }
   int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
   const int grid = tiles < sms ? tiles : sms;
   gemm_tcgen05_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, a);
@@ -430,6 +631,11 @@ cudaError_t gemm_tcgen05(const GemmArgs& a, cudaStream_t stream) {
   if (a.N % 8 != 0 || a.ldd % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a.D) & 15) != 0) return cudaErrorMisalignedAddress;
   if (a.ab_dtype != kF16 && a.ab_dtype != kBF16) return cudaErrorInvalidValue;
+  if (a.comm.world > 1) {
+    ETHB_RETURN_IF(a.comm.world > kGemmMaxPeers, cudaErrorInvalidValue, "fused all-reduce: too many peers");
+    ETHB_RETURN_IF(a.d_dtype != a.ab_dtype || a.accumulate || a.D2 != nullptr || a.aux_mode == kAuxGeluGrad,
+                   cudaErrorInvalidValue, "fused all-reduce: unsupported epilogue");
+  }
   // Pick the tile width that minimises (waves x cost per wave).
   const int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
   const int tm = (a.M + BM - 1) / BM;

@@ -12,6 +12,25 @@ enum GemmAuxMode : int {
   kAuxGeluGrad = 2,  // value *= gelu'(aux[row, col])          (dgrad of GEMM-2 fused with dGeLU)
 };
 
+constexpr int kGemmMaxPeers = 8;
+
+// Tensor-parallel all-reduce fused into the GEMM epilogue (world > 1). Every pointer array holds
+// the addresses of the same symmetric allocation on each rank of the tensor-parallel group:
+//   stage[r] : r's staging area for partial tiles, [source rank][owned slot][128 x BN] 16-bit
+//   out[r]   : r's copy of the reduced result D (row stride GemmArgs::ldd)
+//   flags[r] : r's int32 flags: arrive[tile * kGemmMaxPeers + source] then done[tile] at
+//              offset max_tiles * kGemmMaxPeers
+// Tile T is owned by rank T % world: every rank writes its partial of T into the owner's staging
+// area, the owner sums the partials in fp32, applies bias / residual, and writes the result into
+// every rank's `out`. `epoch` must increase with every call that uses the same flags.
+struct GemmComm {
+  int world, rank, epoch, max_tiles;
+  void* stage[kGemmMaxPeers];
+  void* out[kGemmMaxPeers];
+  int* flags[kGemmMaxPeers];
+  int64_t stage_elems;  // capacity of one rank's staging area in 16-bit elements
+};
+
 struct GemmArgs {
   // problem: D[M,N] = sum_k A(m,k) * B(n,k)
   int M, N, K;
@@ -30,6 +49,7 @@ struct GemmArgs {
   float alpha;
   int* status;                       // device status word (0 == ok)
   int sm_count;                      // CTAs to launch at most (0 = all SMs)
+  GemmComm comm;                     // comm.world <= 1: plain GEMM
 };
 
 // Returns cudaSuccess or the launch/encode error. Never allocates.

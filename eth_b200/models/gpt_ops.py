@@ -90,6 +90,16 @@ class TPComm:
             torch.distributed.all_reduce(t, group=self.group)
         return t
 
+    def linear_all_reduce(self, x, weight, *, b_mn=False):
+        """sum over the TP group of x W^T (b_mn False) or x W (b_mn True): one fused kernel when the
+        peer-memory backend is available, else a GEMM followed by an all-reduce."""
+        if self.size > 1 and self.backend is not None and x.is_cuda:
+            n = weight.shape[1] if b_mn else weight.shape[0]
+            if self.backend.supports(x.shape[0], n):
+                return self.backend.gemm_all_reduce(x, weight, b_mn=b_mn)
+        y = raw.gemm(x, weight, b_mn=b_mn)
+        return self.all_reduce_(y)
+
     def gather_stats(self, stats: torch.Tensor) -> torch.Tensor:
         """[rows, 3] -> [tp, rows, 3] (cross-entropy statistics)."""
         if self.size == 1:
@@ -285,8 +295,7 @@ class ColumnLinearOp(Op):
 
     def bwd(self, genv, ctx, mb):
         dy = _take(genv, self.out_name)
-        dx = raw.linear_dgrad(dy, self.p("weight"))
-        self.tp.all_reduce_(dx)
+        dx = self.tp.linear_all_reduce(dy, self.p("weight"), b_mn=True)
         raw.linear_wgrad(dy, ctx["x"], self.p("weight"), self.p("bias"))
         genv["hidden_states"] = dx
 
@@ -310,9 +319,7 @@ class RowLinearOp(Op):
     def fwd(self, env, ctx, mb):
         x = env["hidden_states"]
         ctx["x"] = x
-        y = raw.linear_fwd(x, self.p("weight"))
-        self.tp.all_reduce_(y)
-        env["hidden_states"] = y
+        env["hidden_states"] = self.tp.linear_all_reduce(x, self.p("weight"))
         env["output_bias"] = self.p("bias")
 
     def bwd(self, genv, ctx, mb):
@@ -416,8 +423,7 @@ class PostProcessOp(Op):
         dloss = _take(genv, "output")
         dlogits = raw.ce_bwd_(ctx["logits"], ctx["labels"], ctx["gmax"], ctx["gsum"], dloss, ctx["vstart"])
         w = self.p("word")
-        dx = raw.linear_dgrad(dlogits, w)
-        self.tp.all_reduce_(dx)
+        dx = self.tp.linear_all_reduce(dlogits, w, b_mn=True)
         raw.linear_wgrad(dlogits, ctx["x"], w)
         ctx.pop("logits")
         genv["hidden_states"] = dx

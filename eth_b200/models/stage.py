@@ -174,7 +174,8 @@ class GPTStage:
         saved_envs: Dict[int, dict] = {}
         for (i, j, recompute) in self._segments:
             if recompute:
-                saved_envs[i] = dict(env)
+                # tensors that live in a short-lived ring slot must be copied to survive until backward
+                saved_envs[i] = {k: (v.clone() if getattr(v, "_ethb_ring", False) else v) for k, v in env.items()}
                 scratch: Dict[int, dict] = {}
                 mb.ctxs = scratch
                 for op in self.ops[i:j]:

@@ -1,0 +1,78 @@
+"""Tensor-parallel linears fused with their all-reduce over NVLink peer memory.
+
+Row-parallel forward (`Y = sum_r X_r W_r^T`) and column-parallel data-gradient
+(`dX = sum_r dY_r W_r`) are each ONE launch of the tcgen05 GEMM whose epilogue pushes partial tiles
+into the owning peer's staging area, reduces owned tiles in fp32 as soon as the peers' partials have
+arrived, and writes the result into every rank's output buffer -- the transfer of tile i overlaps
+the MMAs of tile i+1 (reference: a cuBLAS GEMM followed by an exposed NCCL all-reduce,
+eth/runtime/megatron/mpu/layers.py:459-461, mappings.py:84-97).
+
+The outputs live in a small ring of symmetric buffers (peers write into them directly), so a
+returned tensor is valid until `ring` further fused calls have been issued; the stage program
+consumes every such tensor with the very next kernel.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from .peer_memory import SymmetricBuffer
+
+MAX_TILES = 8192
+RING = 4
+
+
+class FusedTPBackend:
+    def __init__(self, group_ranks, my_rank, group, device, max_tokens: int, hidden: int, dtype):
+        self.group, self.device, self.dtype = group, torch.device(device), dtype
+        self.world = len(group_ranks)
+        self.max_tokens, self.hidden = max_tokens, hidden
+        esize = 2
+        rows = (max_tokens + 127) // 128 * 128
+        cols = (hidden + 255) // 256 * 256
+        self.out_slot_bytes = rows * cols * esize
+        # staging holds `world` partials of each owned tile: about one full output, plus rounding
+        self.stage_elems = rows * cols + self.world * 128 * 256
+        self.stage = SymmetricBuffer(self.stage_elems * esize, group_ranks, my_rank, group, device)
+        self.out = SymmetricBuffer(self.out_slot_bytes * RING, group_ranks, my_rank, group, device)
+        self.flags = SymmetricBuffer(MAX_TILES * 9 * 4, group_ranks, my_rank, group, device)
+        self.rank = self.stage.index
+        self.epoch = 0
+        self.slot = 0
+
+    @classmethod
+    def create(cls, pstate, coll, device, args):
+        cfg = pstate.config
+        max_tokens = pstate.local_micro_batch * cfg["seq_length"]
+        return cls(pstate.tp_group_ranks, pstate.rank, pstate.tp_group, device, max_tokens, cfg["hidden_size"],
+                   args.params_dtype)
+
+    def supports(self, m: int, n: int) -> bool:
+        return m <= self.max_tokens and n <= self.hidden and n % 8 == 0
+
+    def gemm_all_reduce(self, a, b, *, b_mn=False, bias=None, residual=None, alpha=1.0):
+        """sum over the TP group of (a x b^T) (+ bias + residual, added once). Returns a view of a
+        ring slot holding the [M, N] result."""
+        m = a.shape[0]
+        n = b.shape[1] if b_mn else b.shape[0]
+        if not self.supports(m, n):
+            raise ValueError(f"fused all-reduce GEMM: shape {m}x{n} exceeds the symmetric buffers")
+        self.epoch += 1
+        slot = self.slot
+        self.slot = (self.slot + 1) % RING
+        off = slot * self.out_slot_bytes
+        native.lib().gemm_allreduce(a, False, b, b_mn, bias, residual, float(alpha), native.status(a.device),
+                                    self.stage.ptrs, self.out.offset_ptrs(off), self.flags.ptrs, self.rank,
+                                    self.epoch, MAX_TILES, self.stage_elems, n)
+        out = self.out.tensor((m, n), self.dtype, off)
+        out._ethb_ring = True   # short-lived: valid until RING further fused calls
+        return out
+
+    def all_reduce_(self, t):
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def close(self):
+        for b in (self.stage, self.out, self.flags):
+            b.close()

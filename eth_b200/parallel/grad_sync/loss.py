@@ -92,7 +92,13 @@ def synthetic_gpt_batch(sample_ids, sequence_length: int, vocab_size: int, devic
     Returns (tokens, loss_mask, position_ids, attention_mask) -- attention_mask is None because the
     attention kernel applies the causal mask implicitly -- plus labels when `with_labels`
     (the next position's token under the same formula)."""
-    ids = torch.as_tensor(sample_ids, dtype=torch.long, device=device)
+    sample_ids = tuple(sample_ids) if not isinstance(sample_ids, torch.Tensor) else sample_ids
+    if (not isinstance(sample_ids, torch.Tensor) and len(sample_ids) > 0
+            and sample_ids[-1] - sample_ids[0] == len(sample_ids) - 1):
+        # consecutive slots: build the ids on the device (a host->device copy would synchronise)
+        ids = torch.arange(sample_ids[0], sample_ids[0] + len(sample_ids), dtype=torch.long, device=device)
+    else:
+        ids = torch.as_tensor(sample_ids, dtype=torch.long, device=device)
     n = ids.numel()
     if ids.is_cuda:
         from ...ops import native

@@ -17,11 +17,16 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, fn, args, outdir):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+def _worker(rank, world, port, fn, args, outdir, backend="gloo"):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
     torch.set_num_threads(1)
     try:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
         result = fn(rank, world, *args)
         torch.save({"ok": True, "result": result}, os.path.join(outdir, f"rank{rank}.pt"))
     except Exception:
@@ -31,11 +36,11 @@ def _worker(rank, world, port, fn, args, outdir):
             dist.destroy_process_group()
 
 
-def run_ranks(world, fn, *args, timeout=240):
+def run_ranks(world, fn, *args, timeout=240, backend="gloo"):
     port = _free_port()
     with tempfile.TemporaryDirectory() as outdir:
         ctx = mp.get_context("spawn")
-        procs = [ctx.Process(target=_worker, args=(r, world, port, fn, args, outdir)) for r in range(world)]
+        procs = [ctx.Process(target=_worker, args=(r, world, port, fn, args, outdir, backend)) for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:

@@ -1,0 +1,109 @@
+"""Multi-GPU kernels and engine paths (NCCL ranks on 2+ GPUs of one node; skipped with fewer)."""
+import pytest
+import torch
+
+from tests.helpers.multiproc import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(n):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _fused_gemm_ar(rank, world, shapes):
+    import torch.distributed as dist
+    from eth_b200.ops import native
+    from eth_b200.parallel.fused_tp import FusedTPBackend
+    dev = torch.device("cuda", rank)
+    be = FusedTPBackend(tuple(range(world)), rank, None, dev, max_tokens=4096, hidden=2048, dtype=torch.bfloat16)
+    errs = []
+    for (m, n, k, b_mn, reps) in shapes:
+        for rep in range(reps):
+            g = torch.Generator(device=dev).manual_seed(1000 * rank + rep)
+            a = torch.randn(m, k, device=dev, dtype=torch.bfloat16, generator=g)
+            w = torch.randn((k, n) if b_mn else (n, k), device=dev, dtype=torch.bfloat16, generator=g) * 0.05
+            out = be.gemm_all_reduce(a, w, b_mn=b_mn).clone()
+            ref = a.float() @ (w.float() if b_mn else w.float().t())
+            dist.all_reduce(ref)
+            errs.append(((out.float() - ref).norm() / ref.norm()).item())
+    native.check_status()
+    # every rank must hold the same bits
+    chk = out.float().sum().reshape(1).clone()
+    lst = [torch.zeros_like(chk) for _ in range(world)]
+    dist.all_gather(lst, chk)
+    same = all(torch.equal(lst[0], x) for x in lst)
+    be.close()
+    return {"errs": errs, "same": same}
+
+
+def test_fused_gemm_allreduce_two_gpus():
+    _need(2)
+    shapes = [(256, 512, 256, False, 2), (4096, 2048, 1024, False, 3), (1000, 2048, 512, True, 2), (4096, 2048, 4096, True, 2)]
+    res = run_ranks(2, _fused_gemm_ar, shapes, backend="nccl")
+    for r in res:
+        assert max(r["errs"]) < 1e-2, r["errs"]
+        assert r["same"]
+
+
+def _peer_allreduce(rank, world):
+    import torch.distributed as dist
+    from eth_b200.ops import native
+    from eth_b200.parallel.peer_memory import SymmetricBuffer
+    dev = torch.device("cuda", rank)
+    n = 1_000_003
+    buf = SymmetricBuffer(n * 4, tuple(range(world)), rank, None, dev)
+    flags = SymmetricBuffer(64 * 4, tuple(range(world)), rank, None, dev)
+    mine = buf.tensor((n,), torch.float32)
+    out = torch.empty(n, device=dev)
+    acc = torch.zeros(2, device=dev)
+    errs = []
+    for epoch in (1, 2, 3):
+        src = torch.randn(n, device=dev) * (rank + 1)
+        mine.copy_(src)
+        ref = src.clone()
+        dist.all_reduce(ref)
+        ref *= 0.5
+        acc.zero_()
+        native.lib().peer_allreduce(buf.ptrs, flags.ptrs, rank, epoch, n, 0, 0.5, out, acc, 1.0, native.status(dev))
+        errs.append(((out - ref).norm() / ref.norm()).item())
+        errs.append(abs(acc[0].item() - ref.pow(2).sum().item()) / ref.pow(2).sum().item())
+    native.check_status()
+    return errs
+
+
+def test_peer_allreduce_two_gpus():
+    _need(2)
+    for errs in run_ranks(2, _peer_allreduce, backend="nccl"):
+        assert max(errs) < 1e-4, errs
+
+
+def _engine_loss(rank, world, tp):
+    from eth_b200.contract.config import make_config, make_pipe, manifest_size
+    from eth_b200.ops import native
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+    layers = 2
+    cfg = make_config([make_pipe([manifest_size(layers)], [tp], [world // tp], gbs=8, mbs=4)], num_layers=layers,
+                      hidden_size=512, num_attention_heads=4, seq_length=256)
+    args = parse_args(["--bf16", "--hidden-dropout", "0.0", "--vocab-size", "2000", "--lr", "1e-3",
+                       "--lr-warmup-fraction", "0.0", "--make-vocab-size-divisible-by", "64"],
+                      config=cfg, rank=rank, world_size=world)
+    eng = TrainEngine(args)
+    out = []
+    for _ in range(3):
+        st = eng.train_step()
+        out.append((eng.reduced_loss(), st["grad_norm"]))
+    native.check_status()
+    return out
+
+
+def test_engine_tp2_and_dp2_match_single_gpu():
+    _need(2)
+    single = run_ranks(1, _engine_loss, 1, backend="nccl")[0]
+    tp2 = run_ranks(2, _engine_loss, 2, backend="nccl")[0]
+    dp2 = run_ranks(2, _engine_loss, 1, backend="nccl")[0]
+    for (l1, n1), (l2, n2), (l3, n3) in zip(single, tp2, dp2):
+        assert abs(l1 - l2) < 3e-2 and abs(l1 - l3) < 3e-2, (single, tp2, dp2)
+        assert abs(n1 - n2) / n1 < 5e-2 and abs(n1 - n3) / n1 < 5e-2, (single, tp2, dp2)
