@@ -57,7 +57,8 @@ template <int BN> struct Cfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiBytes = 4 * 4096;  // per-epilogue-warp 32 x 128 B transpose buffer (fused all-reduce)
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kEpiBytes;
 };
 
 struct Barriers {
@@ -102,59 +103,71 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int target, int* stat
   return true;
 }
 
+// Staging layout of one 128 x BN partial tile: 16-byte pieces ordered [chunk of 32 columns][piece
+// 0..3][row], so that a warp-wide store or load of one piece of 32 consecutive rows is 512
+// contiguous bytes (NVLink-friendly when the owner is a peer).
+__device__ __forceinline__ int64_t stage_piece_offset(int c, int q, int row_in_tile) {
+  return (static_cast<int64_t>(c * 4 + q) * BM + row_in_tile) * 8;  // in 16-bit elements
+}
+
 // Sum the `world` staged partials of one owned tile, add bias / residual, and write the result
-// into every rank's output. Called by the 128 epilogue threads (thread == tile row).
+// into every rank's output. Called by the 128 epilogue threads (thread == tile row). Results go
+// through a per-warp shared-memory transpose so that global stores are 128-byte row segments.
 template <int BN>
-__device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, int tiles_m, int tiles_n,
-                                                 int slots, int row_in_tile, int tid_e) {
+__device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, int slot, int tiles_m,
+                                                 int tiles_n, int slots, int quarter, int lane,
+                                                 uint8_t* warp_buf) {
   const GemmComm& cm = p.comm;
   int tm, tn;
   tile_coords(tile, tiles_m, tiles_n, tm, tn);
-  const int slot = tile / cm.world;
+  const int row_in_tile = quarter * 32 + lane;
   const int row = tm * BM + row_in_tile;
   const bool row_ok = row < p.M;
   const uint16_t* base = reinterpret_cast<const uint16_t*>(cm.stage[cm.rank]) +
-                         static_cast<int64_t>(slot) * (BM * BN) + row_in_tile * BN;
+                         static_cast<int64_t>(slot) * (BM * BN);
   const int64_t src_stride = static_cast<int64_t>(slots) * (BM * BN);
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
-    const int col0 = tn * BN + c * 32;
-    if (col0 >= p.N) break;
-    float v[32];
+  for (int cp = 0; cp < BN / 64; ++cp) {
+    if (tn * BN + cp * 64 >= p.N) break;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = 0.f;
-    for (int s = 0; s < cm.world; ++s) {
-      const uint4* sp = reinterpret_cast<const uint4*>(base + s * src_stride + c * 32);
+    for (int half = 0; half < 2; ++half) {
+      const int c = cp * 2 + half;
+      const int col0 = tn * BN + c * 32;
+      float v[32];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint4 u = __ldcg(sp + q);   // L2 only: peers write these lines through NVLink
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+      for (int j = 0; j < 32; ++j) v[j] = 0.f;
+#pragma unroll 2
+      for (int s = 0; s < cm.world; ++s) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = unpack2(w[e], p.ab_dtype);
-          v[q * 8 + e * 2] += f.x;
-          v[q * 8 + e * 2 + 1] += f.y;
-        }
-      }
-    }
-    if (p.bias != nullptr) {
-      const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        if (col0 + q * 8 < p.N) {
-          const uint4 b = __ldg(bp + q);
-          const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+        for (int q = 0; q < 4; ++q) {
+          const uint4 u = __ldcg(reinterpret_cast<const uint4*>(base + s * src_stride +
+                                                                 stage_piece_offset(c, q, row_in_tile)));
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 f = unpack2(bw[e], p.ab_dtype);
+            const float2 f = unpack2(w[e], p.ab_dtype);
             v[q * 8 + e * 2] += f.x;
             v[q * 8 + e * 2 + 1] += f.y;
           }
         }
       }
-    }
-    if (row_ok) {
-      if (p.aux_mode == kAuxAdd) {
+      if (p.bias != nullptr && col0 < p.N) {
+        const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (col0 + q * 8 < p.N) {
+            const uint4 b = __ldg(bp + q);
+            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack2(bw[e], p.ab_dtype);
+              v[q * 8 + e * 2] += f.x;
+              v[q * 8 + e * 2 + 1] += f.y;
+            }
+          }
+        }
+      }
+      if (row_ok && p.aux_mode == kAuxAdd && col0 < p.N) {
         const uint4* ap = reinterpret_cast<const uint4*>(
             reinterpret_cast<const uint16_t*>(p.aux) + static_cast<int64_t>(row) * p.ldaux + col0);
 #pragma unroll
@@ -171,27 +184,35 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, in
           }
         }
       }
-      uint4 o[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        o[q].x = pack2(v[q * 8 + 0], v[q * 8 + 1], p.ab_dtype);
-        o[q].y = pack2(v[q * 8 + 2], v[q * 8 + 3], p.ab_dtype);
-        o[q].z = pack2(v[q * 8 + 4], v[q * 8 + 5], p.ab_dtype);
-        o[q].w = pack2(v[q * 8 + 6], v[q * 8 + 7], p.ab_dtype);
-      }
-      for (int dst = 0; dst < cm.world; ++dst) {
-        uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[dst]) +
-                                             static_cast<int64_t>(row) * p.ldd + col0);
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          if (col0 + q * 8 < p.N) dp[q] = o[q];
+        uint4 o;
+        o.x = pack2(v[q * 8 + 0], v[q * 8 + 1], p.ab_dtype);
+        o.y = pack2(v[q * 8 + 2], v[q * 8 + 3], p.ab_dtype);
+        o.z = pack2(v[q * 8 + 4], v[q * 8 + 5], p.ab_dtype);
+        o.w = pack2(v[q * 8 + 6], v[q * 8 + 7], p.ab_dtype);
+        const int piece = half * 4 + q;   // 16-byte piece inside this row's 128-byte segment
+        *reinterpret_cast<uint4*>(warp_buf + lane * 128 + ((piece ^ (lane & 7)) * 16)) = o;
       }
     }
+    __syncwarp();
+    // 8 lanes cover one row's 128 bytes; 4 rows per store instruction
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rl = i * 4 + (lane >> 3);
+      const int piece = lane & 7;
+      const uint4 o = *reinterpret_cast<const uint4*>(warp_buf + rl * 128 + ((piece ^ (rl & 7)) * 16));
+      const int grow = tm * BM + quarter * 32 + rl;
+      const int gcol = tn * BN + cp * 64 + piece * 8;
+      if (grow < p.M && gcol < p.N) {
+        for (int dst = 0; dst < cm.world; ++dst)
+          if (!(cm.debug & 2) || dst == cm.rank)
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[dst]) +
+                                    static_cast<int64_t>(grow) * p.ldd + gcol) = o;
+      }
+    }
+    __syncwarp();
   }
-  __threadfence_system();
-  epi_bar_sync();
-  if (tid_e < cm.world && tid_e != cm.rank)
-    st_release_sys(cm.flags[tid_e] + cm.max_tiles * kGemmMaxPeers + tile, cm.epoch);
 }
 
 template <int BN>
@@ -204,6 +225,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kStages * C::kStageBytes);
+  uint8_t* epi_smem = smem + C::kStages * C::kStageBytes + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -312,20 +334,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     }
   } else if (p.comm.world > 1) {
     // ---------------------------------------------- epilogue fused with the TP all-reduce
+    // Ownership alternates along each CTA's own tile list (tile index it -> rank (cta + it) % W),
+    // so every CTA reduces 1/W of what it computes. System-scope fences are expensive (they
+    // wait for all outstanding NVLink stores), so partial tiles are published in batches: after
+    // kBatch tiles (and at the end) one fence + one flag store per tile covers all of them.
     const GemmComm& cm = p.comm;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const int tid_e = threadIdx.x - 64;
     const int W = cm.world, me = cm.rank;
-    const int slots = (num_tiles + W - 1) / W;
+    const int slots = (num_tiles + W - 1) / W + static_cast<int>(gridDim.x);
     int* my_flags = cm.flags[me];
     __shared__ int s_ready;
     const int n_my = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    int red = 0;   // next entry of this CTA's tile list to consider for reduction
+    auto owner_of = [&](int it) { return static_cast<int>((blockIdx.x + it) % W); };
+    // staging slot of the it-th tile of this CTA inside its owner's area: slots are per CTA
+    auto slot_of = [&](int it) { return static_cast<int>(blockIdx.x) + (it / W) * static_cast<int>(gridDim.x); };
+    constexpr int kBatch = 2;
+    int red = 0, published = 0;
     bool ok = true;
+    auto publish = [&](int upto) {   // make partial tiles [published, upto) visible to their owners
+      if (upto <= published) return;
+      if (!(cm.debug & 1)) __threadfence_system();
+      epi_bar_sync();
+      for (int j = published + tid_e; j < upto; j += kEpiThreads) {
+        const int o = owner_of(j);
+        if (o != me) st_release_sys(cm.flags[o] + (blockIdx.x + j * gridDim.x) * kGemmMaxPeers + me, cm.epoch);
+      }
+      published = upto;
+    };
     for (int it = 0; it < n_my && ok; ++it) {
-      const int tile = blockIdx.x + it * gridDim.x;
-      const int owner = tile % W, slot = tile / W;
+      const int owner = owner_of(it), slot = slot_of(it);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) {
@@ -335,7 +374,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       tc_fence_after();
       // phase A: this rank's partial tile -> the owner's staging area (a peer store unless owned)
       uint16_t* dst = reinterpret_cast<uint16_t*>(cm.stage[owner]) +
-                      (static_cast<int64_t>(me) * slots + slot) * (BM * BN) + row_in_tile * BN;
+                      (static_cast<int64_t>(me) * slots + slot) * (BM * BN);
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -343,7 +382,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         __syncwarp();
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
-        uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 o;
@@ -351,18 +389,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
           o.y = pack2(__uint_as_float(r[q * 8 + 2]) * p.alpha, __uint_as_float(r[q * 8 + 3]) * p.alpha, p.ab_dtype);
           o.z = pack2(__uint_as_float(r[q * 8 + 4]) * p.alpha, __uint_as_float(r[q * 8 + 5]) * p.alpha, p.ab_dtype);
           o.w = pack2(__uint_as_float(r[q * 8 + 6]) * p.alpha, __uint_as_float(r[q * 8 + 7]) * p.alpha, p.ab_dtype);
-          d4[q] = o;
+          *reinterpret_cast<uint4*>(dst + stage_piece_offset(c, q, row_in_tile)) = o;
         }
       }
       tc_fence_before();
       mbar_arrive(&bars->tmem_empty[acc]);
-      __threadfence_system();
-      epi_bar_sync();
-      if (tid_e == 0 && owner != me) st_release_sys(cm.flags[owner] + tile * kGemmMaxPeers + me, cm.epoch);
+      if ((it + 1) % kBatch == 0 || it + 1 == n_my) publish(it + 1);
       // phase B (opportunistic): reduce owned tiles whose peer partials have all arrived
-      while (red <= it) {
+      while (red < published) {
+        if (owner_of(red) != me) { ++red; continue; }
         const int t2 = blockIdx.x + red * gridDim.x;
-        if (t2 % W != me) { ++red; continue; }
         if (tid_e == 0) {
           int ready = 1;
           for (int s = 0; s < W; ++s)
@@ -373,25 +409,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         const int ready = s_ready;
         epi_bar_sync();
         if (!ready) break;
-        comm_reduce_tile<BN>(p, t2, tiles_m, tiles_n, slots, row_in_tile, tid_e);
+        if (!(cm.debug & 4))
+          comm_reduce_tile<BN>(p, t2, slot_of(red), tiles_m, tiles_n, slots, quarter, lane, epi_smem + (warp - 2) * 4096);
         ++red;
       }
     }
+    publish(n_my);
     // drain: remaining owned tiles, now with (bounded) blocking waits
+    int first_unsignalled = 0;
     while (red < n_my) {
-      const int t2 = blockIdx.x + red * gridDim.x;
-      if (t2 % W == me) {
+      if (owner_of(red) == me) {
+        const int t2 = blockIdx.x + red * gridDim.x;
         if (tid_e < W && tid_e != me)
           wait_flag_ge(my_flags + t2 * kGemmMaxPeers + tid_e, cm.epoch, p.status);
         epi_bar_sync();
-        comm_reduce_tile<BN>(p, t2, tiles_m, tiles_n, slots, row_in_tile, tid_e);
+        if (!(cm.debug & 4))
+          comm_reduce_tile<BN>(p, t2, slot_of(red), tiles_m, tiles_n, slots, quarter, lane, epi_smem + (warp - 2) * 4096);
       }
       ++red;
     }
+    // one fence for all reduced tiles of this CTA, then tell the peers which tiles have landed
+    if (!(cm.debug & 1)) __threadfence_system();
+    epi_bar_sync();
+    for (int j = first_unsignalled + tid_e; j < n_my * W; j += kEpiThreads) {
+      const int itj = j / W, dstr = j % W;
+      if (owner_of(itj) == me && dstr != me)
+        st_release_sys(cm.flags[dstr] + cm.max_tiles * kGemmMaxPeers + (blockIdx.x + itj * gridDim.x), cm.epoch);
+    }
     // the tiles owned by peers must have landed in this rank's output before the kernel ends
     for (int i = tid_e; i < n_my; i += kEpiThreads) {
-      const int t = blockIdx.x + i * gridDim.x;
-      if (t % W != me) wait_flag_ge(my_flags + cm.max_tiles * kGemmMaxPeers + t, cm.epoch, p.status);
+      if (owner_of(i) != me && !(cm.debug & 4))
+        wait_flag_ge(my_flags + cm.max_tiles * kGemmMaxPeers + (blockIdx.x + i * gridDim.x), cm.epoch, p.status);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -612,7 +660,7 @@ cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
   }
   const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
   if (a.comm.world > 1) {
-    const int64_t slots = (tiles + a.comm.world - 1) / a.comm.world;
+    const int64_t slots = (tiles + a.comm.world - 1) / a.comm.world + (tiles < device_sm_count() ? tiles : device_sm_count());
     ETHB_RETURN_IF(tiles > a.comm.max_tiles, cudaErrorInvalidValue, "fused all-reduce: more tiles than flags");
     ETHB_RETURN_IF(slots * a.comm.world * BM * BN > a.comm.stage_elems, cudaErrorInvalidValue,
                    "fused all-reduce: staging area too small");

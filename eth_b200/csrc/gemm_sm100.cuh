@@ -29,6 +29,7 @@ struct GemmComm {
   void* out[kGemmMaxPeers];
   int* flags[kGemmMaxPeers];
   int64_t stage_elems;  // capacity of one rank's staging area in 16-bit elements
+  int debug;            // timing experiments only: 1 no system fences, 2 no peer output stores, 4 no reduce
 };
 
 struct GemmArgs {

@@ -32,14 +32,17 @@ class FusedTPBackend:
         rows = (max_tokens + 127) // 128 * 128
         cols = (hidden + 255) // 256 * 256
         self.out_slot_bytes = rows * cols * esize
-        # staging holds `world` partials of each owned tile: about one full output, plus rounding
-        self.stage_elems = rows * cols + self.world * 128 * 256
+        # staging holds `world` partials of each owned tile (about one full output) plus one spare
+        # slot per CTA and source, because slots are assigned per CTA
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.stage_elems = rows * cols + (sms + 1) * self.world * 128 * 256
         self.stage = SymmetricBuffer(self.stage_elems * esize, group_ranks, my_rank, group, device)
         self.out = SymmetricBuffer(self.out_slot_bytes * RING, group_ranks, my_rank, group, device)
         self.flags = SymmetricBuffer(MAX_TILES * 9 * 4, group_ranks, my_rank, group, device)
         self.rank = self.stage.index
         self.epoch = 0
         self.slot = 0
+        self.debug = 0   # timing experiments only (see GemmComm::debug)
 
     @classmethod
     def create(cls, pstate, coll, device, args):
@@ -64,7 +67,7 @@ class FusedTPBackend:
         off = slot * self.out_slot_bytes
         native.lib().gemm_allreduce(a, False, b, b_mn, bias, residual, float(alpha), native.status(a.device),
                                     self.stage.ptrs, self.out.offset_ptrs(off), self.flags.ptrs, self.rank,
-                                    self.epoch, MAX_TILES, self.stage_elems, n)
+                                    self.epoch, MAX_TILES, self.stage_elems, n, self.debug)
         out = self.out.tensor((m, n), self.dtype, off)
         out._ethb_ring = True   # short-lived: valid until RING further fused calls
         return out
