@@ -35,6 +35,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--output", type=Path, required=True)
     ap.add_argument("--status", required=True, choices=["planned", "complete"])
+    ap.add_argument("--model", default="gpt")
     ap.add_argument("--model-size", required=True)
     ap.add_argument("--hardware", required=True)
     ap.add_argument("--tp-sizes", required=True, help="comma separated")
@@ -43,7 +44,7 @@ def main(argv=None):
     ap.add_argument("--node-rank", type=int, default=0)
     a = ap.parse_args(argv)
     write_metadata(a.output, a.status, a.model_size, a.hardware, [int(t) for t in a.tp_sizes.split(",")],
-                   a.num_nodes, a.gpus_per_node, a.node_rank)
+                   a.num_nodes, a.gpus_per_node, a.node_rank, model_name=a.model)
 
 
 if __name__ == "__main__":
