@@ -255,6 +255,9 @@ class TrainEngine:
         a = self.args
         if sync is None:
             sync = not getattr(a, "async_optimizer", False)
+        evidence_dir = getattr(a, "grad_sync_evidence_dir", None)
+        if evidence_dir and self.iteration == 0:
+            self._evidence("init", evidence_dir)
         self.optimizer.zero_grad()
         self.loss_acc.zero_()
         n_mb = self.pstate.num_microbatches
@@ -265,10 +268,16 @@ class TrainEngine:
         # global loss weight -> normalisation factor (device scalar)
         self.coll.all_reduce_sum(self.loss_acc)
         normalization = a.nominal_global_loss_scale / self.loss_acc[1]
+        if evidence_dir:
+            self._evidence("pre_sync", evidence_dir)
         if self._needs_reduction:
             self.grad_sync.execute(1.0)
         self.optimizer.set_grad_factor(normalization)
+        if evidence_dir:
+            self._evidence("post_sync", evidence_dir, grad_factor=float(self.optimizer.ctrl[2]))
         ok, grad_norm, _ = self.optimizer.step(sync=sync)
+        if evidence_dir:
+            self._evidence("post_step", evidence_dir, update_successful=bool(ok))
         increment = self.clock.after_attempt(ok)
         if ok:
             self.lr_scheduler.step(increment)
@@ -278,6 +287,10 @@ class TrainEngine:
                  "loss_acc": self.loss_acc}
         self.last_stats = stats
         return stats
+
+    def _evidence(self, phase, out_dir, **metrics):
+        from ..parallel.grad_sync.evidence import snapshot_rank
+        snapshot_rank(self, phase, self.iteration + 1, out_dir, metrics)
 
     def reduced_loss(self) -> float:
         """Mean masked LM loss of the last iteration (synchronises)."""
