@@ -156,7 +156,8 @@ class GradientBucketExecutor:
 
     def _table(self, bucket, payload):
         """Device-resident copy tables of a bucket (built on first use)."""
-        tab = self._tables.get(bucket.bucket_id)
+        key = (bucket.bucket_id, payload.data_ptr())
+        tab = self._tables.get(key)
         if tab is not None:
             return tab
         pack_rows, unpack_rows, scales, biggest = [], [], set(), 1
@@ -181,7 +182,7 @@ class GradientBucketExecutor:
         tab = {"pack": torch.tensor(pack_rows, dtype=torch.int64, device=dev),
                "unpack": torch.tensor(unpack_rows, dtype=torch.int64, device=dev),
                "scale": scales.pop() if scales else 1.0, "max": biggest}
-        self._tables[bucket.bucket_id] = tab
+        self._tables[key] = tab
         return tab
 
     # ------------------------------------------------------------------ pack / unpack
@@ -224,8 +225,8 @@ class GradientBucketExecutor:
         if self._evidence is not None:
             self._evidence.observe_packed_bucket(bucket, payload)
         if self._peer is not None and self._peer.handles(bucket):
-            self._peer.all_reduce(bucket, payload, normalization_scale)
-            self.unpack(bucket, payload, 1.0)
+            reduced = self._peer.all_reduce(bucket, payload, normalization_scale)
+            self.unpack(bucket, reduced, 1.0)
         else:
             self._all_reduce_sum(payload, self._registry.handle(bucket.process_group_id))
             self.unpack(bucket, payload, normalization_scale)

@@ -1,0 +1,68 @@
+"""Peer-memory reduction backend of the gradient bucket executor.
+
+Every rank's packed bucket lives in a symmetric scratch buffer that all ranks of the node have
+mapped; the reduction of a bucket is ONE kernel (`peer_allreduce`, csrc/comm.cu): it signals
+arrival to the peers of the bucket's process group, reads every peer's bucket over NVLink, sums in
+fp32 in rank order (bit-identical results on all ranks), applies the normalisation scale, and
+writes the result into a local buffer from which the bucket is unpacked. A release phase at the end
+of the kernel guarantees that nobody still reads a rank's scratch when that rank repacks it.
+
+Used when all ranks share one node; otherwise the executor falls back to the injected all-reduce.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ...ops import native
+from ..peer_memory import SymmetricBuffer
+
+_DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+FLAG_INTS_PER_GROUP = 64
+
+
+class PeerReduceBackend:
+    def __init__(self, plan, global_rank: int, coll, device):
+        world = coll.world_size
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", world))
+        if local_world != world:
+            raise RuntimeError("peer-memory gradient reduction needs all ranks on one node")
+        self.plan, self.rank, self.device = plan, global_rank, torch.device(device)
+        self.groups = {g.process_group_id: g.ranks for g in plan.process_groups}
+        self.group_index = {g.process_group_id: i for i, g in enumerate(plan.process_groups)}
+        self.world_ranks = tuple(range(world))
+        # one scratch size for everybody: the largest bucket of any rank, per dtype
+        self.max_numel = {}
+        for (_r, dtype), numel in plan.max_scratch_numel_by_rank_and_dtype:
+            self.max_numel[dtype] = max(self.max_numel.get(dtype, 0), numel)
+        self.scratch = {}
+        self.reduced = {}
+        self.flags = SymmetricBuffer(max(1, len(plan.process_groups)) * FLAG_INTS_PER_GROUP * 4, self.world_ranks,
+                                     global_rank, None, self.device)
+        self.epoch = {}
+
+    def scratch_factory(self, name, numel, dtype, device):
+        """Scratch of the executor: symmetric, sized by the largest bucket in the world."""
+        n = max(self.max_numel.get(name, numel), numel)
+        esize = torch.empty((), dtype=dtype).element_size()
+        buf = SymmetricBuffer(n * esize, self.world_ranks, self.rank, None, self.device)
+        self.scratch[name] = buf
+        self.reduced[name] = torch.empty(n, dtype=dtype, device=self.device)
+        return buf.tensor((n,), dtype)
+
+    def handles(self, bucket) -> bool:
+        return len(self.groups[bucket.process_group_id]) > 1 and bucket.grad_dtype in self.scratch
+
+    def all_reduce(self, bucket, payload, scale: float):
+        ranks = self.groups[bucket.process_group_id]
+        gi = self.group_index[bucket.process_group_id]
+        buf = self.scratch[bucket.grad_dtype]
+        bufs = [buf.ptrs[r] for r in ranks]
+        flags = [self.flags.ptrs[r] + gi * FLAG_INTS_PER_GROUP * 4 for r in ranks]
+        self.epoch[gi] = self.epoch.get(gi, 0) + 1
+        out = self.reduced[bucket.grad_dtype][:bucket.exact_numel]
+        native.lib().peer_allreduce(bufs, flags, ranks.index(self.rank), self.epoch[gi], bucket.exact_numel,
+                                    _DTYPE_CODE[payload.dtype], float(scale), out, None, 0.0,
+                                    native.status(self.device))
+        return out

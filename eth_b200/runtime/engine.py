@@ -141,12 +141,16 @@ class TrainEngine:
         peer_factory = None
         backend = getattr(args, "grad_sync_backend", "auto")
         if backend in ("auto", "peer") and self.device.type == "cuda" and self.coll.enabled:
-            try:
-                from ..parallel.grad_sync.peer_backend import PeerReduceBackend
-                peer_factory = lambda plan, rank: PeerReduceBackend(plan, rank, self.coll, self.device)  # noqa: E731
-            except Exception:
-                if backend == "peer":
-                    raise
+            def peer_factory(plan, rank):
+                try:
+                    from ..parallel.grad_sync.peer_backend import PeerReduceBackend
+                    if not any(len(g.ranks) > 1 for g in plan.process_groups):
+                        return None
+                    return PeerReduceBackend(plan, rank, self.coll, self.device)
+                except Exception:
+                    if backend == "peer":
+                        raise
+                    return None
 
         def group_gather(out, obj, handle):
             self.coll.all_gather_object(out, obj, group=handle)
