@@ -129,68 +129,90 @@ __global__ void ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gam
   }
 }
 
-// Backward: a persistent grid strides over rows; every thread owns fixed columns, so the
-// dgamma/dbeta partial sums stay in registers and are written once per CTA to the workspace.
-template <typename T, int kLnMaxIter>
-__global__ void ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
-                              const T* __restrict__ gamma, const float* __restrict__ mean,
-                              const float* __restrict__ rstd, T* __restrict__ dx,
-                              float* __restrict__ ws, int rows, int hidden) {
-  __shared__ float red[32];
+// Backward, two kernels.
+//  (1) dx: one warp per row, no block-level synchronisation. Two passes over the row: the first
+//      accumulates sum(dy*gamma) and sum(dy*gamma*xhat), the second recomputes the terms (the row is
+//      L1/L2 resident by then) and writes dx.
+//  (2) dgamma / dbeta partials: a (32 x 8) CTA owns 256 columns and a slab of rows; each thread keeps
+//      8 column sums in registers and the 8 row-lanes are combined through shared memory. A last
+//      small kernel sums the slabs (reduce_parts_kernel).
+template <typename T>
+__global__ void ln_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                 const T* __restrict__ gamma, const float* __restrict__ mean,
+                                 const float* __restrict__ rstd, T* __restrict__ dx, int rows,
+                                 int hidden) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
   const int nvec = hidden >> 3;
-  float g[kLnMaxIter][8], dg[kLnMaxIter][8], db[kLnMaxIter][8];
-#pragma unroll
-  for (int i = 0; i < kLnMaxIter; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; g[i][j] = 0.f; }
-    if (c < nvec) load8(gamma + c * 8, g[i]);
-  }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_block) {
     const int64_t off = static_cast<int64_t>(row) * hidden;
     const float mu = mean[row], rs = rstd[row];
-    float xh[kLnMaxIter][8], wdy[kLnMaxIter][8];
     float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < nvec; c += 32) {
+      float xv[8], dyv[8], g[8];
+      load8(x + off + c * 8, xv);
+      load8(dy + off + c * 8, dyv);
+      load8(gamma + c * 8, g);
 #pragma unroll
-    for (int i = 0; i < kLnMaxIter; ++i) {
-      const int c = threadIdx.x + i * blockDim.x;
-      if (c < nvec) {
-        float xv[8], dyv[8];
-        load8(x + off + c * 8, xv);
-        load8(dy + off + c * 8, dyv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (xv[j] - mu) * rs;
-          wdy[i][j] = dyv[j] * g[i][j];
-          s1 += wdy[i][j];
-          s2 += wdy[i][j] * xh[i][j];
-          dg[i][j] += dyv[j] * xh[i][j];
-          db[i][j] += dyv[j];
-        }
+      for (int j = 0; j < 8; ++j) {
+        const float w = dyv[j] * g[j];
+        s1 += w;
+        s2 += w * (xv[j] - mu) * rs;
       }
     }
-    const float m1 = block_sum(s1, red) / hidden;
-    const float m2 = block_sum(s2, red) / hidden;
+    const float m1 = warp_sum(s1) / hidden;
+    const float m2 = warp_sum(s2) / hidden;
+    for (int c = lane; c < nvec; c += 32) {
+      float xv[8], dyv[8], g[8], o[8];
+      load8(x + off + c * 8, xv);
+      load8(dy + off + c * 8, dyv);
+      load8(gamma + c * 8, g);
 #pragma unroll
-    for (int i = 0; i < kLnMaxIter; ++i) {
-      const int c = threadIdx.x + i * blockDim.x;
-      if (c < nvec) {
-        float o[8];
+      for (int j = 0; j < 8; ++j) o[j] = (dyv[j] * g[j] - m1 - (xv[j] - mu) * rs * m2) * rs;
+      store8(dx + off + c * 8, o);
+    }
+  }
+}
+
+template <typename T>
+__global__ void ln_bwd_param_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                    const float* __restrict__ mean, const float* __restrict__ rstd,
+                                    float* __restrict__ ws, int rows, int hidden) {
+  __shared__ float sg[8][256 + 8];
+  __shared__ float sb[8][256 + 8];
+  const int c0 = (blockIdx.x * 32 + threadIdx.x) * 8;
+  const int parts = gridDim.y;
+  const int per = (rows + parts - 1) / parts;
+  const int r0 = per * blockIdx.y, r1 = min(rows, r0 + per);
+  float dg[8] = {0, 0, 0, 0, 0, 0, 0, 0}, db[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c0 < hidden) {
+    for (int r = r0 + threadIdx.y; r < r1; r += 8) {
+      float xv[8], dyv[8];
+      load8(x + static_cast<int64_t>(r) * hidden + c0, xv);
+      load8(dy + static_cast<int64_t>(r) * hidden + c0, dyv);
+      const float mu = mean[r], rs = rstd[r];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = (wdy[i][j] - m1 - xh[i][j] * m2) * rs;
-        store8(dx + off + c * 8, o);
+      for (int j = 0; j < 8; ++j) {
+        dg[j] += dyv[j] * (xv[j] - mu) * rs;
+        db[j] += dyv[j];
       }
     }
   }
-  float* wg = ws + static_cast<int64_t>(blockIdx.x) * hidden;
-  float* wb = ws + static_cast<int64_t>(gridDim.x + blockIdx.x) * hidden;
 #pragma unroll
-  for (int i = 0; i < kLnMaxIter; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-    if (c < nvec) {
-      store8(wg + c * 8, dg[i]);
-      store8(wb + c * 8, db[i]);
-    }
+  for (int j = 0; j < 8; ++j) {
+    sg[threadIdx.y][threadIdx.x * 8 + j] = dg[j];
+    sb[threadIdx.y][threadIdx.x * 8 + j] = db[j];
+  }
+  __syncthreads();
+  const int t = threadIdx.y * 32 + threadIdx.x;
+  const int c = blockIdx.x * 256 + t;
+  if (c < hidden) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { a += sg[k][t]; b += sb[k][t]; }
+    ws[static_cast<int64_t>(blockIdx.y) * hidden + c] = a;
+    ws[static_cast<int64_t>(parts + blockIdx.y) * hidden + c] = b;
   }
 }
 
@@ -691,25 +713,34 @@ cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, vo
   return cudaGetLastError();
 }
 
-int ln_bwd_parts(int rows) { return rows < kSMs * 4 ? rows : kSMs * 4; }
+int ln_bwd_parts(int rows) {
+  int p = rows / 64;
+  if (p < 1) p = 1;
+  if (p > 96) p = 96;
+  return p;
+}
 
 cudaError_t layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, void* dx, void* dgamma, void* dbeta, float* ws,
                           int rows, int hidden, int dtype, int grad_dtype, int accumulate,
                           cudaStream_t st) {
   if (hidden % 8 != 0 || hidden / 8 > 4 * 1024) return cudaErrorInvalidValue;
-  int iters, threads;
-  ln_shape(hidden, iters, threads);
   const int parts = ln_bwd_parts(rows);
-  ETHB_DISPATCH(dtype, T, ETHB_LN_ITERS(iters, I,
-                (ln_bwd_kernel<T, I><<<parts, threads, 0, st>>>((const T*)dy, (const T*)x,
-                                                                 (const T*)gamma, mean, rstd,
-                                                                 (T*)dx, ws, rows, hidden))));
+  const int warps = 4;
+  int grid = (rows + warps - 1) / warps;
+  if (grid > kSMs * 16) grid = kSMs * 16;
+  ETHB_DISPATCH(dtype, T,
+                (ln_bwd_dx_kernel<T><<<grid, warps * 32, 0, st>>>((const T*)dy, (const T*)x, (const T*)gamma,
+                                                                  mean, rstd, (T*)dx, rows, hidden)));
+  dim3 pgrid((hidden + 255) / 256, parts), pblock(32, 8);
+  ETHB_DISPATCH(dtype, T,
+                (ln_bwd_param_kernel<T><<<pgrid, pblock, 0, st>>>((const T*)dy, (const T*)x, mean, rstd, ws,
+                                                                  rows, hidden)));
   const int rthreads = 128;
   ETHB_DISPATCH(grad_dtype, G,
                 (reduce_parts_kernel<G><<<(hidden + rthreads - 1) / rthreads, rthreads, 0, st>>>(
                     ws, (G*)dgamma, (G*)dbeta, parts, hidden, accumulate)));
-  count_launch(2);
+  count_launch(3);
   return cudaGetLastError();
 }
 
