@@ -287,22 +287,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const bool diag = p.causal && (j == qt);
       const bool tail = (j + 1) * kTile > p.seq_k;
       const int col_limit_tail = p.seq_k - j * kTile;  // valid columns in a tail tile
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      // One TMEM read of the whole 128-column score row: the four loads are issued back to back
+      // and waited for once, so their latency overlaps.
+      uint32_t r[4][32];
+      __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c * 32 + i;
-          float s = __uint_as_float(r[i]);
-          if ((diag && col > r_local) || (tail && col >= col_limit_tail)) s = -INFINITY;
-          mx = fmaxf(mx, s);
-        }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, r[c]);
+      tmem_ld_wait();
+      if (diag || tail) {   // rare: the diagonal tile of a causal row block, or a ragged last tile
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            if ((diag && col > r_local) || (tail && col >= col_limit_tail)) r[c][i] = 0xff800000u;  // -inf
+          }
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(r[0][i]));
+        mx1 = fmaxf(mx1, __uint_as_float(r[1][i]));
+        mx2 = fmaxf(mx2, __uint_as_float(r[2][i]));
+        mx3 = fmaxf(mx3, __uint_as_float(r[3][i]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m_run, mx * sl2);
       if (j == 0) {
         m_run = m_new;
@@ -320,37 +329,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < D / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld_32x32b_x16(o_addr + c * 16, r);
+            uint32_t o16[16];
+            tmem_ld_32x32b_x16(o_addr + c * 16, o16);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x16(o_addr + c * 16, r);
+            for (int i = 0; i < 16; ++i) o16[i] = __float_as_uint(__uint_as_float(o16[i]) * alpha);
+            tmem_st_32x32b_x16(o_addr + c * 16, o16);
           }
           tmem_st_wait();
         }
       }
-      // pass 2: P = exp2(s * scale_log2 - m), packed to 16 bit into the first 64 score columns
-      float lsum = 0.f;
-#pragma unroll 1
+      // P = exp2(s * scale_log2 - m), packed to 16 bit into the first 64 score columns
+      float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int col = c * 32 + 2 * i;
-          float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
-          float p0 = exp2f(s0 * sl2 - m_run), p1 = exp2f(s1 * sl2 - m_run);
-          if ((diag && col > r_local) || (tail && col >= col_limit_tail)) p0 = 0.f;
-          if ((diag && col + 1 > r_local) || (tail && col + 1 >= col_limit_tail)) p1 = 0.f;
-          lsum += p0 + p1;
+          const float p0 = exp2f(fmaf(__uint_as_float(r[c][2 * i]), sl2, -m_run));
+          const float p1 = exp2f(fmaf(__uint_as_float(r[c][2 * i + 1]), sl2, -m_run));
+          ls0 += p0;
+          ls1 += p1;
           pk[i] = pack_pair(p0, p1, p.dtype);
         }
         tmem_st_32x32b_x16(s_addr + c * 16, pk);
       }
+      const float lsum = ls0 + ls1;
       l_run += lsum;
       tmem_st_wait();
       tc_fence_before();
@@ -639,24 +643,27 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       const bool diag = p.causal && (i == j);
-#pragma unroll 1
+      uint32_t rs[2][32], rd[2][32];
+      __syncwarp();
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(s_addr + c * 32, rs);
-        tmem_ld_32x32b_x32(dp_addr + c * 32, rd);
-        tmem_ld_wait();
+        tmem_ld_32x32b_x32(s_addr + c * 32, rs[c]);
+        tmem_ld_32x32b_x32(dp_addr + c * 32, rd[c]);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int x = 0; x < 16; ++x) {
           const int col = c * 32 + 2 * x;          // query column inside this 64-wide sub-tile
           const int ql = wg * 64 + col;            // query row inside the 128-row tile
-          float p0 = exp2f(__uint_as_float(rs[2 * x]) * sl2 - a_lse[col]);
-          float p1 = exp2f(__uint_as_float(rs[2 * x + 1]) * sl2 - a_lse[col + 1]);
+          float p0 = exp2f(fmaf(__uint_as_float(rs[c][2 * x]), sl2, -a_lse[col]));
+          float p1 = exp2f(fmaf(__uint_as_float(rs[c][2 * x + 1]), sl2, -a_lse[col + 1]));
           if (diag && r_local > ql) p0 = 0.f;
           if (diag && r_local > ql + 1) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rd[2 * x]) - a_del[col]);
-          const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - a_del[col + 1]);
+          const float d0 = p0 * (__uint_as_float(rd[c][2 * x]) - a_del[col]);
+          const float d1 = p1 * (__uint_as_float(rd[c][2 * x + 1]) - a_del[col + 1]);
           pk[x] = pack_pair(p0, p1, p.dtype);
           dk[x] = pack_pair(d0, d1, p.dtype);
         }
@@ -849,24 +856,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       tc_fence_after();
       const bool diag = p.causal && (t == i);
       const int kv0 = t * kTile + wg * 64;       // first key index of this sub-tile
-#pragma unroll 1
+      const bool ragged = kv0 + 64 > p.seq_k;
+      uint32_t rs[2][32], rd[2][32];
+      __syncwarp();
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(s_addr + c * 32, rs);
-        tmem_ld_32x32b_x32(dp_addr + c * 32, rd);
-        tmem_ld_wait();
+        tmem_ld_32x32b_x32(s_addr + c * 32, rs[c]);
+        tmem_ld_32x32b_x32(dp_addr + c * 32, rd[c]);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t dk[16];
 #pragma unroll
         for (int x = 0; x < 16; ++x) {
           const int col = c * 32 + 2 * x;
           const int kl = wg * 64 + col;            // key row inside the 128-row tile
-          float p0 = exp2f(__uint_as_float(rs[2 * x]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[2 * x + 1]) * sl2 - lse2);
-          if ((diag && kl > r_local) || (kv0 + col >= p.seq_k)) p0 = 0.f;
-          if ((diag && kl + 1 > r_local) || (kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rd[2 * x]) - delta);
-          const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - delta);
+          float p0 = exp2f(fmaf(__uint_as_float(rs[c][2 * x]), sl2, -lse2));
+          float p1 = exp2f(fmaf(__uint_as_float(rs[c][2 * x + 1]), sl2, -lse2));
+          if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
+          if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(rd[c][2 * x]) - delta);
+          const float d1 = p1 * (__uint_as_float(rd[c][2 * x + 1]) - delta);
           dk[x] = pack_pair(d0, d1, p.dtype);
         }
         tmem_st_32x32b_x16(dp_addr + c * 16, dk);
