@@ -1,0 +1,58 @@
+"""Sharding-spec algebra: which collective connects two placements, duals, and execution on Gloo."""
+import pytest
+import torch
+
+from eth_b200.parallel.resharding import ReshardStep, plan_reshard, reshard_bytes
+from eth_b200.search.model_ops import full_op_list, get_op_spec
+from tests.helpers.multiproc import run_ranks
+
+
+def test_op_specs_chain_without_communication_for_algo0():
+    tp, dp = 4, 2
+    ops = full_op_list(1)
+    for a, b in zip(ops, ops[1:]):
+        out, inp = get_op_spec(a, tp, dp, 0, False), get_op_spec(b, tp, dp, 0, True)
+        step = plan_reshard(out, inp)
+        # column -> row pairs need nothing in between; row outputs are reduced inside the op
+        assert step.primitive in ("identity", "split"), (a, b, step)
+    assert len(full_op_list(3)) == 33 and len(full_op_list(3, legacy=True)) == 42
+
+
+@pytest.mark.parametrize("src,dst,prim", [
+    ({"R": 4, "V": 1, "dims": [1, 1, 1]}, {"R": 1, "V": 1, "dims": [1, 1, 4]}, "split"),
+    ({"R": 1, "V": 4, "dims": [1, 1, 1]}, {"R": 4, "V": 1, "dims": [1, 1, 1]}, "all_reduce"),
+    ({"R": 1, "V": 4, "dims": [1, 1, 1]}, {"R": 1, "V": 1, "dims": [1, 4, 1]}, "reduce_scatter"),
+    ({"R": 1, "V": 1, "dims": [1, 1, 4]}, {"R": 4, "V": 1, "dims": [1, 1, 1]}, "all_gather"),
+    ({"R": 1, "V": 1, "dims": [1, 1, 4]}, {"R": 1, "V": 1, "dims": [4, 1, 1]}, "all_to_all"),
+])
+def test_primitive_choice_and_dual(src, dst, prim):
+    step = plan_reshard(src, dst)
+    assert step.primitive == prim and step.group_size == 4
+    if prim in ("split", "all_gather", "all_to_all"):      # nothing turns back into partial sums
+        assert plan_reshard(dst, src).primitive == step.dual().primitive
+    assert reshard_bytes(step, 1000.0) == (0.0 if prim == "split" else (1500.0 if prim == "all_reduce" else 750.0))
+
+
+def test_mismatched_sizes_are_rejected():
+    with pytest.raises(ValueError):
+        plan_reshard({"R": 2, "V": 1, "dims": [1, 1, 1]}, {"R": 1, "V": 1, "dims": [1, 1, 4]})
+
+
+def _run_prims(rank, world):
+    from eth_b200.parallel.resharding import apply_reshard
+    full = torch.arange(4 * 6 * 8, dtype=torch.float32).view(4, 6, 8)
+    out = {}
+    shard = full.chunk(world, dim=2)[rank].contiguous()
+    out["all_gather"] = torch.equal(apply_reshard(shard, ReshardStep("all_gather", world, src_dim=2)), full)
+    out["split"] = torch.equal(apply_reshard(full, ReshardStep("split", world, dst_dim=1)), full.chunk(world, 1)[rank])
+    out["all_reduce"] = torch.equal(apply_reshard(full, ReshardStep("all_reduce", world)), full * world)
+    out["reduce_scatter"] = torch.equal(apply_reshard(full, ReshardStep("reduce_scatter", world, dst_dim=0)),
+                                        (full * world).chunk(world, 0)[rank])
+    a2a = apply_reshard(shard, ReshardStep("all_to_all", world, src_dim=2, dst_dim=0))
+    out["all_to_all"] = torch.equal(a2a, full.chunk(world, 0)[rank])
+    return out
+
+
+def test_primitives_on_gloo():
+    for res in run_ranks(2, _run_prims):
+        assert all(res.values()), res
