@@ -933,3 +933,66 @@ cudaError_t synthetic_batch(int64_t* tokens, int64_t* labels, float* loss_mask,
 }
 
 }  // namespace ethb
+
+// ================================================================================================
+// Allocation-free column sums (see no_alloc.h): same kernels as `colsum`, partial sums in a
+// fixed device array owned by the library.
+// ================================================================================================
+#include "no_alloc.h"
+
+#include <mutex>
+
+namespace {
+
+// parts x cols floats; 64 x 16384 x 4 B = 4 MiB per GPU that loads the library
+static __device__ __align__(256) float g_colsum_scratch[ETHB_COLSUM_NOALLOC_MAX_PARTS * ETHB_COLSUM_NOALLOC_MAX_COLS];
+
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mutex;
+
+// Device address of the scratch array on the current device. In host code the array's name is only
+// a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress, queried
+// once per device with that device current.
+cudaError_t scratch_for_current_device(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_colsum_scratch);
+    if (e != cudaSuccess) return e;
+    g_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *ptr = g_scratch_addr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int ethb_colsum_noalloc(const void* x, void* out, int64_t rows, int32_t cols, int32_t dtype,
+                                   int32_t out_dtype, int32_t accumulate, void* cuda_stream) {
+  using namespace ethb;
+  if (x == nullptr || out == nullptr || rows <= 0 || cols <= 0 || cols % 8 != 0) return ETHB_NOALLOC_BAD_ARGUMENT;
+  if (dtype < 0 || dtype > 2 || out_dtype < 0 || out_dtype > 2) return ETHB_NOALLOC_BAD_ARGUMENT;
+  if (cols > ETHB_COLSUM_NOALLOC_MAX_COLS) return ETHB_NOALLOC_TOO_LARGE;
+  const int parts = colsum_parts(rows);
+  if (parts > ETHB_COLSUM_NOALLOC_MAX_PARTS) return ETHB_NOALLOC_TOO_LARGE;
+  float* ws = nullptr;
+  cudaError_t e = scratch_for_current_device(&ws);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = colsum(x, out, ws, rows, cols, dtype, out_dtype, accumulate, static_cast<cudaStream_t>(cuda_stream));
+  return static_cast<int>(e);
+}
+
+extern "C" const char* ethb_noalloc_strerror(int code) {
+  if (code == 0) return "success";
+  if (code == ETHB_NOALLOC_BAD_ARGUMENT)
+    return "bad argument: null pointer, non-positive size, cols not a multiple of 8, or unknown dtype code";
+  if (code == ETHB_NOALLOC_TOO_LARGE)
+    return "problem exceeds the built-in scratch array (cols <= 16384 and at most 64 row partitions)";
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "unknown error code";
+}
