@@ -6,7 +6,7 @@
     python bench.py --impl reference --gpus 1 ...      (the unmodified reference, if installed)
 
 Model and layout follow the GPT-1.3B fp16 training config (24 layers, hidden 2048, 16 heads,
-seq 2048, vocab 50257, micro-batch 4, block-wise gradient sync with 32 MiB buckets):
+seq 2048, vocab 50257, micro-batch 4 per data-parallel replica, block-wise gradient sync with 32 MiB buckets):
     8 GPUs: PP2 x TP2 x DP2, global batch 512
     4 GPUs: TP2 x DP2, global batch 256      2 GPUs: TP2, global batch 128      1 GPU: global batch 64
 so the work per GPU is constant (weak scaling). Data is synthetic (closed-form token ids), weights
@@ -95,7 +95,8 @@ def build_config(n_gpus: int):
     from eth_b200.contract.config import uniform_config
     pp, tp, dp = LAYOUTS[n_gpus]
     gbs = SAMPLES_PER_GPU * n_gpus
-    return uniform_config(MODEL, pp=pp, tp=tp, dp=dp, gbs=gbs, mbs=MICRO_BATCH), (pp, tp, dp), gbs
+    # a pipe's micro_batch_size spans its DP replicas; every replica runs MICRO_BATCH samples per micro-batch
+    return uniform_config(MODEL, pp=pp, tp=tp, dp=dp, gbs=gbs, mbs=MICRO_BATCH * dp), (pp, tp, dp), gbs
 
 
 def host_batch_provider(vocab: int):
@@ -209,7 +210,7 @@ def run_ours(opts):
             "dtype": "bf16" if opts.bf16 else "fp16", "data": "synthetic token ids, random-init weights",
             "impl": "eth_b200",
             "config": {"model": "GPT-1.3B (24 layers, hidden 2048, 16 heads)", "global_batch": gbs,
-                       "seq_len": MODEL["seq_length"], "micro_batch": MICRO_BATCH,
+                       "seq_len": MODEL["seq_length"], "micro_batch": MICRO_BATCH, "pipeline_micro_batch": MICRO_BATCH * dp,
                        "parallelism": f"pp{pp}tp{tp}dp{dp}", "grad_sync": "block, 32 MiB buckets",
                        "l2": "inputs larger than L2 (each step streams several GB of weights and activations)"},
             "clocks": clocks,
