@@ -2,6 +2,10 @@
 //
 //   D[M,N] = epilogue( alpha * sum_k A(m,k) * B(n,k) )
 //
+// Two kernels share the epilogue. The single-CTA kernel (also the one that carries the fused
+// tensor-parallel all-reduce) is described here; the CTA-pair kernel further down computes
+// 256 x BN tiles with `cta_group::2` MMAs and is the default for plain GEMMs.
+//
 // One CTA per SM walks a static list of 128 x BN output tiles. Inside a CTA:
 //   warp 0   : TMA producer  - streams 128x64 / BNx64 operand tiles through a ring of shared
 //              memory stages (128-byte swizzle), signalling `full[stage]` by transaction count.
@@ -29,6 +33,8 @@ namespace ethb {
 static std::atomic<int64_t> g_launches{0};
 int64_t launch_count() { return g_launches.load(); }
 void count_launch(int n) { g_launches.fetch_add(n); }
+static std::atomic<int> g_gemm_variant{0};
+void set_gemm_variant(int v) { g_gemm_variant.store(v); }
 static thread_local const char* g_error_detail = "";
 const char* last_error_detail() { return g_error_detail; }
 void set_error_detail(const char* where) { g_error_detail = where; }
@@ -212,6 +218,119 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, in
       }
     }
     __syncwarp();
+  }
+}
+
+// Drain one 128 x BN accumulator (this thread owns TMEM lane == output row `row`) through the
+// fused epilogue: alpha, bias, residual / GeLU-gradient, accumulate, convert, optional GeLU copy.
+// `n_base` is the first output column of the tile.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& p, uint32_t taddr, int row, int n_base) {
+  const bool row_ok = row < p.M;
+  const int out_is_f32 = (p.d_dtype == kF32);
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    const int col0 = n_base + c * 32;
+    if (col0 >= p.N) break;  // uniform across the warp
+    uint32_t r[32];
+    __syncwarp();
+    tmem_ld_32x32b_x32(taddr + c * 32, r);
+    tmem_ld_wait();
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+    if (p.bias != nullptr) {
+      const uint4* bp = reinterpret_cast<const uint4*>(
+          reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (col0 + q * 8 < p.N) {
+          uint4 b = __ldg(bp + q);
+          const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 f = unpack2(bw[e], p.ab_dtype);
+            v[q * 8 + e * 2] += f.x;
+            v[q * 8 + e * 2 + 1] += f.y;
+          }
+        }
+      }
+    }
+    if (row_ok) {
+      if (p.aux_mode != kAuxNone) {
+        const uint4* ap = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const uint16_t*>(p.aux) + static_cast<int64_t>(row) * p.ldaux +
+            col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (col0 + q * 8 < p.N) {
+            uint4 a = __ldg(ap + q);
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float2 f = unpack2(aw[e], p.ab_dtype);
+              if (p.aux_mode == kAuxAdd) {
+                v[q * 8 + e * 2] += f.x;
+                v[q * 8 + e * 2 + 1] += f.y;
+              } else {
+                v[q * 8 + e * 2] *= gelu_tanh_grad(f.x);
+                v[q * 8 + e * 2 + 1] *= gelu_tanh_grad(f.y);
+              }
+            }
+          }
+        }
+      }
+      if (out_is_f32) {
+        float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.D) +
+                                               static_cast<int64_t>(row) * p.ldd + col0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          if (col0 + q * 4 < p.N) {
+            float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            if (p.accumulate) {
+              float4 old = dp[q];
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            dp[q] = o;
+          }
+        }
+      } else {
+        uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.D) +
+                                             static_cast<int64_t>(row) * p.ldd + col0);
+        uint4* d2p = p.D2 ? reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.D2) +
+                                                     static_cast<int64_t>(row) * p.ldd + col0)
+                          : nullptr;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (col0 + q * 8 < p.N) {
+            if (p.accumulate) {
+              uint4 old = dp[q];
+              const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 f = unpack2(ow[e], p.d_dtype);
+                v[q * 8 + e * 2] += f.x;
+                v[q * 8 + e * 2 + 1] += f.y;
+              }
+            }
+            uint4 o;
+            o.x = pack2(v[q * 8 + 0], v[q * 8 + 1], p.d_dtype);
+            o.y = pack2(v[q * 8 + 2], v[q * 8 + 3], p.d_dtype);
+            o.z = pack2(v[q * 8 + 4], v[q * 8 + 5], p.d_dtype);
+            o.w = pack2(v[q * 8 + 6], v[q * 8 + 7], p.d_dtype);
+            dp[q] = o;
+            if (d2p) {
+              uint4 g;
+              g.x = pack2(gelu_tanh(v[q * 8 + 0]), gelu_tanh(v[q * 8 + 1]), p.ab_dtype);
+              g.y = pack2(gelu_tanh(v[q * 8 + 2]), gelu_tanh(v[q * 8 + 3]), p.ab_dtype);
+              g.z = pack2(gelu_tanh(v[q * 8 + 4]), gelu_tanh(v[q * 8 + 5]), p.ab_dtype);
+              g.w = pack2(gelu_tanh(v[q * 8 + 6]), gelu_tanh(v[q * 8 + 7]), p.ab_dtype);
+              d2p[q] = g;
+            }
+          }
+        }
+      }
+    }
   }
 }
 
@@ -445,7 +564,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     const int row_in_tile = quarter * 32 + lane;
-    const int out_is_f32 = (p.d_dtype == kF32);
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
@@ -457,113 +575,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         ok = false;
       if (!ok) break;
       tc_fence_after();
-      const int row = tm * BM + row_in_tile;
-      const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = tn * BN + c * 32;
-        if (col0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        if (p.bias != nullptr) {
-          const uint4* bp = reinterpret_cast<const uint4*>(
-              reinterpret_cast<const uint16_t*>(p.bias) + col0);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (col0 + q * 8 < p.N) {
-              uint4 b = __ldg(bp + q);
-              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float2 f = unpack2(bw[e], p.ab_dtype);
-                v[q * 8 + e * 2] += f.x;
-                v[q * 8 + e * 2 + 1] += f.y;
-              }
-            }
-          }
-        }
-        if (row_ok) {
-          if (p.aux_mode != kAuxNone) {
-            const uint4* ap = reinterpret_cast<const uint4*>(
-                reinterpret_cast<const uint16_t*>(p.aux) + static_cast<int64_t>(row) * p.ldaux +
-                col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (col0 + q * 8 < p.N) {
-                uint4 a = __ldg(ap + q);
-                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float2 f = unpack2(aw[e], p.ab_dtype);
-                  if (p.aux_mode == kAuxAdd) {
-                    v[q * 8 + e * 2] += f.x;
-                    v[q * 8 + e * 2 + 1] += f.y;
-                  } else {
-                    v[q * 8 + e * 2] *= gelu_tanh_grad(f.x);
-                    v[q * 8 + e * 2 + 1] *= gelu_tanh_grad(f.y);
-                  }
-                }
-              }
-            }
-          }
-          if (out_is_f32) {
-            float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.D) +
-                                                   static_cast<int64_t>(row) * p.ldd + col0);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              if (col0 + q * 4 < p.N) {
-                float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                if (p.accumulate) {
-                  float4 old = dp[q];
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                dp[q] = o;
-              }
-            }
-          } else {
-            uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.D) +
-                                                 static_cast<int64_t>(row) * p.ldd + col0);
-            uint4* d2p = p.D2 ? reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.D2) +
-                                                         static_cast<int64_t>(row) * p.ldd + col0)
-                              : nullptr;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (col0 + q * 8 < p.N) {
-                if (p.accumulate) {
-                  uint4 old = dp[q];
-                  const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    float2 f = unpack2(ow[e], p.d_dtype);
-                    v[q * 8 + e * 2] += f.x;
-                    v[q * 8 + e * 2 + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack2(v[q * 8 + 0], v[q * 8 + 1], p.d_dtype);
-                o.y = pack2(v[q * 8 + 2], v[q * 8 + 3], p.d_dtype);
-                o.z = pack2(v[q * 8 + 4], v[q * 8 + 5], p.d_dtype);
-                o.w = pack2(v[q * 8 + 6], v[q * 8 + 7], p.d_dtype);
-                dp[q] = o;
-                if (d2p) {
-                  uint4 g;
-                  g.x = pack2(gelu_tanh(v[q * 8 + 0]), gelu_tanh(v[q * 8 + 1]), p.ab_dtype);
-                  g.y = pack2(gelu_tanh(v[q * 8 + 2]), gelu_tanh(v[q * 8 + 3]), p.ab_dtype);
-                  g.z = pack2(gelu_tanh(v[q * 8 + 4]), gelu_tanh(v[q * 8 + 5]), p.ab_dtype);
-                  g.w = pack2(gelu_tanh(v[q * 8 + 6]), gelu_tanh(v[q * 8 + 7]), p.ab_dtype);
-                  d2p[q] = g;
-                }
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<BN>(p, taddr, tm * BM + row_in_tile, tn * BN);
       tc_fence_before();
       mbar_arrive(&bars->tmem_empty[acc]);
     }
@@ -574,6 +587,180 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs computes one 256 x BN tile. Each CTA loads its own 128
+// rows of A and its own half (BN/2 rows) of the B tile, so every byte of B is fetched from L2 once
+// per pair instead of once per CTA; the even CTA issues `tcgen05.mma.cta_group::2` (M = 256), which
+// reads both CTAs' shared memory and writes 128 accumulator rows into each CTA's TMEM. Barriers:
+//   full[s]       leader only; transaction bytes of both CTAs' loads
+//   empty[s]      in both CTAs; signalled by the leader's multicast commit
+//   tmem_full[a]  in both CTAs; multicast commit after the last k-block
+//   tmem_empty[a] leader only; all 256 epilogue threads of the pair arrive on it
+// ------------------------------------------------------------------------------------------
+template <int BN> struct PairCfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = (BN / 2) * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 6 : 8;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
+                         const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
+  using C = PairCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kStages * C::kStageBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();      // 0 = leader, 1 = peer
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 2 * kEpiThreads);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tma_a);
+    prefetch_tmap(&tma_b);
+  }
+  if (warp == 1) tmem_alloc_pair(&bars->tmem_base, C::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * 2 * BM + static_cast<int>(cta) * BM;
+        const int n0 = tn * BN + static_cast<int>(cta) * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          if (cta == 0) mbar_expect_tx(&bars->full[stage], 2 * C::kStageBytes);
+          const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[stage]), 0);
+          if (!p.a_mn) {
+            tma_load_2d_pair(sa, &tma_a, full_leader, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d_pair(sa + j * 8192, &tma_a, full_leader, m0 + j * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(sb, &tma_b, full_leader, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              tma_load_2d_pair(sb + j * 8192, &tma_b, full_leader, n0 + j * 64, kb * BK);
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      // Every load issued above has been consumed once the slots it used are free again; wait for
+      // that so that no commit arrives in this CTA's shared memory after it has exited.
+      for (int i = 0; i < C::kStages && ok; ++i) {
+        if (!mbar_wait(&bars->empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) ok = false;
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (cta == 0 && elect_one()) {
+      const uint32_t idesc = make_idesc_f16(p.ab_dtype == kBF16 ? 1 : 0, p.a_mn, p.b_mn, 2 * BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase, p.status, kStatusTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = p.a_mn ? make_smem_desc_sw128(sa + k * 2048, 8192, 1024)
+                                       : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = p.b_mn ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
+                                       : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            tc_mma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(&bars->empty[stage], 3);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit_pair(&bars->tmem_full[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    int it = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      epilogue_tile<BN>(p, taddr, tm * 2 * BM + static_cast<int>(cta) * BM + row_in_tile, tn * BN);
+      tc_fence_before();
+      mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
+    }
+  }
+
+  // Neither CTA may free its TMEM or exit while its partner can still touch its shared memory,
+  // barriers or accumulators.
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
 }
 
@@ -672,6 +859,82 @@ cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// How many CTA pairs the device can keep resident at once (a pair needs two SMs of one
+// cluster-capable group; parts with an odd number of usable SMs per group fit fewer than SMs / 2).
+template <int BN>
+int resident_pairs() {
+  static int pairs = -1;
+  if (pairs >= 0) return pairs;
+  using C = PairCfg<BN>;
+  if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           C::kSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return pairs = 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (device_sm_count() / 2));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<BN>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  const int cap = device_sm_count() / 2;
+  return pairs = (n < cap ? n : cap);
+}
+
+template <int BN>
+cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
+  using C = PairCfg<BN>;
+  CUtensorMap ta, tb;
+  cudaError_t e;
+  if (!a.a_mn)
+    e = make_tmap_2d_16bit(&ta, a.A, a.ab_dtype, a.K, a.M, a.lda, BK, BM);
+  else
+    e = make_tmap_2d_16bit(&ta, a.A, a.ab_dtype, a.M, a.K, a.lda, 64, BK);
+  if (e != cudaSuccess) return e;
+  if (!a.b_mn)
+    e = make_tmap_2d_16bit(&tb, a.B, a.ab_dtype, a.K, a.N, a.ldb, BK, BN / 2);
+  else
+    e = make_tmap_2d_16bit(&tb, a.B, a.ab_dtype, a.N, a.K, a.ldb, 64, BK);
+  if (e != cudaSuccess) return e;
+  static bool attr_set = false;
+  if (!attr_set) {
+    e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int tiles = ((a.M + 2 * BM - 1) / (2 * BM)) * ((a.N + BN - 1) / BN);
+  const int max_pairs = a.sm_count > 0 ? (a.sm_count / 2 < resident_pairs<BN>() ? a.sm_count / 2 : resident_pairs<BN>())
+                                       : resident_pairs<BN>();
+  if (max_pairs <= 0) return cudaErrorLaunchOutOfResources;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<BN>, ta, tb, a);
+  count_launch();
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t gemm_tcgen05(const GemmArgs& a, cudaStream_t stream) {
@@ -684,6 +947,14 @@ cudaError_t gemm_tcgen05(const GemmArgs& a, cudaStream_t stream) {
     ETHB_RETURN_IF(a.d_dtype != a.ab_dtype || a.accumulate || a.D2 != nullptr || a.aux_mode == kAuxGeluGrad,
                    cudaErrorInvalidValue, "fused all-reduce: unsupported epilogue");
   }
+  const int variant = g_gemm_variant.load();
+  if (a.comm.world <= 1 && variant >= 3) return variant == 3 ? launch_pair<128>(a, stream) : launch_pair<256>(a, stream);
+  if (variant == 1) return launch<128>(a, stream);
+  if (variant == 2 && a.N > 128) return launch<256>(a, stream);
+  // Plain GEMMs wider than one 128-column tile run on CTA pairs (256 x 256 tiles): measured faster
+  // than either single-CTA tile on every shape of the GPT layers.
+  if (variant == 0 && a.comm.world <= 1 && a.N > 128 && a.M > 128 && resident_pairs<256>() > 0)
+    return launch_pair<256>(a, stream);
   // Pick the tile width that minimises (waves x cost per wave).
   const int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
   const int tm = (a.M + BM - 1) / BM;

@@ -40,6 +40,29 @@ def test_gemm_layouts(dtype, shape, a_mn, b_mn):
     native.check_status()
 
 
+@pytest.mark.parametrize("variant", [3, 4])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [(512, 512, 256), (1000, 776, 136), (128, 256, 64), (2304, 1536, 1024)])
+def test_gemm_cta_pair_variants(variant, a_mn, b_mn, shape):
+    """The two-CTA (256-row) kernels against fp32 matmul, all operand layouts, ragged edges."""
+    M, N, K = shape
+    torch.manual_seed(5)
+    dtype = torch.bfloat16
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=dtype)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=dtype)
+    bias = torch.randn(N, device=DEV, dtype=dtype)
+    native.lib().set_gemm_variant(variant)
+    try:
+        out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias)
+        again = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias)
+    finally:
+        native.lib().set_gemm_variant(0)
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float() + bias.float()
+    assert _rel_err(out, ref) < 5e-3
+    assert torch.equal(out, again)
+    native.check_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_gemm_epilogues(dtype):
     torch.manual_seed(1)
