@@ -206,26 +206,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const uint32_t idesc_qk = make_idesc_f16(fmt, 0, 0, 128, 128);
       const uint32_t idesc_pv = make_idesc_f16(fmt, 0, 1, 128, D);
       bool ok = mbar_wait(&bars->q_full, 0, p.status, kStatusTimeoutFull);
+      // One thread issues every MMA, so the issue path is kept short: descriptors of the tile
+      // origins are built once, each MMA only adds a constant to them.
+      const uint64_t dq0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dk0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);
+      const uint64_t dv0 = make_smem_desc_sw128(smem_u32(sKV + C::kKBytes), 16384, 1024);
       auto issue_qk = [&](int t, int stage) {
-        const uint32_t sq = smem_u32(sQ + t * C::kHalves * 16384);
-        const uint32_t sk = smem_u32(sKV + stage * C::kStageBytes);
+        const uint64_t dq = desc_advance(dq0, t * C::kHalves * 16384);
+        const uint64_t dk = desc_advance(dk0, stage * C::kStageBytes);
 #pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + t * 128,
-                       make_smem_desc_sw128(sq + h * 16384 + k * 32, 16, 1024),
-                       make_smem_desc_sw128(sk + h * 16384 + k * 32, 16, 1024), idesc_qk,
-                       (h | k) != 0 ? 1u : 0u);
+            tc_mma_f16(tmem_base + t * 128, desc_advance(dq, h * 16384 + k * 32),
+                       desc_advance(dk, h * 16384 + k * 32), idesc_qk, (h | k) != 0 ? 1u : 0u);
         tc_commit(&bars->s_full[t]);
       };
       auto issue_pv = [&](int t, int stage, int j) {
-        const uint32_t sv = smem_u32(sKV + stage * C::kStageBytes + C::kKBytes);
+        const uint64_t dv = desc_advance(dv0, stage * C::kStageBytes);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           tc_mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
-                        make_smem_desc_sw128(sv + k * 2048, 16384, 1024), idesc_pv,
-                        (j | k) != 0 ? 1u : 0u);
+                        desc_advance(dv, k * 2048), idesc_pv, (j | k) != 0 ? 1u : 0u);
         tc_commit(&bars->o_done[t]);
       };
       if (ok && n > 0) {
@@ -556,27 +558,28 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       const int fmt = p.dtype == kBF16 ? 1 : 0;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, 128, 64);
       const uint32_t idesc_acc = make_idesc_f16(fmt, 0, 1, 128, D);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      // One thread issues every MMA and the score MMAs are short (N = 64), so the issue path must
+      // stay short too: tile-origin descriptors are built once, each MMA adds a constant.
+      const uint64_t dK0 = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t dV0 = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
+      const uint64_t dQk0 = make_smem_desc_sw128(smem_u32(sStage), 16, 1024);          // K-major view
+      const uint64_t dQm0 = make_smem_desc_sw128(smem_u32(sStage), 16384, 1024);       // MN-major view
       auto issue_sdp = [&](int u) {
         const int stage = (u >> 1) & 1, sub = u & 1, b = u & 1;
-        const uint32_t aQ = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
-        const uint32_t aDO = aQ + C::kTileBytes;
+        const uint64_t dQ = desc_advance(dQk0, stage * C::kStageBytes + sub * 8192);
+        const uint64_t dDO = desc_advance(dQ, C::kTileBytes);
 #pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + b * 128,
-                       make_smem_desc_sw128(aK + h * 16384 + k * 32, 16, 1024),
-                       make_smem_desc_sw128(aQ + h * 16384 + k * 32, 16, 1024), idesc_s,
-                       (h | k) != 0 ? 1u : 0u);
+            tc_mma_f16(tmem_base + b * 128, desc_advance(dK0, h * 16384 + k * 32),
+                       desc_advance(dQ, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + b * 128 + 64,
-                       make_smem_desc_sw128(aV + h * 16384 + k * 32, 16, 1024),
-                       make_smem_desc_sw128(aDO + h * 16384 + k * 32, 16, 1024), idesc_s,
-                       (h | k) != 0 ? 1u : 0u);
+            tc_mma_f16(tmem_base + b * 128 + 64, desc_advance(dV0, h * 16384 + k * 32),
+                       desc_advance(dDO, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
         tc_commit(&bars->s_full[b]);
       };
       bool ok = mbar_wait(&bars->res_full, 0, p.status, kStatusTimeoutFull);
@@ -590,18 +593,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         ok = mbar_wait(&bars->p_full[b], (u >> 1) & 1, p.status, kStatusTimeoutTmemFull);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
-        const uint32_t aDO = aQ + C::kTileBytes;
+        const uint64_t dQ = desc_advance(dQm0, stage * C::kStageBytes + sub * 8192);
+        const uint64_t dDO = desc_advance(dQ, C::kTileBytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // dV += P^T dO
-          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + k * 8,
-                        make_smem_desc_sw128(aDO + k * 2048, 16384, 1024), idesc_acc,
-                        (u | k) != 0 ? 1u : 0u);
+          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + k * 8, desc_advance(dDO, k * 2048),
+                        idesc_acc, (u | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // dK += dS^T Q
-          tc_mma_f16_ts(tmem_base + 384, tmem_base + b * 128 + 64 + k * 8,
-                        make_smem_desc_sw128(aQ + k * 2048, 16384, 1024), idesc_acc,
-                        (u | k) != 0 ? 1u : 0u);
+          tc_mma_f16_ts(tmem_base + 384, tmem_base + b * 128 + 64 + k * 8, desc_advance(dQ, k * 2048),
+                        idesc_acc, (u | k) != 0 ? 1u : 0u);
         if (sub == 1) tc_commit(&bars->st_empty[stage]);
         if (u + 2 < U) {
           const int u2 = u + 2;
@@ -783,27 +784,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       const int fmt = p.dtype == kBF16 ? 1 : 0;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, 128, 64);
       const uint32_t idesc_acc = make_idesc_f16(fmt, 0, 1, 128, D);
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      // short issue path: tile-origin descriptors once, constants added per MMA
+      const uint64_t dQ0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dDO0 = make_smem_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t dKk0 = make_smem_desc_sw128(smem_u32(sStage), 16, 1024);          // K-major view
+      const uint64_t dKm0 = make_smem_desc_sw128(smem_u32(sStage), 16384, 1024);       // MN-major view
       auto issue_sdp = [&](int u) {
         const int stage = (u >> 1) & 1, sub = u & 1, b = u & 1;
-        const uint32_t aK = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
-        const uint32_t aV = aK + C::kTileBytes;
+        const uint64_t dK = desc_advance(dKk0, stage * C::kStageBytes + sub * 8192);
+        const uint64_t dV = desc_advance(dK, C::kTileBytes);
 #pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + b * 128,
-                       make_smem_desc_sw128(aQ + h * 16384 + k * 32, 16, 1024),
-                       make_smem_desc_sw128(aK + h * 16384 + k * 32, 16, 1024), idesc_s,
-                       (h | k) != 0 ? 1u : 0u);
+            tc_mma_f16(tmem_base + b * 128, desc_advance(dQ0, h * 16384 + k * 32),
+                       desc_advance(dK, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + b * 128 + 64,
-                       make_smem_desc_sw128(aDO + h * 16384 + k * 32, 16, 1024),
-                       make_smem_desc_sw128(aV + h * 16384 + k * 32, 16, 1024), idesc_s,
-                       (h | k) != 0 ? 1u : 0u);
+            tc_mma_f16(tmem_base + b * 128 + 64, desc_advance(dDO0, h * 16384 + k * 32),
+                       desc_advance(dV, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
         tc_commit(&bars->s_full[b]);
       };
       bool ok = mbar_wait(&bars->res_full, 0, p.status, kStatusTimeoutFull);
@@ -817,12 +818,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         ok = mbar_wait(&bars->p_full[b], (u >> 1) & 1, p.status, kStatusTimeoutTmemFull);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t aK = smem_u32(sStage + stage * C::kStageBytes) + sub * 8192;
+        const uint64_t dK = desc_advance(dKm0, stage * C::kStageBytes + sub * 8192);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // dQ += dS K
-          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + 64 + k * 8,
-                        make_smem_desc_sw128(aK + k * 2048, 16384, 1024), idesc_acc,
-                        (u | k) != 0 ? 1u : 0u);
+          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + 64 + k * 8, desc_advance(dK, k * 2048),
+                        idesc_acc, (u | k) != 0 ? 1u : 0u);
         if (sub == 1) tc_commit(&bars->st_empty[stage]);
         if (u + 2 < U) {
           const int u2 = u + 2;

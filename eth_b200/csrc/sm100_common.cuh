@@ -283,6 +283,11 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
 
 // Instruction descriptor for kind::f16, fp32 accumulation.
 //   ab_fmt: 0 = fp16, 1 = bf16.  a_mn / b_mn: 1 if the operand is MN-major in shared memory.
+// Descriptor of the same tile `byte_offset` bytes further into shared memory (the start-address
+// field counts 16-byte units; shared memory is smaller than the field, so no carry can leave it).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t byte_offset) {
+  return desc + static_cast<uint64_t>(byte_offset >> 4);
+}
 __host__ __device__ __forceinline__ uint32_t make_idesc_f16(int ab_fmt, int a_mn, int b_mn, int m,
                                                             int n) {
   uint32_t d = 0;
