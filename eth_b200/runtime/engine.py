@@ -292,6 +292,20 @@ class TrainEngine:
         self.last_stats = stats
         return stats
 
+    def eval_step(self) -> None:
+        """Forward-only pass over one global batch with dropout disabled; accumulates the masked loss
+        sum and weight into `loss_acc` (read them with `reduced_loss`). Gradients, optimizer state,
+        the data cursor and the iteration counter are left untouched."""
+        cfg = self.stage.cfg
+        saved = cfg.hidden_dropout
+        cfg.hidden_dropout = 0.0
+        try:
+            self.loss_acc.zero_()
+            schedules.forward_only(self, self.pstate.num_microbatches)
+            self.coll.all_reduce_sum(self.loss_acc)
+        finally:
+            cfg.hidden_dropout = saved
+
     def _evidence(self, phase, out_dir, **metrics):
         from ..parallel.grad_sync.evidence import snapshot_rank
         snapshot_rank(self, phase, self.iteration + 1, out_dir, metrics)

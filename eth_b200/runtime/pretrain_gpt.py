@@ -9,6 +9,7 @@ iteration, and write the per-rank CSV summary.
 from __future__ import annotations
 
 import csv
+import math
 import json
 import os
 import sys
@@ -81,6 +82,24 @@ def write_rank_csv(engine, rows):
             w.writerow(list(r) + [f"{mem:.1f}", f"{res:.1f}"])
 
 
+def evaluate(engine, eval_iters: int):
+    """Mean masked LM loss and perplexity over `eval_iters` forward-only global batches
+    (reference: eth/runtime/megatron/training.py:1399-1475). Evaluation batches are drawn after the
+    training cursor without advancing it."""
+    total, weight = 0.0, 0.0
+    cursor = engine.clock.global_data_cursor
+    try:
+        for _ in range(eval_iters):
+            engine.eval_step()
+            s, w = engine.loss_acc.tolist()
+            total, weight = total + s, weight + w
+            engine.clock.global_data_cursor += engine.clock.total_gbs
+    finally:
+        engine.clock.global_data_cursor = cursor
+    loss = total / weight if weight > 0 else float("nan")
+    return {"lm loss": loss, "lm loss ppl": math.exp(min(20.0, loss)) if loss == loss else float("nan")}
+
+
 def pretrain(argv=None):
     args = parse_args(argv)
     device = initialize_distributed(args)
@@ -114,6 +133,10 @@ def pretrain(argv=None):
         if stats["iteration"] % args.log_interval == 0:
             loss, tps = training_log(engine, stats, ms, total_ms, log_state)
             rows.append((stats["iteration"], f"{ms:.2f}", f"{tps:.1f}", f"{loss:.6f}", stats["grad_norm"]))
+        if args.eval_iters and args.eval_interval and engine.iteration % args.eval_interval == 0:
+            res = evaluate(engine, args.eval_iters)
+            print_rank_0(f" validation loss at iteration {engine.iteration} | lm loss value: {res['lm loss']:.6E} | "
+                         f"lm loss PPL: {res['lm loss ppl']:.6E}")
         if args.save and args.save_interval and engine.iteration % args.save_interval == 0:
             save_checkpoint(engine, engine.iteration, args.save)
         if args.exit_interval and engine.iteration % args.exit_interval == 0:

@@ -38,3 +38,15 @@ def forward_backward_1f1b(engine, num_microbatches: int) -> None:
         gin = engine.backward_step(steady + i, grads)
         comm.send_backward(gin)
     del t
+
+
+def forward_only(engine, num_microbatches: int) -> None:
+    """Evaluation pass: forwards only, activations dropped at once (reference: schedules.py
+    `forward_only=True` branches of the same schedules)."""
+    ps, comm = engine.pstate, engine.comm
+    for i in range(num_microbatches):
+        inputs = comm.recv_forward() if ps.num_stages > 1 else None
+        out = engine.forward_step(i, inputs)
+        engine.stage.drop_context(i)
+        if ps.num_stages > 1:
+            comm.send_forward(out)
