@@ -130,17 +130,24 @@ void layernorm_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Ten
                             static_cast<float>(eps), dtype_code(x), cur_stream()),
         "layernorm_fwd");
 }
-int64_t ln_bwd_parts(int64_t rows) { return ethb::ln_bwd_parts(static_cast<int>(rows)); }
+int64_t ln_bwd_parts(int64_t rows, int64_t hidden, bool fp32) {
+  return ethb::ln_bwd_parts(static_cast<int>(rows), static_cast<int>(hidden), fp32 ? 0 : 2);
+}
 void layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const Tensor& mean,
                    const Tensor& rstd, Tensor& dx, Tensor& dgamma, Tensor& dbeta, Tensor& ws,
-                   bool accumulate) {
+                   bool accumulate, const c10::optional<Tensor>& dres) {
   c10::cuda::CUDAGuard guard(x.device());
   const int hidden = static_cast<int>(x.size(-1));
   const int rows = static_cast<int>(x.numel() / hidden);
-  TORCH_CHECK(ws.numel() >= 2LL * ethb::ln_bwd_parts(rows) * hidden, "ln workspace too small");
+  TORCH_CHECK(ws.numel() >= 2LL * ethb::ln_bwd_parts(rows, hidden, dtype_code(x)) * hidden, "ln workspace too small");
   TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous());
+  const void* res = nullptr;
+  if (dres.has_value()) {
+    TORCH_CHECK(dres->is_contiguous() && dres->numel() == x.numel() && dres->scalar_type() == x.scalar_type());
+    res = dres->data_ptr();
+  }
   check(ethb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr<float>(),
-                            rstd.data_ptr<float>(), dx.data_ptr(), dgamma.data_ptr(),
+                            rstd.data_ptr<float>(), res, dx.data_ptr(), dgamma.data_ptr(),
                             dbeta.data_ptr(), ws.data_ptr<float>(), rows, hidden, dtype_code(x),
                             dtype_code(dgamma), accumulate, cur_stream()),
         "layernorm_bwd");
@@ -174,6 +181,24 @@ void dropout_bwd(const Tensor& dy, Tensor& dx, double p, int64_t seed, int64_t o
                           static_cast<float>(p), static_cast<uint64_t>(seed),
                           static_cast<uint64_t>(offset), dtype_code(dy), cur_stream()),
         "dropout_bwd");
+}
+int64_t dropout_bwd_colsum_parts(int64_t rows, int64_t cols, bool fp32) {
+  return ethb::dropout_bwd_colsum_parts(rows, static_cast<int>(cols), fp32 ? 0 : 2);
+}
+void dropout_bwd_colsum(const Tensor& dy, Tensor& dx, Tensor& bias_grad, Tensor& ws, double p, int64_t seed,
+                        int64_t offset, bool accumulate) {
+  c10::cuda::CUDAGuard guard(dy.device());
+  const int cols = static_cast<int>(dy.size(-1));
+  const int64_t rows = dy.numel() / cols;
+  TORCH_CHECK(dy.is_contiguous() && dx.is_contiguous() && bias_grad.numel() == cols);
+  const int parts = ethb::dropout_bwd_colsum_parts(rows, cols, dtype_code(dy));
+  TORCH_CHECK(parts > 0, "dropout_bwd_colsum: unsupported shape");
+  TORCH_CHECK(ws.numel() >= static_cast<int64_t>(parts) * cols, "dropout_bwd_colsum workspace too small");
+  check(ethb::dropout_bwd_colsum(dy.data_ptr(), dx.data_ptr(), bias_grad.data_ptr(), ws.data_ptr<float>(), rows,
+                                 cols, static_cast<float>(p), static_cast<uint64_t>(seed),
+                                 static_cast<uint64_t>(offset), dtype_code(dy), dtype_code(bias_grad),
+                                 accumulate, cur_stream()),
+        "dropout_bwd_colsum");
 }
 int64_t colsum_parts(int64_t rows) { return ethb::colsum_parts(rows); }
 void colsum(const Tensor& x, Tensor& out, Tensor& ws, bool accumulate) {
@@ -426,12 +451,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("ln_bwd_parts", &ln_bwd_parts);
-  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"),
+        py::arg("rstd"), py::arg("dx"), py::arg("dgamma"), py::arg("dbeta"), py::arg("ws"), py::arg("accumulate"),
+        py::arg("dres") = py::none());
   m.def("bias_gelu_fwd", &bias_gelu_fwd);
   m.def("bias_gelu_bwd", &bias_gelu_bwd);
   m.def("bias_dropout_add_fwd", &bias_dropout_add_fwd);
   m.def("dropout_bwd", &dropout_bwd);
   m.def("colsum_parts", &colsum_parts);
+  m.def("dropout_bwd_colsum_parts", &dropout_bwd_colsum_parts);
+  m.def("dropout_bwd_colsum", &dropout_bwd_colsum);
   m.def("colsum", &colsum);
   m.def("softmax_fwd", &softmax_fwd);
   m.def("softmax_bwd", &softmax_bwd);

@@ -40,6 +40,20 @@ __device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
   }
 }
 
+// 8 packed 16-bit values held in a register quad -> floats (the fused LayerNorm backward keeps rows
+// packed between its two phases). Only meaningful for 16-bit T.
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    const T* h = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = HalfTraits<T>::to_f(h[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -129,7 +143,103 @@ __global__ void ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gam
   }
 }
 
-// Backward, two kernels.
+// Backward. One pass over dy and x: thread t of a CTA owns columns [8t, 8t + 8) of every row the CTA
+// visits (blockDim.x = hidden / 8), so the dgamma / dbeta column sums stay in registers for the
+// whole kernel and dx needs only two block-wide reductions per batch of R rows (sum(dy*gamma) and
+// sum(dy*gamma*xhat) of each row). A CTA keeps its R rows as packed 16-bit registers between the
+// reduction and the dx pass. Each CTA writes one slab of partial column sums; reduce_parts_kernel
+// adds the slabs. Rows wider than 8192 elements use the two-kernel fallback below.
+template <typename T, int R>
+__global__ void __launch_bounds__(R == 4 ? 512 : 1024, R == 4 ? 2 : 1)
+ln_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                    const float* __restrict__ mean, const float* __restrict__ rstd,
+                    const T* __restrict__ dres, T* __restrict__ dx, float* __restrict__ ws, int rows,
+                    int hidden) {
+  __shared__ float red[2][R][32];
+  __shared__ float tot[2][R];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
+  const int c0 = t * 8;
+  float g[8];
+  load8(gamma + c0, g);
+  float dg[8] = {0, 0, 0, 0, 0, 0, 0, 0}, db[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int r0 = blockIdx.x * R; r0 < rows; r0 += gridDim.x * R) {
+    uint4 xr[R], dyr[R];
+    float mu[R], rs[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = r0 + i;
+      if (r < rows) {
+        xr[i] = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(r) * hidden + c0);
+        dyr[i] = *reinterpret_cast<const uint4*>(dy + static_cast<int64_t>(r) * hidden + c0);
+        mu[i] = mean[r];
+        rs[i] = rstd[r];
+      } else {
+        xr[i] = make_uint4(0, 0, 0, 0);
+        dyr[i] = make_uint4(0, 0, 0, 0);
+        mu[i] = 0.f;
+        rs[i] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      float xv[8], dv[8];
+      unpack8<T>(xr[i], xv);
+      unpack8<T>(dyr[i], dv);
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float w = dv[j] * g[j];
+        s1 += w;
+        s2 += w * (xv[j] - mu[i]) * rs[i];
+      }
+      s1 = warp_sum(s1);
+      s2 = warp_sum(s2);
+      if (lane == 0) {
+        red[0][i][warp] = s1;
+        red[1][i][warp] = s2;
+      }
+    }
+    __syncthreads();
+    if (t < 2 * R) {
+      const int which = t / R, i = t % R;
+      float a = 0.f;
+      for (int w = 0; w < nwarps; ++w) a += red[which][i][w];
+      tot[which][i] = a / hidden;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = r0 + i;
+      if (r >= rows) break;
+      float xv[8], dv[8], o[8];
+      unpack8<T>(xr[i], xv);
+      unpack8<T>(dyr[i], dv);
+      const float m1 = tot[0][i], m2 = tot[1][i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (xv[j] - mu[i]) * rs[i];
+        o[j] = (dv[j] * g[j] - m1 - xh * m2) * rs[i];
+        dg[j] += dv[j] * xh;
+        db[j] += dv[j];
+      }
+      if (dres != nullptr) {   // gradient arriving through the residual branch
+        float rv[8];
+        load8(dres + static_cast<int64_t>(r) * hidden + c0, rv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += rv[j];
+      }
+      store8(dx + static_cast<int64_t>(r) * hidden + c0, o);
+    }
+  }
+  float* wg = ws + static_cast<int64_t>(blockIdx.x) * hidden + c0;
+  float* wb = ws + static_cast<int64_t>(gridDim.x + blockIdx.x) * hidden + c0;
+  *reinterpret_cast<float4*>(wg) = make_float4(dg[0], dg[1], dg[2], dg[3]);
+  *reinterpret_cast<float4*>(wg + 4) = make_float4(dg[4], dg[5], dg[6], dg[7]);
+  *reinterpret_cast<float4*>(wb) = make_float4(db[0], db[1], db[2], db[3]);
+  *reinterpret_cast<float4*>(wb + 4) = make_float4(db[4], db[5], db[6], db[7]);
+}
+
+// Fallback for very wide rows, two kernels.
 //  (1) dx: one warp per row, no block-level synchronisation. Two passes over the row: the first
 //      accumulates sum(dy*gamma) and sum(dy*gamma*xhat), the second recomputes the terms (the row is
 //      L1/L2 resident by then) and writes dx.
@@ -139,8 +249,8 @@ __global__ void ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gam
 template <typename T>
 __global__ void ln_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                  const T* __restrict__ gamma, const float* __restrict__ mean,
-                                 const float* __restrict__ rstd, T* __restrict__ dx, int rows,
-                                 int hidden) {
+                                 const float* __restrict__ rstd, const T* __restrict__ dres,
+                                 T* __restrict__ dx, int rows, int hidden) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int nvec = hidden >> 3;
@@ -170,6 +280,12 @@ __global__ void ln_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__
       load8(gamma + c * 8, g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = (dyv[j] * g[j] - m1 - (xv[j] - mu) * rs * m2) * rs;
+      if (dres != nullptr) {
+        float rv[8];
+        load8(dres + off + c * 8, rv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += rv[j];
+      }
       store8(dx + off + c * 8, o);
     }
   }
@@ -217,15 +333,27 @@ __global__ void ln_bwd_param_kernel(const T* __restrict__ dy, const T* __restric
 }
 
 // out[c] (+)= sum_p ws[p, c]   for two stacked workspaces (dgamma | dbeta) or one (colsum).
+// CTA = 32 columns x 8 part-lanes: each thread adds every 8th slab, shared memory adds the lanes.
 template <typename G>
 __global__ void reduce_parts_kernel(const float* __restrict__ ws, G* __restrict__ out0,
                                     G* __restrict__ out1, int parts, int cols, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float sa[8][33], sb[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
-  for (int p = 0; p < parts; ++p) {
-    a += ws[static_cast<int64_t>(p) * cols + c];
-    if (out1) b += ws[static_cast<int64_t>(parts + p) * cols + c];
+  if (c < cols) {
+    for (int p = threadIdx.y; p < parts; p += 8) {
+      a += ws[static_cast<int64_t>(p) * cols + c];
+      if (out1) b += ws[static_cast<int64_t>(parts + p) * cols + c];
+    }
+  }
+  sa[threadIdx.y][threadIdx.x] = a;
+  sb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y != 0 || c >= cols) return;
+#pragma unroll
+  for (int k = 1; k < 8; ++k) {
+    a += sa[k][threadIdx.x];
+    b += sb[k][threadIdx.x];
   }
   if (accumulate) {
     a += HalfTraits<G>::to_f(out0[c]);
@@ -332,6 +460,44 @@ __global__ void dropout_bwd_kernel(const T* __restrict__ dy, T* __restrict__ dx,
     for (int j = 0; j < 8; ++j) o[j] = keep[j] ? d[j] * inv_keep : 0.f;
     store8(dx + i * 8, o);
   }
+}
+
+// dropout backward fused with the column sums of its result (the bias gradient of the preceding
+// row-parallel GEMM): thread t of a CTA owns columns [8t, 8t + 8) of every row the CTA visits and
+// keeps their sums in registers; one slab of partial sums per CTA, added by reduce_parts_kernel.
+template <typename T>
+__global__ void dropout_bwd_colsum_kernel(const T* __restrict__ dy, T* __restrict__ dx,
+                                          float* __restrict__ ws, int64_t rows, int cols, float p,
+                                          uint64_t seed, uint64_t offset) {
+  const float inv_keep = 1.0f / (1.0f - p);
+  const int cvec = cols >> 3;
+  const int t = threadIdx.x;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  constexpr int U = 4;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * U; r0 < rows; r0 += static_cast<int64_t>(gridDim.x) * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (r0 + u < rows) raw[u] = *reinterpret_cast<const uint4*>(dy + ((r0 + u) * cvec + t) * 8);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (r0 + u >= rows) break;
+      const int64_t i = (r0 + u) * cvec + t;
+      float d[8], o[8];
+      unpack8<T>(raw[u], d);
+      bool keep[8];
+      keep8(seed, offset, i, p, keep);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = keep[j] ? d[j] * inv_keep : 0.f;
+        acc[j] += o[j];
+      }
+      store8(dx + i * 8, o);
+    }
+  }
+  float* w = ws + static_cast<int64_t>(blockIdx.x) * cols + t * 8;
+  *reinterpret_cast<float4*>(w) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  *reinterpret_cast<float4*>(w + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
 // =============================================================================================
@@ -713,7 +879,25 @@ cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, vo
   return cudaGetLastError();
 }
 
-int ln_bwd_parts(int rows) {
+// Rows per batch of the fused backward, chosen so that the packed rows fit the register budget of
+// a CTA of hidden / 8 threads.
+static int ln_bwd_rows_per_batch(int hidden) {
+  const int threads = hidden / 8;
+  return threads <= 512 ? 4 : 2;
+}
+static bool ln_bwd_fused_ok(int hidden, int dtype) {
+  return dtype != kF32 && hidden % 256 == 0 && hidden <= 8192;
+}
+
+int ln_bwd_parts(int rows, int hidden, int dtype) {
+  if (ln_bwd_fused_ok(hidden, dtype)) {
+    const int r = ln_bwd_rows_per_batch(hidden);
+    const int threads = hidden / 8;
+    const int per_sm = threads <= 256 ? 4 : (threads <= 512 ? 2 : 1);
+    int p = (rows + r - 1) / r;
+    if (p > kSMs * per_sm) p = kSMs * per_sm;
+    return p < 1 ? 1 : p;
+  }
   int p = rows / 64;
   if (p < 1) p = 1;
   if (p > 96) p = 96;
@@ -721,25 +905,42 @@ int ln_bwd_parts(int rows) {
 }
 
 cudaError_t layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
-                          const float* rstd, void* dx, void* dgamma, void* dbeta, float* ws,
-                          int rows, int hidden, int dtype, int grad_dtype, int accumulate,
+                          const float* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
+                          float* ws, int rows, int hidden, int dtype, int grad_dtype, int accumulate,
                           cudaStream_t st) {
   if (hidden % 8 != 0 || hidden / 8 > 4 * 1024) return cudaErrorInvalidValue;
-  const int parts = ln_bwd_parts(rows);
+  const int parts = ln_bwd_parts(rows, hidden, dtype);
+  dim3 rgrid((hidden + 31) / 32), rblock(32, 8);
+  if (ln_bwd_fused_ok(hidden, dtype)) {
+    const int threads = hidden / 8;
+    const int r = ln_bwd_rows_per_batch(hidden);
+#define ETHB_LN_BWD(R)                                                                              \
+  ETHB_DISPATCH(dtype, T,                                                                           \
+                (ln_bwd_fused_kernel<T, R><<<parts, threads, 0, st>>>(                              \
+                    (const T*)dy, (const T*)x, (const T*)gamma, mean, rstd, (const T*)dres, (T*)dx, ws, rows, \
+                    hidden)))
+    if (r == 4) { ETHB_LN_BWD(4); } else { ETHB_LN_BWD(2); }
+#undef ETHB_LN_BWD
+    ETHB_DISPATCH(grad_dtype, G,
+                  (reduce_parts_kernel<G><<<rgrid, rblock, 0, st>>>(ws, (G*)dgamma, (G*)dbeta, parts, hidden,
+                                                                    accumulate)));
+    count_launch(2);
+    return cudaGetLastError();
+  }
   const int warps = 4;
   int grid = (rows + warps - 1) / warps;
   if (grid > kSMs * 16) grid = kSMs * 16;
   ETHB_DISPATCH(dtype, T,
                 (ln_bwd_dx_kernel<T><<<grid, warps * 32, 0, st>>>((const T*)dy, (const T*)x, (const T*)gamma,
-                                                                  mean, rstd, (T*)dx, rows, hidden)));
+                                                                  mean, rstd, (const T*)dres, (T*)dx, rows,
+                                                                  hidden)));
   dim3 pgrid((hidden + 255) / 256, parts), pblock(32, 8);
   ETHB_DISPATCH(dtype, T,
                 (ln_bwd_param_kernel<T><<<pgrid, pblock, 0, st>>>((const T*)dy, (const T*)x, mean, rstd, ws,
                                                                   rows, hidden)));
-  const int rthreads = 128;
   ETHB_DISPATCH(grad_dtype, G,
-                (reduce_parts_kernel<G><<<(hidden + rthreads - 1) / rthreads, rthreads, 0, st>>>(
-                    ws, (G*)dgamma, (G*)dbeta, parts, hidden, accumulate)));
+                (reduce_parts_kernel<G><<<rgrid, rblock, 0, st>>>(ws, (G*)dgamma, (G*)dbeta, parts, hidden,
+                                                                  accumulate)));
   count_launch(3);
   return cudaGetLastError();
 }
@@ -788,6 +989,28 @@ cudaError_t dropout_bwd(const void* dy, void* dx, int64_t rows, int cols, float 
   return cudaGetLastError();
 }
 
+int dropout_bwd_colsum_parts(int64_t rows, int cols, int dtype) {
+  if (dtype == kF32 || cols % 256 != 0 || cols > 8192) return 0;   // not fusable: use the separate kernels
+  int64_t p = (rows + 3) / 4;
+  const int cap = kSMs * (cols / 8 <= 256 ? 4 : (cols / 8 <= 512 ? 2 : 1));
+  if (p > cap) p = cap;
+  return static_cast<int>(p < 1 ? 1 : p);
+}
+cudaError_t dropout_bwd_colsum(const void* dy, void* dx, void* bias_grad, float* ws, int64_t rows,
+                               int cols, float p, uint64_t seed, uint64_t offset, int dtype,
+                               int grad_dtype, int accumulate, cudaStream_t st) {
+  const int parts = dropout_bwd_colsum_parts(rows, cols, dtype);
+  if (parts <= 0) return cudaErrorInvalidValue;
+  ETHB_DISPATCH(dtype, T,
+                (dropout_bwd_colsum_kernel<T><<<parts, cols / 8, 0, st>>>((const T*)dy, (T*)dx, ws, rows, cols,
+                                                                         p, seed, offset)));
+  ETHB_DISPATCH(grad_dtype, G,
+                (reduce_parts_kernel<G><<<dim3((cols + 31) / 32), dim3(32, 8), 0, st>>>(
+                    ws, (G*)bias_grad, (G*)nullptr, parts, cols, accumulate)));
+  count_launch(2);
+  return cudaGetLastError();
+}
+
 int colsum_parts(int64_t rows) {
   int64_t p = (rows + 63) / 64;
   if (p > 64) p = 64;
@@ -802,7 +1025,7 @@ cudaError_t colsum(const void* x, void* out, float* ws, int64_t rows, int cols, 
   ETHB_DISPATCH(dtype, T,
                 (colsum_partial_kernel<T><<<grid, block, 0, st>>>((const T*)x, ws, rows, cols)));
   ETHB_DISPATCH(out_dtype, G,
-                (reduce_parts_kernel<G><<<(cols + 127) / 128, 128, 0, st>>>(
+                (reduce_parts_kernel<G><<<dim3((cols + 31) / 32), dim3(32, 8), 0, st>>>(
                     ws, (G*)out, (G*)nullptr, parts, cols, accumulate)));
   count_launch(2);
   return cudaGetLastError();

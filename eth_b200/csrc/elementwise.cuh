@@ -11,11 +11,14 @@ namespace ethb {
 cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
                           float* mean, float* rstd, int rows, int hidden, float eps, int dtype,
                           cudaStream_t st);
-// Workspace: `ws` holds 2 * ln_bwd_parts(rows) * hidden floats (partial dgamma | partial dbeta).
-int ln_bwd_parts(int rows);
+// Workspace: `ws` holds 2 * ln_bwd_parts(rows, hidden, dtype) * hidden floats (partial dgamma |
+// partial dbeta).
+int ln_bwd_parts(int rows, int hidden, int dtype);
+// `dres` (may be null): a gradient of the same shape that is added to dx, i.e. the gradient that
+// reaches the LayerNorm input through the residual branch.
 cudaError_t layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
-                          const float* rstd, void* dx, void* dgamma, void* dbeta, float* ws,
-                          int rows, int hidden, int dtype, int grad_dtype, int accumulate,
+                          const float* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
+                          float* ws, int rows, int hidden, int dtype, int grad_dtype, int accumulate,
                           cudaStream_t st);
 
 // ---- bias + GeLU(tanh) ----------------------------------------------------------------------
@@ -31,6 +34,13 @@ cudaError_t bias_dropout_add_fwd(const void* x, const void* bias, const void* re
                                  int dtype, cudaStream_t st);
 cudaError_t dropout_bwd(const void* dy, void* dx, int64_t rows, int cols, float p, uint64_t seed,
                         uint64_t offset, int dtype, cudaStream_t st);
+// dx = dropout_bwd(dy) and bias_grad (+)= column sums of dx, in one pass over dy. Workspace:
+// dropout_bwd_colsum_parts(rows, cols, dtype) * cols floats; 0 parts means "shape not supported,
+// call dropout_bwd and colsum separately".
+int dropout_bwd_colsum_parts(int64_t rows, int cols, int dtype);
+cudaError_t dropout_bwd_colsum(const void* dy, void* dx, void* bias_grad, float* ws, int64_t rows,
+                               int cols, float p, uint64_t seed, uint64_t offset, int dtype,
+                               int grad_dtype, int accumulate, cudaStream_t st);
 
 // ---- column sums: out[c] (+)= sum_r x[r, c]  (bias gradients) -----------------------------
 // Workspace: colsum_parts(rows) * cols floats.

@@ -221,15 +221,122 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, in
   }
 }
 
+// Epilogue for 16-bit outputs that are only written (no accumulate): the same math as
+// `epilogue_tile`, but rows leave -- and the `aux` operand arrives -- through a per-warp 4 KB
+// shared-memory transpose, so that every global load / store instruction of a warp moves four
+// whole 128-byte row segments instead of 32 scattered 16-byte pieces. `row0` is the first of the
+// warp's 32 rows; columns are handled 64 at a time.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_staged(const GemmArgs& p, uint32_t taddr, int row0,
+                                                     int lane, int n_base, int c_begin, int c_end,
+                                                     uint8_t* warp_buf) {
+  auto slot = [&](int r, int piece) { return warp_buf + r * 128 + ((piece ^ (r & 7)) * 16); };
+#pragma unroll 1
+  for (int cp = c_begin / 2; cp < c_end / 2; ++cp) {
+    const int gc0 = n_base + cp * 64;
+    if (gc0 >= p.N) break;  // uniform across the warp
+    if (p.aux_mode != kAuxNone) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rl = i * 4 + (lane >> 3), piece = lane & 7;
+        const int grow = row0 + rl, gcol = gc0 + piece * 8;
+        uint4 a = make_uint4(0, 0, 0, 0);
+        if (grow < p.M && gcol < p.N)
+          a = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.aux) +
+                                                   static_cast<int64_t>(grow) * p.ldaux + gcol));
+        *reinterpret_cast<uint4*>(slot(rl, piece)) = a;
+      }
+      __syncwarp();
+    }
+    float v[2][32];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int col0 = gc0 + half * 32;
+      uint32_t r[32];
+      __syncwarp();
+      tmem_ld_32x32b_x32(taddr + (cp * 2 + half) * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[half][j] = __uint_as_float(r[j]) * p.alpha;
+      if (p.bias != nullptr) {
+        const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (col0 + q * 8 < p.N) {
+            const uint4 b = __ldg(bp + q);
+            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack2(bw[e], p.ab_dtype);
+              v[half][q * 8 + e * 2] += f.x;
+              v[half][q * 8 + e * 2 + 1] += f.y;
+            }
+          }
+        }
+      }
+      if (p.aux_mode != kAuxNone) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 a = *reinterpret_cast<const uint4*>(slot(lane, half * 4 + q));
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack2(aw[e], p.ab_dtype);
+            if (p.aux_mode == kAuxAdd) {
+              v[half][q * 8 + e * 2] += f.x;
+              v[half][q * 8 + e * 2 + 1] += f.y;
+            } else {
+              v[half][q * 8 + e * 2] *= gelu_tanh_grad(f.x);
+              v[half][q * 8 + e * 2 + 1] *= gelu_tanh_grad(f.y);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      void* out = which == 0 ? p.D : p.D2;
+      if (out == nullptr) break;
+      const int odt = which == 0 ? p.d_dtype : p.ab_dtype;
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) w[e] = which == 0 ? v[half][q * 8 + e] : gelu_tanh(v[half][q * 8 + e]);
+          uint4 o;
+          o.x = pack2(w[0], w[1], odt);
+          o.y = pack2(w[2], w[3], odt);
+          o.z = pack2(w[4], w[5], odt);
+          o.w = pack2(w[6], w[7], odt);
+          *reinterpret_cast<uint4*>(slot(lane, half * 4 + q)) = o;
+        }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rl = i * 4 + (lane >> 3), piece = lane & 7;
+        const int grow = row0 + rl, gcol = gc0 + piece * 8;
+        if (grow < p.M && gcol < p.N)
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + static_cast<int64_t>(grow) * p.ldd + gcol) =
+              *reinterpret_cast<const uint4*>(slot(rl, piece));
+      }
+      __syncwarp();
+    }
+  }
+}
+
 // Drain one 128 x BN accumulator (this thread owns TMEM lane == output row `row`) through the
 // fused epilogue: alpha, bias, residual / GeLU-gradient, accumulate, convert, optional GeLU copy.
-// `n_base` is the first output column of the tile.
+// `n_base` is the first output column of the tile; [c_begin, c_end) selects 32-column chunks of it.
 template <int BN>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& p, uint32_t taddr, int row, int n_base) {
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& p, uint32_t taddr, int row, int n_base,
+                                              int c_begin = 0, int c_end = BN / 32) {
   const bool row_ok = row < p.M;
   const int out_is_f32 = (p.d_dtype == kF32);
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = c_begin; c < c_end; ++c) {
     const int col0 = n_base + c * 32;
     if (col0 >= p.N) break;  // uniform across the warp
     uint32_t r[32];
@@ -598,7 +705,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
 //   full[s]       leader only; transaction bytes of both CTAs' loads
 //   empty[s]      in both CTAs; signalled by the leader's multicast commit
 //   tmem_full[a]  in both CTAs; multicast commit after the last k-block
-//   tmem_empty[a] leader only; all 256 epilogue threads of the pair arrive on it
+//   tmem_empty[a] leader only; all 512 epilogue threads of the pair arrive on it
 // ------------------------------------------------------------------------------------------
 template <int BN> struct PairCfg {
   static constexpr int kABytes = BM * BK * 2;
@@ -606,11 +713,15 @@ template <int BN> struct PairCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 6 : 8;
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kEpiBytes = 8 * 4096;   // per-epilogue-warp 32 x 128 B transpose buffer
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kEpiBytes;
 };
 
+constexpr int kPairThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
+constexpr int kPairEpiThreads = 256;
+
 template <int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kPairThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
                          const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
   using C = PairCfg<BN>;
@@ -636,7 +747,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->tmem_full[a], 1);
-      mbar_init(&bars->tmem_empty[a], 2 * kEpiThreads);
+      mbar_init(&bars->tmem_empty[a], 2 * kPairEpiThreads);
     }
     fence_mbar_init();
     prefetch_tmap(&tma_a);
@@ -734,19 +845,32 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    // A warp may only touch the TMEM lane quarter (warp % 4); two warps share each quarter and
+    // split the tile's columns, which halves the drain time of an accumulator.
     const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;
     const int row_in_tile = quarter * 32 + lane;
+    // The transpose costs shared-memory bandwidth that the MMAs also need, so it is used only where
+    // the direct path is slower: a second output or an `aux` operand.
+    const bool staged = p.d_dtype != kF32 && !p.accumulate && (p.D2 != nullptr || p.aux_mode != kAuxNone);
+    uint8_t* epi_smem = smem + C::kStages * C::kStageBytes + 256;
     int it = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) break;
+      if (!mbar_wait_relaxed(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      epilogue_tile<BN>(p, taddr, tm * 2 * BM + static_cast<int>(cta) * BM + row_in_tile, tn * BN);
+      const int row_base = tm * 2 * BM + static_cast<int>(cta) * BM;
+      if (staged)
+        epilogue_tile_staged<BN>(p, taddr, row_base + quarter * 32, lane, tn * BN, col_half * (BN / 64),
+                                 (col_half + 1) * (BN / 64), epi_smem + (warp - 2) * 4096);
+      else
+        epilogue_tile<BN>(p, taddr, row_base + row_in_tile, tn * BN, col_half * (BN / 64),
+                          (col_half + 1) * (BN / 64));
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
     }
@@ -873,7 +997,7 @@ int resident_pairs() {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * (device_sm_count() / 2));
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kPairThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -920,7 +1044,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kPairThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -102,6 +102,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return true;
 }
 
+// Bounded wait for long waits (an epilogue waiting for a whole tile of MMAs): polls, then sleeps
+// between polls so that the waiting warps do not take issue slots from the producer / MMA warps.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (int i = 0; i < 8; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(128);
+    if ((++spins & 0x3f) == 0) {
+      if (globaltimer_ns() - t0 > ETHB_WAIT_NS) {
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // ----------------------------------------------------------------------------------------
 // TMA
 // ----------------------------------------------------------------------------------------

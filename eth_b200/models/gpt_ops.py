@@ -260,12 +260,9 @@ class LayerNormOp(Op):
 
     def bwd(self, genv, ctx, mb):
         dy = _take(genv, "hidden_states")
-        dx = raw.ln_bwd(dy, ctx["x"], self.p("weight"), self.p("bias"), ctx["mean"], ctx["rstd"])
-        if self.residual_name:
-            res = genv.pop(self.residual_name, None)
-            if res is not None:
-                dx.add_(res)
-        genv["hidden_states"] = dx
+        res = genv.pop(self.residual_name, None) if self.residual_name else None
+        genv["hidden_states"] = raw.ln_bwd(dy, ctx["x"], self.p("weight"), self.p("bias"), ctx["mean"],
+                                           ctx["rstd"], residual_grad=res)
 
 
 class ColumnLinearOp(Op):
@@ -372,10 +369,10 @@ class BiasDropoutAddOp(Op):
 
     def bwd(self, genv, ctx, mb):
         dout = _take(genv, "hidden_states")
-        dx = raw.dropout_bwd(dout, *ctx["drop"])
+        dx, dbias = raw.dropout_bwd_colsum(dout, *ctx["drop"])
         genv["hidden_states"] = dx
         genv[self.residual_name] = dout
-        genv["output_bias"] = raw.colsum(dx, out_dtype=torch.float32)
+        genv["output_bias"] = dbias
 
 
 class GeluOp(Op):

@@ -215,7 +215,7 @@ class _LayerNormFn(torch.autograd.Function):
             else:
                 dg = torch.empty(hidden, dtype=gamma.dtype, device=x.device)
                 db = torch.empty(hidden, dtype=gamma.dtype, device=x.device)
-            parts = native.lib().ln_bwd_parts(rows)
+            parts = native.lib().ln_bwd_parts(rows, hidden, x.dtype == torch.float32)
             ws = _workspace(x.device, 2 * parts * hidden)
             native.lib().layernorm_bwd(dy, x, gamma, mean, rstd, dx, dg, db, ws, fused)
             if fused:

@@ -41,16 +41,19 @@ def ln_fwd(x, gamma, beta, eps):
     return y, mean, rstd
 
 
-def ln_bwd(dy, x, gamma, beta, mean, rstd):
-    """Returns dx; accumulates dgamma / dbeta into the parameters' main_grad."""
+def ln_bwd(dy, x, gamma, beta, mean, rstd, residual_grad=None):
+    """Returns dx (+ `residual_grad`, the gradient reaching the input through the residual branch);
+    accumulates dgamma / dbeta into the parameters' main_grad."""
     hidden = x.shape[-1]
     rows = x.numel() // hidden
     dg, db = _grad_of(gamma).view(-1), _grad_of(beta).view(-1)
     if native.use_native(x):
         dx = torch.empty_like(x)
-        parts = native.lib().ln_bwd_parts(rows)
+        parts = native.lib().ln_bwd_parts(rows, hidden, x.dtype == torch.float32)
+        if residual_grad is not None and not residual_grad.is_contiguous():
+            residual_grad = residual_grad.contiguous()
         native.lib().layernorm_bwd(dy, x, gamma, mean, rstd, dx, dg, db,
-                                   _workspace(x.device, 2 * parts * hidden), True)
+                                   _workspace(x.device, 2 * parts * hidden), True, residual_grad)
         return dx
     xf, dyf = x.float().reshape(rows, hidden), dy.float().reshape(rows, hidden)
     xh = (xf - mean[:, None]) * rstd[:, None]
@@ -59,7 +62,10 @@ def ln_bwd(dy, x, gamma, beta, mean, rstd):
     m2 = (wdy * xh).mean(1, keepdim=True)
     dg.add_((dyf * xh).sum(0).to(dg.dtype))
     db.add_(dyf.sum(0).to(db.dtype))
-    return ((wdy - m1 - xh * m2) * rstd[:, None]).to(x.dtype).reshape(x.shape)
+    dx = ((wdy - m1 - xh * m2) * rstd[:, None]).to(x.dtype).reshape(x.shape)
+    if residual_grad is not None:
+        dx = dx + residual_grad.reshape(x.shape)
+    return dx
 
 
 # ---------------------------------------------------------------------------------- linear
@@ -130,6 +136,23 @@ def dropout_bwd(dy, p, seed, offset):
         return dx
     keep = _keep_mask_ref(dy.shape, p, seed, offset, dy.device)
     return torch.where(keep, dy.float() / (1.0 - p), torch.zeros_like(dy.float())).to(dy.dtype)
+
+
+def dropout_bwd_colsum(dy, p, seed, offset):
+    """(dropout_bwd(dy), fp32 column sums of it): the input gradient of a bias-dropout-add op and the
+    gradient of its bias, in one pass where the fused kernel supports the shape."""
+    cols = dy.shape[-1]
+    if p > 0 and native.use_native(dy) and dy.is_contiguous():
+        rows = dy.numel() // cols
+        parts = native.lib().dropout_bwd_colsum_parts(rows, cols, dy.dtype == torch.float32)
+        if parts > 0:
+            dx = torch.empty_like(dy)
+            bias_grad = torch.empty(cols, dtype=torch.float32, device=dy.device)
+            native.lib().dropout_bwd_colsum(dy, dx, bias_grad, _workspace(dy.device, parts * cols), float(p),
+                                            int(seed), int(offset), False)
+            return dx, bias_grad
+    dx = dropout_bwd(dy, p, seed, offset)
+    return dx, colsum(dx, out_dtype=torch.float32)
 
 
 def add_(a, b):

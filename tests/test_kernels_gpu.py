@@ -304,3 +304,45 @@ def test_synthetic_batch_matches_reference_formula():
     ref = (ids[:, None] * 1103515245 + pos[None] * 12345).remainder(V)
     assert torch.equal(tok, ref)
     assert torch.equal(mask, ((ids[:, None] + pos[None]) % 4 != 0).float())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,hidden", [(777, 2048), (130, 4096), (64, 5120), (1000, 256)])
+def test_layernorm_bwd_with_residual_gradient(dtype, rows, hidden):
+    """Fused LayerNorm backward (dx + residual-branch gradient, dgamma, dbeta) against fp32 autograd."""
+    from eth_b200.ops import raw
+    torch.manual_seed(11)
+    x = torch.randn(rows, hidden, device=DEV, dtype=dtype)
+    g = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(dtype)
+    b = (0.1 * torch.randn(hidden, device=DEV)).to(dtype)
+    g.main_grad = torch.zeros(hidden, device=DEV, dtype=torch.float32)
+    b.main_grad = torch.zeros(hidden, device=DEV, dtype=torch.float32)
+    y, mean, rstd = raw.ln_fwd(x, g, b, 1e-5)
+    dy, res = torch.randn_like(x), torch.randn_like(x)
+    dx = raw.ln_bwd(dy, x, g, b, mean, rstd, residual_grad=res)
+    xr, gr, br = (t.detach().float().requires_grad_(True) for t in (x, g, b))
+    torch.nn.functional.layer_norm(xr, (hidden,), gr, br, 1e-5).backward(dy.float())
+    assert _rel_err(dx, xr.grad + res.float()) < 1e-2
+    assert _rel_err(g.main_grad, gr.grad) < 5e-3
+    assert _rel_err(b.main_grad, br.grad) < 5e-3
+    # a second call accumulates into main_grad
+    raw.ln_bwd(dy, x, g, b, mean, rstd)
+    assert _rel_err(g.main_grad, 2 * gr.grad) < 5e-3
+
+
+@pytest.mark.parametrize("rows,cols", [(8192, 2048), (333, 4096), (50, 256), (64, 264)])
+def test_dropout_bwd_colsum(rows, cols):
+    """dx and its column sums from the fused kernel equal the two separate kernels (same Philox mask)."""
+    from eth_b200.ops import raw
+    torch.manual_seed(12)
+    dy = torch.randn(rows, cols, device=DEV, dtype=torch.bfloat16)
+    p, seed, off = 0.1, 77, 5
+    dx, db = raw.dropout_bwd_colsum(dy, p, seed, off)
+    ref = raw.dropout_bwd(dy, p, seed, off)
+    assert torch.equal(dx, ref)
+    assert db.dtype == torch.float32
+    exact = torch.where(ref != 0, dy.float() / (1.0 - p), torch.zeros_like(dy.float())).sum(0)   # unrounded terms
+    fused = cols % 256 == 0   # otherwise the two separate kernels run and sum the rounded dx
+    assert _rel_err(db, exact) < (1e-5 if fused else 3e-3)
+    zeros = (dx == 0).float().mean().item()
+    assert abs(zeros - p) < 0.02
