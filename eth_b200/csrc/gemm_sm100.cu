@@ -13,7 +13,7 @@
 //              per stage into one of two TMEM accumulators, then tcgen05.commit releases the
 //              stage (`empty[stage]`) and, after the last k-block, publishes the accumulator
 //              (`tmem_full[acc]`).
-//   warps 2-5: epilogue      - tcgen05.ld the accumulator (lane == output row), apply
+//   warps 2-9: epilogue      - tcgen05.ld the accumulator (lane == output row), apply
 //              bias / residual / GeLU / GeLU-grad / accumulate, convert and store. While they
 //              drain accumulator `acc`, the MMA warp already fills `acc ^ 1`.
 //
@@ -53,8 +53,9 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;          // 6 warps
-constexpr int kEpiThreads = 128;
+constexpr int kThreads = 352;          // producer warp, MMA warp, 8 epilogue warps, publisher warp
+constexpr int kPublisherWarp = 10;
+constexpr int kEpiThreads = 256;       // two warps per TMEM lane quarter; they split a tile's columns
 constexpr int kGroupM = 16;            // band height (in tiles) of the L2-friendly rasterisation
 
 template <int BN> struct Cfg {
@@ -63,7 +64,7 @@ template <int BN> struct Cfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
-  static constexpr int kEpiBytes = 4 * 4096;  // per-epilogue-warp 32 x 128 B transpose buffer (fused all-reduce)
+  static constexpr int kEpiBytes = 8 * 4096;  // per-epilogue-warp 32 x 128 B transpose buffer (fused all-reduce)
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kEpiBytes;
 };
 
@@ -73,8 +74,25 @@ struct Barriers {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
+  uint32_t pub_count;   // fused all-reduce: epilogue-warp arrivals after storing a partial tile
+  uint32_t rpub_count;  // fused all-reduce: epilogue-warp arrivals after reducing an owned tile
   uint32_t pad;
 };
+
+// Monotonic arrival counters between the epilogue warps and the publisher thread (an mbarrier's
+// parity could only tell phases apart while the publisher lags by at most one tile).
+__device__ __forceinline__ void warp_arrive(uint32_t* counter, int lane) {
+  __syncwarp();
+  if (lane == 0) {
+    __threadfence_block();
+    atomicAdd_block(counter, 1u);
+  }
+}
+__device__ __forceinline__ bool counter_reached(const uint32_t* counter, uint32_t target) {
+  if (*reinterpret_cast<const volatile uint32_t*>(counter) < target) return false;
+  __threadfence_block();
+  return true;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_band = kGroupM * tiles_n;
@@ -86,7 +104,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 }
 
 __device__ __forceinline__ void epi_bar_sync() {
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -117,12 +135,13 @@ __device__ __forceinline__ int64_t stage_piece_offset(int c, int q, int row_in_t
 }
 
 // Sum the `world` staged partials of one owned tile, add bias / residual, and write the result
-// into every rank's output. Called by the 128 epilogue threads (thread == tile row). Results go
+// into every rank's output. Called by the 256 epilogue threads (row = lane of a TMEM quarter, two
+// warps per quarter take half of the columns each). Results go
 // through a per-warp shared-memory transpose so that global stores are 128-byte row segments.
 template <int BN>
 __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, int slot, int tiles_m,
-                                                 int tiles_n, int slots, int quarter, int lane,
-                                                 uint8_t* warp_buf) {
+                                                 int tiles_n, int slots, int quarter, int col_half,
+                                                 int lane, uint8_t* warp_buf) {
   const GemmComm& cm = p.comm;
   int tm, tn;
   tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -133,7 +152,7 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, in
                          static_cast<int64_t>(slot) * (BM * BN);
   const int64_t src_stride = static_cast<int64_t>(slots) * (BM * BN);
 #pragma unroll 1
-  for (int cp = 0; cp < BN / 64; ++cp) {
+  for (int cp = col_half * (BN / 128); cp < (col_half + 1) * (BN / 128); ++cp) {
     if (tn * BN + cp * 64 >= p.N) break;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -470,6 +489,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       mbar_init(&bars->tmem_full[a], 1);
       mbar_init(&bars->tmem_empty[a], kEpiThreads);
     }
+    bars->pub_count = 0;
+    bars->rpub_count = 0;
     fence_mbar_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_b);
@@ -558,14 +579,59 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         tc_commit(&bars->tmem_full[acc]);
       }
     }
+  } else if (warp == kPublisherWarp) {
+    // ---------------------------------------------- publisher of the fused all-reduce
+    // System-scope fences wait for every outstanding NVLink store of the SM (microseconds). The
+    // epilogue warps therefore never fence: they arrive on a CTA-local mbarrier after the stores of
+    // a tile and carry on (one counter increment per warp); this thread then issues the (cumulative)
+    // fence and writes the flags.
+    if (p.comm.world > 1 && elect_one()) {
+      const GemmComm& cm = p.comm;
+      const int W = cm.world, me = cm.rank;
+      const int n_my = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const int first_owned = ((me - static_cast<int>(blockIdx.x % W)) + W) % W;
+      const int n_red = n_my > first_owned ? (n_my - first_owned + W - 1) / W : 0;
+      int pa = 0, pr = 0;
+      uint64_t t0 = globaltimer_ns();
+      while (pa < n_my || pr < n_red) {
+        bool progressed = false;
+        if (pa < n_my && counter_reached(&bars->pub_count, (kEpiThreads / 32) * (pa + 1))) {
+          const int o = (blockIdx.x + pa) % W;
+          if (o != me) {
+            if (!(cm.debug & 1)) __threadfence_system();
+            st_release_sys(cm.flags[o] + (blockIdx.x + pa * gridDim.x) * kGemmMaxPeers + me, cm.epoch);
+          }
+          ++pa;
+          progressed = true;
+        }
+        if (pr < n_red && counter_reached(&bars->rpub_count, (kEpiThreads / 32) * (pr + 1))) {
+          const int it = first_owned + pr * W;
+          if (!(cm.debug & 1)) __threadfence_system();
+          for (int d = 0; d < W; ++d)
+            if (d != me)
+              st_release_sys(cm.flags[d] + cm.max_tiles * kGemmMaxPeers + (blockIdx.x + it * gridDim.x), cm.epoch);
+          ++pr;
+          progressed = true;
+        }
+        if (progressed) {
+          t0 = globaltimer_ns();
+        } else {
+          __nanosleep(64);
+          if (globaltimer_ns() - t0 > ETHB_WAIT_NS) {
+            if (p.status) atomicCAS(p.status, 0, kStatusTimeoutGridFlag);
+            break;
+          }
+        }
+      }
+    }
   } else if (p.comm.world > 1) {
     // ---------------------------------------------- epilogue fused with the TP all-reduce
     // Ownership alternates along each CTA's own tile list (tile index it -> rank (cta + it) % W),
-    // so every CTA reduces 1/W of what it computes. System-scope fences are expensive (they
-    // wait for all outstanding NVLink stores), so partial tiles are published in batches: after
-    // kBatch tiles (and at the end) one fence + one flag store per tile covers all of them.
+    // so every CTA reduces 1/W of what it computes. Publishing (fence + flag) is left to the
+    // publisher warp; `pub_count` counts partial tiles stored, `rpub_count` owned tiles reduced.
     const GemmComm& cm = p.comm;
     const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;
     const int row_in_tile = quarter * 32 + lane;
     const int tid_e = threadIdx.x - 64;
     const int W = cm.world, me = cm.rank;
@@ -576,18 +642,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     auto owner_of = [&](int it) { return static_cast<int>((blockIdx.x + it) % W); };
     // staging slot of the it-th tile of this CTA inside its owner's area: slots are per CTA
     auto slot_of = [&](int it) { return static_cast<int>(blockIdx.x) + (it / W) * static_cast<int>(gridDim.x); };
-    constexpr int kBatch = 2;
-    int red = 0, published = 0;
+    int red = 0, drained = 0;
     bool ok = true;
-    auto publish = [&](int upto) {   // make partial tiles [published, upto) visible to their owners
-      if (upto <= published) return;
-      if (!(cm.debug & 1)) __threadfence_system();
-      epi_bar_sync();
-      for (int j = published + tid_e; j < upto; j += kEpiThreads) {
-        const int o = owner_of(j);
-        if (o != me) st_release_sys(cm.flags[o] + (blockIdx.x + j * gridDim.x) * kGemmMaxPeers + me, cm.epoch);
-      }
-      published = upto;
+    auto reduce_one = [&](int it) {
+      if (!(cm.debug & 4))
+        comm_reduce_tile<BN>(p, blockIdx.x + it * gridDim.x, slot_of(it), tiles_m, tiles_n, slots, quarter,
+                             col_half, lane, epi_smem + (warp - 2) * 4096);
+      warp_arrive(&bars->rpub_count, lane);
     };
     for (int it = 0; it < n_my && ok; ++it) {
       const int owner = owner_of(it), slot = slot_of(it);
@@ -603,7 +664,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                       (static_cast<int64_t>(me) * slots + slot) * (BM * BN);
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld_32x32b_x32(taddr + c * 32, r);
@@ -618,11 +679,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
           *reinterpret_cast<uint4*>(dst + stage_piece_offset(c, q, row_in_tile)) = o;
         }
       }
+      warp_arrive(&bars->pub_count, lane);
       tc_fence_before();
       mbar_arrive(&bars->tmem_empty[acc]);
-      if ((it + 1) % kBatch == 0 || it + 1 == n_my) publish(it + 1);
+      drained = it + 1;
       // phase B (opportunistic): reduce owned tiles whose peer partials have all arrived
-      while (red < published) {
+      while (red < drained) {
         if (owner_of(red) != me) { ++red; continue; }
         const int t2 = blockIdx.x + red * gridDim.x;
         if (tid_e == 0) {
@@ -635,35 +697,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         const int ready = s_ready;
         epi_bar_sync();
         if (!ready) break;
-        if (!(cm.debug & 4))
-          comm_reduce_tile<BN>(p, t2, slot_of(red), tiles_m, tiles_n, slots, quarter, lane, epi_smem + (warp - 2) * 4096);
+        reduce_one(red);
         ++red;
       }
     }
-    publish(n_my);
     // drain: remaining owned tiles, now with (bounded) blocking waits
-    int first_unsignalled = 0;
-    while (red < n_my) {
+    while (ok && red < n_my) {
       if (owner_of(red) == me) {
         const int t2 = blockIdx.x + red * gridDim.x;
         if (tid_e < W && tid_e != me)
           wait_flag_ge(my_flags + t2 * kGemmMaxPeers + tid_e, cm.epoch, p.status);
         epi_bar_sync();
-        if (!(cm.debug & 4))
-          comm_reduce_tile<BN>(p, t2, slot_of(red), tiles_m, tiles_n, slots, quarter, lane, epi_smem + (warp - 2) * 4096);
+        reduce_one(red);
       }
       ++red;
     }
-    // one fence for all reduced tiles of this CTA, then tell the peers which tiles have landed
-    if (!(cm.debug & 1)) __threadfence_system();
-    epi_bar_sync();
-    for (int j = first_unsignalled + tid_e; j < n_my * W; j += kEpiThreads) {
-      const int itj = j / W, dstr = j % W;
-      if (owner_of(itj) == me && dstr != me)
-        st_release_sys(cm.flags[dstr] + cm.max_tiles * kGemmMaxPeers + (blockIdx.x + itj * gridDim.x), cm.epoch);
-    }
     // the tiles owned by peers must have landed in this rank's output before the kernel ends
-    for (int i = tid_e; i < n_my; i += kEpiThreads) {
+    for (int i = tid_e; i < n_my && ok; i += kEpiThreads) {
       if (owner_of(i) != me && !(cm.debug & 4))
         wait_flag_ge(my_flags + cm.max_tiles * kGemmMaxPeers + (blockIdx.x + i * gridDim.x), cm.epoch, p.status);
     }
@@ -683,7 +733,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      epilogue_tile<BN>(p, taddr, tm * BM + row_in_tile, tn * BN);
+      const int col_half = (warp - 2) >> 2;
+      epilogue_tile<BN>(p, taddr, tm * BM + row_in_tile, tn * BN, col_half * (BN / 64), (col_half + 1) * (BN / 64));
       tc_fence_before();
       mbar_arrive(&bars->tmem_empty[acc]);
     }
