@@ -108,3 +108,21 @@ def test_batch_balancing_favours_the_faster_pipeline():
     sizes = S.balance_batches([fast, slow], 64)
     assert sum(sizes) == 64 and sizes[0] > sizes[1] and sizes[0] % 4 == 0
     assert S.compositions_pow2(8, 3, 8) and all(sum(c) == 8 for c in S.compositions_pow2(8, 3, 8))
+
+
+def test_search_on_the_measured_b200_profile(tmp_path):
+    """The profile directory measured on two B200s (examples/profiles) drives a search for that node."""
+    prof = os.path.join(ROOT, "examples", "profiles", "b200_gpt_1_3B")
+    node = os.path.join(ROOT, "examples", "configs", "node_b200x2.json")
+    out = tmp_path / "out"
+    r = subprocess.run(["bash", os.path.join(ROOT, "scripts", "search_gpt.sh"), "--profile-dir", prof,
+                        "--model-size", "1_3B", "--search-budget", "5", "--global-batch-size", "128",
+                        "--node-description", node, "--output", str(out), "--python", sys.executable],
+                       capture_output=True, text=True, env=ENV)
+    assert r.returncode == 0, r.stdout + r.stderr
+    cfg = json.loads((out / "gpt_config.json").read_text())
+    assert cfg["world_size"] == 2 and cfg["total_gbs"] == 128
+    shipped = json.loads(open(os.path.join(ROOT, "examples", "configs", "gpt_1_3b_searched_2xb200.json")).read())
+    assert cfg["config_hash"] == shipped["config_hash"]      # the search is deterministic
+    # one B200 holds GPT-1.3B, so the search prefers two single-GPU pipelines over TP2 on NVLink
+    assert [p["num_gpus"] for p in cfg["pipe"]] == [[1], [1]]
