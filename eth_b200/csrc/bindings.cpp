@@ -79,7 +79,7 @@ void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, cons
                     const OptTensor& aux, double alpha, const OptTensor& status,
                     const std::vector<int64_t>& stage_ptrs, const std::vector<int64_t>& out_ptrs,
                     const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, int64_t max_tiles,
-                    int64_t stage_elems, int64_t ldd, int64_t debug) {
+                    int64_t stage_elems, int64_t ldd, int64_t debug, int64_t mode) {
   need_cuda(a, "a"); need_cuda(b, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1);
   TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a/b dtype mismatch");
@@ -110,12 +110,58 @@ void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, cons
   g.comm.max_tiles = static_cast<int>(max_tiles);
   g.comm.stage_elems = stage_elems;
   g.comm.debug = static_cast<int>(debug);
+  g.comm.mode = static_cast<int>(mode);
   for (size_t i = 0; i < w; ++i) {
     g.comm.stage[i] = reinterpret_cast<void*>(stage_ptrs[i]);
     g.comm.out[i] = reinterpret_cast<void*>(out_ptrs[i]);
     g.comm.flags[i] = reinterpret_cast<int*>(flag_ptrs[i]);
   }
   check(ethb::gemm_tcgen05(g, cur_stream()), "gemm_allreduce");
+}
+
+// All-gather of the row-sharded operand fused into the GEMM that consumes it (GemmComm mode 2).
+// `a_full` is this rank's [M, K] operand buffer inside a symmetric allocation; a_ptrs are the base
+// addresses of that buffer on every rank of the group.
+void gemm_allgather(const Tensor& a_full, const Tensor& b, bool b_mn, Tensor& d, const OptTensor& bias,
+                    const OptTensor& d2, const OptTensor& status, const std::vector<int64_t>& a_ptrs,
+                    const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch) {
+  need_cuda(a_full, "a_full"); need_cuda(b, "b"); need_cuda(d, "d");
+  TORCH_CHECK(a_full.dim() == 2 && b.dim() == 2 && d.dim() == 2 && a_full.stride(1) == 1 && b.stride(1) == 1 &&
+              d.stride(1) == 1);
+  TORCH_CHECK(a_full.scalar_type() == b.scalar_type(), "a/b dtype mismatch");
+  c10::cuda::CUDAGuard guard(a_full.device());
+  ethb::GemmArgs g{};
+  g.M = static_cast<int>(a_full.size(0));
+  g.K = static_cast<int>(a_full.size(1));
+  g.N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == g.K, "reduction dims differ");
+  TORCH_CHECK(d.size(0) == g.M && d.size(1) == g.N, "bad output shape");
+  TORCH_CHECK(g.K % 8 == 0, "K must be a multiple of 8");
+  g.A = a_full.data_ptr(); g.lda = a_full.stride(0); g.a_mn = 0;
+  g.B = b.data_ptr(); g.ldb = b.stride(0); g.b_mn = b_mn;
+  g.ab_dtype = dtype_code(a_full);
+  g.D = d.data_ptr(); g.ldd = d.stride(0); g.d_dtype = dtype_code(d);
+  if (d2.has_value()) {
+    TORCH_CHECK(d2->scalar_type() == a_full.scalar_type() && d2->stride(0) == d.stride(0) &&
+                    d.scalar_type() == a_full.scalar_type(), "d2 must match d");
+    g.D2 = d2->data_ptr();
+  }
+  g.bias = optptr(bias);
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == a_full.scalar_type() && bias->numel() == g.N);
+  g.alpha = 1.0f;
+  g.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  const size_t w = a_ptrs.size();
+  TORCH_CHECK(w >= 2 && w <= ethb::kGemmMaxPeers && flag_ptrs.size() == w);
+  TORCH_CHECK(reinterpret_cast<int64_t>(a_full.data_ptr()) == a_ptrs[rank], "a_full must be this rank's buffer");
+  g.comm.world = static_cast<int>(w);
+  g.comm.rank = static_cast<int>(rank);
+  g.comm.epoch = static_cast<int>(epoch);
+  g.comm.mode = 2;
+  for (size_t i = 0; i < w; ++i) {
+    g.comm.stage[i] = reinterpret_cast<void*>(a_ptrs[i]);
+    g.comm.flags[i] = reinterpret_cast<int*>(flag_ptrs[i]);
+  }
+  check(ethb::gemm_tcgen05(g, cur_stream()), "gemm_allgather");
 }
 
 void layernorm_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, Tensor& y,
@@ -449,6 +495,7 @@ void peer_allreduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_allreduce", &gemm_allreduce);
+  m.def("gemm_allgather", &gemm_allgather);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("ln_bwd_parts", &ln_bwd_parts);
   m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"),

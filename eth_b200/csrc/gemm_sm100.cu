@@ -103,6 +103,54 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tm = band * kGroupM + (r - tn * rows);
 }
 
+// The it-th tile of CTA `cta` in a grid of G CTAs. Plain GEMM and fused all-reduce walk the
+// rasterised tile list with stride G. In reduce-scatter mode (W | G) the tile must lie in the row
+// block of its owner (cta + it) % W: within one `it` the CTAs cta = W * j + r cover, for every
+// owner, the G / W consecutive tiles it * (G / W) + j of that owner's block.
+__device__ __forceinline__ bool sched_tile(const GemmArgs& p, int cta, int G, int it, int tiles_m,
+                                           int tiles_n, int& tm, int& tn) {
+  if (p.comm.world > 1 && p.comm.mode == 1) {
+    const int W = p.comm.world;
+    const int rows_per = tiles_m / W;
+    const int vp = it * (G / W) + cta / W;
+    if (vp >= rows_per * tiles_n) return false;
+    tile_coords(vp, rows_per, tiles_n, tm, tn);
+    tm += ((cta + it) % W) * rows_per;
+    return true;
+  }
+  const int tile = cta + it * G;
+  if (tile >= tiles_m * tiles_n) return false;
+  tile_coords(tile, tiles_m, tiles_n, tm, tn);
+  if (p.comm.world > 1 && p.comm.mode == 2)   // all-gather: rows this rank already holds come first
+    tm = (tm + p.comm.rank * (tiles_m / p.comm.world)) % tiles_m;
+  return true;
+}
+
+// ---- all-gather mode --------------------------------------------------------------------------
+// flags[r] (ints, symmetric):  [src]            shard of `src` is ready to be read   (written by src)
+//                              [W + src]        `src` has finished reading r's shard (written by src)
+//                              [2W]             arrival counter of r's own gather warps (wraps)
+//                              [kAgUnitFlags..] one flag per 8-row unit of r's operand buffer
+constexpr int kAgUnitRows = 8;
+constexpr int kAgUnitFlags = 64;
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int sched_count(const GemmArgs& p, int cta, int G, int tiles_m, int tiles_n) {
+  if (p.comm.world > 1 && p.comm.mode == 1) {
+    const int W = p.comm.world;
+    const int per = (tiles_m / W) * tiles_n, step = G / W, first = cta / W;
+    return first < per ? (per - first + step - 1) / step : 0;
+  }
+  const int num = tiles_m * tiles_n;
+  return cta < num ? (num - cta + G - 1) / G : 0;
+}
+
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
@@ -139,12 +187,9 @@ __device__ __forceinline__ int64_t stage_piece_offset(int c, int q, int row_in_t
 // warps per quarter take half of the columns each). Results go
 // through a per-warp shared-memory transpose so that global stores are 128-byte row segments.
 template <int BN>
-__device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, int slot, int tiles_m,
-                                                 int tiles_n, int slots, int quarter, int col_half,
-                                                 int lane, uint8_t* warp_buf) {
+__device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tm, int tn, int slot, int slots,
+                                                 int quarter, int col_half, int lane, uint8_t* warp_buf) {
   const GemmComm& cm = p.comm;
-  int tm, tn;
-  tile_coords(tile, tiles_m, tiles_n, tm, tn);
   const int row_in_tile = quarter * 32 + lane;
   const int row = tm * BM + row_in_tile;
   const bool row_ok = row < p.M;
@@ -194,7 +239,8 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, in
       }
       if (row_ok && p.aux_mode == kAuxAdd && col0 < p.N) {
         const uint4* ap = reinterpret_cast<const uint4*>(
-            reinterpret_cast<const uint16_t*>(p.aux) + static_cast<int64_t>(row) * p.ldaux + col0);
+            reinterpret_cast<const uint16_t*>(p.aux) +
+            static_cast<int64_t>(cm.mode == 1 ? row - cm.rank * (p.M / cm.world) : row) * p.ldaux + col0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           if (col0 + q * 8 < p.N) {
@@ -230,10 +276,15 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tile, in
       const int grow = tm * BM + quarter * 32 + rl;
       const int gcol = tn * BN + cp * 64 + piece * 8;
       if (grow < p.M && gcol < p.N) {
-        for (int dst = 0; dst < cm.world; ++dst)
-          if (!(cm.debug & 2) || dst == cm.rank)
-          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[dst]) +
-                                    static_cast<int64_t>(grow) * p.ldd + gcol) = o;
+        if (cm.mode == 1) {   // reduce-scatter: the owner keeps its rows, nothing goes back to the peers
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[cm.rank]) +
+                                    static_cast<int64_t>(grow - cm.rank * (p.M / cm.world)) * p.ldd + gcol) = o;
+        } else {
+          for (int dst = 0; dst < cm.world; ++dst)
+            if (!(cm.debug & 2) || dst == cm.rank)
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[dst]) +
+                                        static_cast<int64_t>(grow) * p.ldd + gcol) = o;
+        }
       }
     }
     __syncwarp();
@@ -509,10 +560,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      int tm, tn;
+      for (int it = 0; ok && sched_tile(p, blockIdx.x, gridDim.x, it, tiles_m, tiles_n, tm, tn); ++it) {
         const int m0 = tm * BM, n0 = tn * BN;
+        if (p.comm.world > 1 && p.comm.mode == 2 && tm / (tiles_m / p.comm.world) != p.comm.rank) {
+          // rows gathered from a peer: all 16 eight-row units of this 128-row block must have landed
+          const int* uf = p.comm.flags[p.comm.rank] + kAgUnitFlags + tm * (BM / kAgUnitRows);
+          const uint64_t t0 = globaltimer_ns();
+          for (int u = 0; u < BM / kAgUnitRows && ok; ++u) {
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(uf + u) < p.comm.epoch) {
+              if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > ETHB_WAIT_NS) {
+                if (p.status) atomicCAS(p.status, 0, kStatusTimeoutGridFlag);
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores -> TMA (async proxy) reads
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) {
             ok = false;
@@ -546,9 +613,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
           make_idesc_f16(p.ab_dtype == kBF16 ? 1 : 0, p.a_mn, p.b_mn, BM, BN);
       int stage = 0;
       uint32_t phase = 0;
-      int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int n_my = sched_count(p, blockIdx.x, gridDim.x, tiles_m, tiles_n);
+      for (int it = 0; it < n_my && ok; ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutTmemEmpty)) {
@@ -579,6 +646,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         tc_commit(&bars->tmem_full[acc]);
       }
     }
+  } else if (warp == kPublisherWarp && p.comm.world > 1 && p.comm.mode == 2) {
+    // ---------------------------------------------- gather warp (all-gather of A)
+    // One warp per CTA copies 8-row units of the peers' row blocks into the local operand buffer,
+    // in the order in which the tile schedule will need them, and flags every unit.
+    const GemmComm& cm = p.comm;
+    const int W = cm.world, me = cm.rank;
+    const int rows_per = p.M / W;
+    int* my_flags = cm.flags[me];
+    bool ok = true;
+    if (blockIdx.x == 0 && lane < W && lane != me) {          // my block is complete: tell the peers
+      __threadfence_system();
+      st_release_sys(cm.flags[lane] + me, cm.epoch);
+    }
+    const int units_per_rank = rows_per / kAgUnitRows;
+    const int remote_units = (W - 1) * units_per_rank;
+    const int row_vecs = p.K / 8;                               // 16-byte pieces per row
+    for (int u = blockIdx.x; u < remote_units && ok; u += gridDim.x) {
+      const int src = (me + 1 + u / units_per_rank) % W;        // blocks in schedule order after my own
+      const int row0 = src * rows_per + (u % units_per_rank) * kAgUnitRows;
+      if (!wait_flag_ge(my_flags + src, cm.epoch, p.status)) { ok = false; break; }
+      const uint16_t* from = reinterpret_cast<const uint16_t*>(cm.stage[src]);
+      uint16_t* to = reinterpret_cast<uint16_t*>(cm.stage[me]);
+      const int total = kAgUnitRows * row_vecs;
+      for (int base = 0; base < total; base += 32 * 16) {
+        uint4 v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int idx = base + j * 32 + lane;
+          if (idx < total) {
+            const int r = idx / row_vecs, c = idx - r * row_vecs;
+            v[j] = *reinterpret_cast<const uint4*>(from + static_cast<int64_t>(row0 + r) * p.lda + c * 8);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int idx = base + j * 32 + lane;
+          if (idx < total) {
+            const int r = idx / row_vecs, c = idx - r * row_vecs;
+            *reinterpret_cast<uint4*>(to + static_cast<int64_t>(row0 + r) * p.lda + c * 8) = v[j];
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        st_release_gpu(my_flags + kAgUnitFlags + row0 / kAgUnitRows, cm.epoch);
+      }
+    }
+    // the last gather warp of this GPU tells every peer that its block is no longer being read
+    __syncwarp();
+    if (lane == 0) {
+      const unsigned old = atomicInc(reinterpret_cast<unsigned*>(my_flags + 2 * W), gridDim.x - 1);
+      if (old == gridDim.x - 1) {
+        __threadfence_system();
+        for (int d = 0; d < W; ++d)
+          if (d != me) st_release_sys(cm.flags[d] + W + me, cm.epoch);
+      }
+    }
+    // nobody may still read my block when this kernel ends (the caller overwrites it afterwards)
+    if (blockIdx.x == 0 && lane < W && lane != me && ok) wait_flag_ge(my_flags + W + lane, cm.epoch, p.status);
   } else if (warp == kPublisherWarp) {
     // ---------------------------------------------- publisher of the fused all-reduce
     // System-scope fences wait for every outstanding NVLink store of the SM (microseconds). The
@@ -588,7 +715,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     if (p.comm.world > 1 && elect_one()) {
       const GemmComm& cm = p.comm;
       const int W = cm.world, me = cm.rank;
-      const int n_my = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const int n_my = sched_count(p, blockIdx.x, gridDim.x, tiles_m, tiles_n);
       const int first_owned = ((me - static_cast<int>(blockIdx.x % W)) + W) % W;
       const int n_red = n_my > first_owned ? (n_my - first_owned + W - 1) / W : 0;
       int pa = 0, pr = 0;
@@ -624,7 +751,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
       }
     }
-  } else if (p.comm.world > 1) {
+  } else if (p.comm.world > 1 && p.comm.mode != 2) {
     // ---------------------------------------------- epilogue fused with the TP all-reduce
     // Ownership alternates along each CTA's own tile list (tile index it -> rank (cta + it) % W),
     // so every CTA reduces 1/W of what it computes. Publishing (fence + flag) is left to the
@@ -638,16 +765,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     const int slots = (num_tiles + W - 1) / W + static_cast<int>(gridDim.x);
     int* my_flags = cm.flags[me];
     __shared__ int s_ready;
-    const int n_my = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int n_my = sched_count(p, blockIdx.x, gridDim.x, tiles_m, tiles_n);
     auto owner_of = [&](int it) { return static_cast<int>((blockIdx.x + it) % W); };
     // staging slot of the it-th tile of this CTA inside its owner's area: slots are per CTA
     auto slot_of = [&](int it) { return static_cast<int>(blockIdx.x) + (it / W) * static_cast<int>(gridDim.x); };
     int red = 0, drained = 0;
     bool ok = true;
     auto reduce_one = [&](int it) {
-      if (!(cm.debug & 4))
-        comm_reduce_tile<BN>(p, blockIdx.x + it * gridDim.x, slot_of(it), tiles_m, tiles_n, slots, quarter,
-                             col_half, lane, epi_smem + (warp - 2) * 4096);
+      int rtm, rtn;
+      if (!(cm.debug & 4) && sched_tile(p, blockIdx.x, gridDim.x, it, tiles_m, tiles_n, rtm, rtn))
+        comm_reduce_tile<BN>(p, rtm, rtn, slot_of(it), slots, quarter, col_half, lane,
+                             epi_smem + (warp - 2) * 4096);
       warp_arrive(&bars->rpub_count, lane);
     };
     for (int it = 0; it < n_my && ok; ++it) {
@@ -721,11 +849,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     const int row_in_tile = quarter * 32 + lane;
-    int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+    int tm, tn;
+    for (int it = 0; sched_tile(p, blockIdx.x, gridDim.x, it, tiles_m, tiles_n, tm, tn); ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (ok && !mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull))
@@ -1021,14 +1147,23 @@ cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
     attr_set = true;
   }
   const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
-  if (a.comm.world > 1) {
-    const int64_t slots = (tiles + a.comm.world - 1) / a.comm.world + (tiles < device_sm_count() ? tiles : device_sm_count());
-    ETHB_RETURN_IF(tiles > a.comm.max_tiles, cudaErrorInvalidValue, "fused all-reduce: more tiles than flags");
-    ETHB_RETURN_IF(slots * a.comm.world * BM * BN > a.comm.stage_elems, cudaErrorInvalidValue,
-                   "fused all-reduce: staging area too small");
-  }
   int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
-  const int grid = tiles < sms ? tiles : sms;
+  int grid = tiles < sms ? tiles : sms;
+  if (a.comm.world > 1 && a.comm.mode == 2) {
+    ETHB_RETURN_IF(a.M % (BM * a.comm.world) != 0 || a.a_mn, cudaErrorInvalidValue,
+                   "fused all-gather GEMM: M must be a multiple of 128 * world and A row-major");
+  } else if (a.comm.world > 1) {
+    const int W = a.comm.world;
+    if (a.comm.mode == 1) {   // reduce-scatter: the schedule needs W | grid and whole row blocks per rank
+      ETHB_RETURN_IF(a.M % (BM * W) != 0, cudaErrorInvalidValue, "fused reduce-scatter: M must be a multiple of 128 * world");
+      grid = grid / W * W;
+      ETHB_RETURN_IF(grid <= 0, cudaErrorInvalidValue, "fused reduce-scatter: fewer SMs than ranks");
+    }
+    const int64_t slots = (tiles + W - 1) / W + grid;
+    ETHB_RETURN_IF(tiles + grid > a.comm.max_tiles, cudaErrorInvalidValue, "fused collective GEMM: more tiles than flags");
+    ETHB_RETURN_IF(slots * W * BM * BN > a.comm.stage_elems, cudaErrorInvalidValue,
+                   "fused collective GEMM: staging area too small");
+  }
   gemm_tcgen05_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, a);
   count_launch();
   return cudaGetLastError();
@@ -1119,7 +1254,8 @@ cudaError_t gemm_tcgen05(const GemmArgs& a, cudaStream_t stream) {
   if (a.ab_dtype != kF16 && a.ab_dtype != kBF16) return cudaErrorInvalidValue;
   if (a.comm.world > 1) {
     ETHB_RETURN_IF(a.comm.world > kGemmMaxPeers, cudaErrorInvalidValue, "fused all-reduce: too many peers");
-    ETHB_RETURN_IF(a.d_dtype != a.ab_dtype || a.accumulate || a.D2 != nullptr || a.aux_mode == kAuxGeluGrad,
+    ETHB_RETURN_IF(a.comm.mode != 2 && (a.d_dtype != a.ab_dtype || a.accumulate || a.D2 != nullptr ||
+                                        a.aux_mode == kAuxGeluGrad),
                    cudaErrorInvalidValue, "fused all-reduce: unsupported epilogue");
   }
   const int variant = g_gemm_variant.load();

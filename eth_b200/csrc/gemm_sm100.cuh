@@ -30,6 +30,16 @@ struct GemmComm {
   int* flags[kGemmMaxPeers];
   int64_t stage_elems;  // capacity of one rank's staging area in 16-bit elements
   int debug;            // timing experiments only: 1 no system fences, 2 no peer output stores, 4 no reduce
+  // 0: all-reduce (every rank receives the full [M, N] result).
+  // 1: reduce-scatter along rows: rank r receives rows [r * M / world, (r + 1) * M / world) of the sum
+  //    in its own `out[rank]` buffer of M / world rows; M must be a multiple of 128 * world. Tiles of a
+  //    rank's row block are owned by that rank, so reduced data never crosses NVLink a second time.
+  // 2: all-gather of A, then a plain GEMM. `stage[r]` is rank r's [M, K] operand buffer (row stride
+  //    lda) in which rank r has filled its own row block [r * M / world, (r + 1) * M / world) before
+  //    the call; the kernel copies the peers' blocks into `stage[rank]` over NVLink (8 rows per step,
+  //    plain peer loads) while the MMAs already work on the local rows, and computes the full
+  //    [M, N] product with the usual epilogue. `out` is unused. M must be a multiple of 128 * world.
+  int mode;
 };
 
 struct GemmArgs {

@@ -39,6 +39,12 @@ class FusedTPBackend:
         self.stage = SymmetricBuffer(self.stage_elems * esize, group_ranks, my_rank, group, device)
         self.out = SymmetricBuffer(self.out_slot_bytes * RING, group_ranks, my_rank, group, device)
         self.flags = SymmetricBuffer(MAX_TILES * 9 * 4, group_ranks, my_rank, group, device)
+        # all-gather + GEMM: a ring of [max_tokens, hidden-or-wider] operand buffers and their own flags
+        self.ag_cols = max(hidden, cols)
+        self.ag_slot_bytes = rows * self.ag_cols * esize
+        self.ag = SymmetricBuffer(self.ag_slot_bytes * RING, group_ranks, my_rank, group, device)
+        self.ag_flags = SymmetricBuffer((64 + rows // 8) * 4, group_ranks, my_rank, group, device)
+        self.ag_slot = 0
         self.rank = self.stage.index
         self.epoch = 0
         self.slot = 0
@@ -67,9 +73,59 @@ class FusedTPBackend:
         off = slot * self.out_slot_bytes
         native.lib().gemm_allreduce(a, False, b, b_mn, bias, residual, float(alpha), native.status(a.device),
                                     self.stage.ptrs, self.out.offset_ptrs(off), self.flags.ptrs, self.rank,
-                                    self.epoch, MAX_TILES, self.stage_elems, n, self.debug)
+                                    self.epoch, MAX_TILES, self.stage_elems, n, self.debug, 0)
         out = self.out.tensor((m, n), self.dtype, off)
         out._ethb_ring = True   # short-lived: valid until RING further fused calls
+        return out
+
+    def gemm_reduce_scatter(self, a, b, *, b_mn=False, bias=None, residual=None, alpha=1.0):
+        """Rows [rank * M / world, (rank + 1) * M / world) of the sum over the TP group of (a x b^T)
+        (+ bias, + residual given as this rank's [M / world, N] slice): the sequence-parallel form of
+        a row-parallel linear. One kernel: every rank pushes the partial tiles of a peer's row block
+        into that peer's staging area while it computes the next tile; the owner reduces and keeps
+        the rows. M must be a multiple of 128 * world. Returns a view of a ring slot."""
+        m = a.shape[0]
+        n = b.shape[1] if b_mn else b.shape[0]
+        if not self.supports(m, n):
+            raise ValueError(f"fused reduce-scatter GEMM: shape {m}x{n} exceeds the symmetric buffers")
+        if m % (128 * self.world):
+            raise ValueError("fused reduce-scatter GEMM: rows must be a multiple of 128 * world")
+        self.epoch += 1
+        slot = self.slot
+        self.slot = (self.slot + 1) % RING
+        off = slot * self.out_slot_bytes
+        native.lib().gemm_allreduce(a, False, b, b_mn, bias, residual, float(alpha), native.status(a.device),
+                                    self.stage.ptrs, self.out.offset_ptrs(off), self.flags.ptrs, self.rank,
+                                    self.epoch, MAX_TILES, self.stage_elems, n, self.debug, 1)
+        out = self.out.tensor((m // self.world, n), self.dtype, off)
+        out._ethb_ring = True
+        return out
+
+    def gather_buffer(self, m: int, k: int):
+        """Next [m, k] operand buffer of the all-gather ring and the view of this rank's own row block
+        inside it; the caller writes its block (e.g. as the output of the producing kernel) and then
+        passes the buffer to `gemm_all_gather`."""
+        if m > self.max_tokens or k > self.ag_cols or m % (128 * self.world) or k % 8:
+            raise ValueError(f"all-gather GEMM: operand {m}x{k} not supported by the symmetric buffers")
+        off = self.ag_slot * self.ag_slot_bytes
+        self.ag_slot = (self.ag_slot + 1) % RING
+        full = self.ag.tensor((m, k), self.dtype, off)
+        rows = m // self.world
+        full._ethb_ring, full._ethb_offset = True, off
+        return full, full[self.rank * rows:(self.rank + 1) * rows]
+
+    def gemm_all_gather(self, full, weight, *, b_mn=False, bias=None, gelu_out=None, out=None):
+        """out = concat_r(A_r) x weight^T where every rank has written its row block A_r into its own
+        `full` buffer (from `gather_buffer`). One kernel: a gather warp per CTA pulls the peers' blocks
+        over NVLink into `full` while the MMAs start on the local rows; tiles of gathered rows wait for
+        their rows only. The column-parallel forward of a sequence-parallel layer."""
+        m = full.shape[0]
+        n = weight.shape[1] if b_mn else weight.shape[0]
+        if out is None:
+            out = torch.empty((m, n), dtype=self.dtype, device=self.device)
+        self.epoch += 1
+        native.lib().gemm_allgather(full, weight, b_mn, out, bias, gelu_out, native.status(full.device),
+                                    self.ag.offset_ptrs(full._ethb_offset), self.ag_flags.ptrs, self.rank, self.epoch)
         return out
 
     def all_reduce_(self, t):
@@ -77,5 +133,5 @@ class FusedTPBackend:
         return t
 
     def close(self):
-        for b in (self.stage, self.out, self.flags):
+        for b in (self.stage, self.out, self.flags, self.ag, self.ag_flags):
             b.close()

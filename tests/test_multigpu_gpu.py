@@ -107,3 +107,54 @@ def test_engine_tp2_and_dp2_match_single_gpu():
     for (l1, n1), (l2, n2), (l3, n3) in zip(single, tp2, dp2):
         assert abs(l1 - l2) < 3e-2 and abs(l1 - l3) < 3e-2, (single, tp2, dp2)
         assert abs(n1 - n2) / n1 < 5e-2 and abs(n1 - n3) / n1 < 5e-2, (single, tp2, dp2)
+
+
+def _fused_rs_ag(rank, world):
+    import torch.distributed as dist
+    from eth_b200.ops import native
+    from eth_b200.parallel.fused_tp import FusedTPBackend
+    dev = torch.device("cuda", rank)
+    dt = torch.bfloat16
+    be = FusedTPBackend(tuple(range(world)), rank, None, dev, max_tokens=4096, hidden=2048, dtype=dt)
+    out = {"rs": [], "ag": []}
+    # GEMM + reduce-scatter: rows [rank * M / W, ...) of the summed product, with bias and a sharded residual
+    for (m, n, k, b_mn) in [(512, 512, 256, False), (4096, 2048, 1024, False), (2048, 2048, 3072, True)]:
+        for rep in range(2):
+            g = torch.Generator(device=dev).manual_seed(77 * rank + rep)
+            a = torch.randn(m, k, device=dev, dtype=dt, generator=g)
+            w = torch.randn((k, n) if b_mn else (n, k), device=dev, dtype=dt, generator=g) * 0.05
+            bias = torch.randn(n, device=dev, dtype=dt, generator=torch.Generator(device=dev).manual_seed(5))
+            res = torch.randn(m // world, n, device=dev, dtype=dt, generator=g)
+            got = be.gemm_reduce_scatter(a, w, b_mn=b_mn, bias=bias, residual=res).clone()
+            ref = a.float() @ (w.float() if b_mn else w.float().t())
+            dist.all_reduce(ref)
+            rows = m // world
+            ref = ref[rank * rows:(rank + 1) * rows] + bias.float() + res.float()
+            out["rs"].append(((got.float() - ref).norm() / ref.norm()).item())
+    # all-gather + GEMM: every rank contributes a row block of the operand
+    for (m, n, k, b_mn) in [(512, 768, 256, False), (4096, 3072, 2048, False), (2048, 1024, 2048, True)]:
+        for rep in range(2):
+            g = torch.Generator(device=dev).manual_seed(31 * rank + rep)
+            full, mine = be.gather_buffer(m, k)
+            block = torch.randn(m // world, k, device=dev, dtype=dt, generator=g)
+            mine.copy_(block)
+            w = torch.randn((k, n) if b_mn else (n, k), device=dev, dtype=dt, generator=torch.Generator(device=dev).manual_seed(9)) * 0.05
+            bias = torch.randn(n, device=dev, dtype=dt, generator=torch.Generator(device=dev).manual_seed(6))
+            got = be.gemm_all_gather(full, w, b_mn=b_mn, bias=bias)
+            blocks = [torch.empty_like(block) for _ in range(world)]
+            dist.all_gather(blocks, block)
+            a_ref = torch.cat(blocks).float()
+            ref = a_ref @ (w.float() if b_mn else w.float().t()) + bias.float()
+            out["ag"].append(((got.float() - ref).norm() / ref.norm()).item())
+            out["ag"].append(float(not torch.equal(full, torch.cat(blocks))))   # gathered operand itself
+    native.check_status()
+    be.close()
+    return out
+
+
+def test_fused_reduce_scatter_and_all_gather_gemm_two_gpus():
+    _need(2)
+    res = run_ranks(2, _fused_rs_ag, backend="nccl")
+    for r in res:
+        assert max(r["rs"]) < 1e-2, r["rs"]
+        assert max(r["ag"]) < 1e-2, r["ag"]
