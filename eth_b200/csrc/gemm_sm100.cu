@@ -127,20 +127,10 @@ __device__ __forceinline__ bool sched_tile(const GemmArgs& p, int cta, int G, in
 }
 
 // ---- all-gather mode --------------------------------------------------------------------------
-// flags[r] (ints, symmetric):  [src]            shard of `src` is ready to be read   (written by src)
-//                              [W + src]        `src` has finished reading r's shard (written by src)
-//                              [2W]             arrival counter of r's own gather warps (wraps)
-//                              [kAgUnitFlags..] one flag per 8-row unit of r's operand buffer
+// flags[r] (ints, symmetric): [kAgUnitFlags + row / 8] = epoch once the 8-row unit starting at `row`
+// of r's operand buffer has been written by the rank that owns those rows.
 constexpr int kAgUnitRows = 8;
 constexpr int kAgUnitFlags = 64;
-__device__ __forceinline__ void st_release_gpu(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ int sched_count(const GemmArgs& p, int cta, int G, int tiles_m, int tiles_n) {
   if (p.comm.world > 1 && p.comm.mode == 1) {
     const int W = p.comm.world;
@@ -569,7 +559,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
           const uint64_t t0 = globaltimer_ns();
           for (int u = 0; u < BM / kAgUnitRows && ok; ++u) {
             uint32_t spins = 0;
-            while (ld_acquire_gpu(uf + u) < p.comm.epoch) {
+            while (ld_acquire_sys(uf + u) < p.comm.epoch) {
               if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > ETHB_WAIT_NS) {
                 if (p.status) atomicCAS(p.status, 0, kStatusTimeoutGridFlag);
                 ok = false;
@@ -647,27 +637,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
     }
   } else if (warp == kPublisherWarp && p.comm.world > 1 && p.comm.mode == 2) {
-    // ---------------------------------------------- gather warp (all-gather of A)
-    // One warp per CTA copies 8-row units of the peers' row blocks into the local operand buffer,
-    // in the order in which the tile schedule will need them, and flags every unit.
+    // ---------------------------------------------- gather warp (all-gather of A, push model)
+    // One warp per CTA copies 8-row units of THIS rank's row block into every peer's operand buffer
+    // (posted NVLink stores need no round trip, unlike loads), in increasing row order -- the order
+    // in which the peers' tile schedules need them -- and then raises the unit's flag on the peer.
+    // A slot of the operand ring is rewritten RING calls later; by then the peer has finished with
+    // it, because every call needs the peer's block of the previous call to complete.
     const GemmComm& cm = p.comm;
     const int W = cm.world, me = cm.rank;
     const int rows_per = p.M / W;
-    int* my_flags = cm.flags[me];
-    bool ok = true;
-    if (blockIdx.x == 0 && lane < W && lane != me) {          // my block is complete: tell the peers
-      __threadfence_system();
-      st_release_sys(cm.flags[lane] + me, cm.epoch);
-    }
-    const int units_per_rank = rows_per / kAgUnitRows;
-    const int remote_units = (W - 1) * units_per_rank;
+    const int units = rows_per / kAgUnitRows;
     const int row_vecs = p.K / 8;                               // 16-byte pieces per row
-    for (int u = blockIdx.x; u < remote_units && ok; u += gridDim.x) {
-      const int src = (me + 1 + u / units_per_rank) % W;        // blocks in schedule order after my own
-      const int row0 = src * rows_per + (u % units_per_rank) * kAgUnitRows;
-      if (!wait_flag_ge(my_flags + src, cm.epoch, p.status)) { ok = false; break; }
-      const uint16_t* from = reinterpret_cast<const uint16_t*>(cm.stage[src]);
-      uint16_t* to = reinterpret_cast<uint16_t*>(cm.stage[me]);
+    const uint16_t* from = reinterpret_cast<const uint16_t*>(cm.stage[me]);
+    int pending = 0;
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const int row0 = me * rows_per + u * kAgUnitRows;
       const int total = kAgUnitRows * row_vecs;
       for (int base = 0; base < total; base += 32 * 16) {
         uint4 v[16];
@@ -679,33 +663,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
             v[j] = *reinterpret_cast<const uint4*>(from + static_cast<int64_t>(row0 + r) * p.lda + c * 8);
           }
         }
+        for (int d = 0; d < W; ++d) {
+          if (d == me) continue;
+          uint16_t* to = reinterpret_cast<uint16_t*>(cm.stage[d]);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int idx = base + j * 32 + lane;
-          if (idx < total) {
-            const int r = idx / row_vecs, c = idx - r * row_vecs;
-            *reinterpret_cast<uint4*>(to + static_cast<int64_t>(row0 + r) * p.lda + c * 8) = v[j];
+          for (int j = 0; j < 16; ++j) {
+            const int idx = base + j * 32 + lane;
+            if (idx < total) {
+              const int r = idx / row_vecs, c = idx - r * row_vecs;
+              *reinterpret_cast<uint4*>(to + static_cast<int64_t>(row0 + r) * p.lda + c * 8) = v[j];
+            }
           }
         }
       }
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence();
-        st_release_gpu(my_flags + kAgUnitFlags + row0 / kAgUnitRows, cm.epoch);
+      // a system-scope fence waits for all outstanding NVLink stores: raise the flags of two units at a time
+      ++pending;
+      if (pending == 2 || u + static_cast<int>(gridDim.x) >= units) {
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();
+          for (int q = 0; q < pending; ++q) {
+            const int uq = u - q * static_cast<int>(gridDim.x);
+            for (int d = 0; d < W; ++d)
+              if (d != me)
+                st_release_sys(cm.flags[d] + kAgUnitFlags + (me * rows_per) / kAgUnitRows + uq, cm.epoch);
+          }
+        }
+        pending = 0;
       }
     }
-    // the last gather warp of this GPU tells every peer that its block is no longer being read
-    __syncwarp();
-    if (lane == 0) {
-      const unsigned old = atomicInc(reinterpret_cast<unsigned*>(my_flags + 2 * W), gridDim.x - 1);
-      if (old == gridDim.x - 1) {
-        __threadfence_system();
-        for (int d = 0; d < W; ++d)
-          if (d != me) st_release_sys(cm.flags[d] + W + me, cm.epoch);
-      }
-    }
-    // nobody may still read my block when this kernel ends (the caller overwrites it afterwards)
-    if (blockIdx.x == 0 && lane < W && lane != me && ok) wait_flag_ge(my_flags + W + lane, cm.epoch, p.status);
   } else if (warp == kPublisherWarp) {
     // ---------------------------------------------- publisher of the fused all-reduce
     // System-scope fences wait for every outstanding NVLink store of the SM (microseconds). The

@@ -36,9 +36,11 @@ struct GemmComm {
   //    rank's row block are owned by that rank, so reduced data never crosses NVLink a second time.
   // 2: all-gather of A, then a plain GEMM. `stage[r]` is rank r's [M, K] operand buffer (row stride
   //    lda) in which rank r has filled its own row block [r * M / world, (r + 1) * M / world) before
-  //    the call; the kernel copies the peers' blocks into `stage[rank]` over NVLink (8 rows per step,
-  //    plain peer loads) while the MMAs already work on the local rows, and computes the full
-  //    [M, N] product with the usual epilogue. `out` is unused. M must be a multiple of 128 * world.
+  //    the call; the kernel pushes that block into every peer's buffer over NVLink (8 rows per step,
+  //    plain peer stores, one flag per step) while the MMAs already work on the local rows, and
+  //    computes the full [M, N] product with the usual epilogue; tiles of a peer's rows wait for
+  //    those rows only. `out` is unused. M must be a multiple of 128 * world. A buffer may be reused
+  //    for this mode after two further calls on the same flags.
   int mode;
 };
 

@@ -116,9 +116,9 @@ class FusedTPBackend:
 
     def gemm_all_gather(self, full, weight, *, b_mn=False, bias=None, gelu_out=None, out=None):
         """out = concat_r(A_r) x weight^T where every rank has written its row block A_r into its own
-        `full` buffer (from `gather_buffer`). One kernel: a gather warp per CTA pulls the peers' blocks
-        over NVLink into `full` while the MMAs start on the local rows; tiles of gathered rows wait for
-        their rows only. The column-parallel forward of a sequence-parallel layer."""
+        `full` buffer (from `gather_buffer`). One kernel: a gather warp per CTA pushes this rank's block
+        into the peers' buffers over NVLink while the MMAs start on the local rows; tiles of a peer's
+        rows wait for those rows only. The column-parallel forward of a sequence-parallel layer."""
         m = full.shape[0]
         n = weight.shape[1] if b_mn else weight.shape[0]
         if out is None:
