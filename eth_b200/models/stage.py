@@ -63,6 +63,9 @@ class GPTStage:
             self._mark_fusions()
         self._segments = self._plan_segments()
         self._contexts: Dict[int, dict] = {}
+        # called with the global op index after every op's backward (the engine sets it for the last
+        # micro-batch of an iteration to start gradient reductions while backward is still running)
+        self.after_op_backward = None
         self.op_events = None   # set to a list to record (op name, phase, start event, end event)
         prev = self.descriptors[op_begin - 1]["name"] if op_begin > 0 else None
         self.input_spec = LIVE_AFTER[prev] if prev else ()
@@ -203,6 +206,8 @@ class GPTStage:
                     self._run(op, "refwd", op.fwd, env, ctxs[op.op_index], mb)
             for op in reversed(self.ops[i:j]):
                 self._run(op, "bwd", op.bwd, genv, ctxs.pop(op.op_index), mb)
+                if self.after_op_backward is not None:
+                    self.after_op_backward(op.op_index)
         keep = {name for name, *_ in self.input_spec}
         return {k: v for k, v in genv.items() if k in keep and isinstance(v, torch.Tensor)}
 

@@ -232,10 +232,24 @@ class GradientBucketExecutor:
             self.unpack(bucket, payload, normalization_scale)
         self.collectives_issued += 1
 
-    def execute(self, normalization_scale=1.0):
+    def bucket_first_op(self, bucket) -> int:
+        """Smallest global op index among the parameters of a bucket: backward visits ops in decreasing
+        index order, so once that op's backward has run every gradient of the bucket is final."""
+        return min(self._descriptors[self._specs[pl.fragment_id].logical_param_id].global_op_index
+                   for pl in bucket.placements)
+
+    def needs_reduction(self, bucket) -> bool:
+        return len(self._groups[bucket.process_group_id].ranks) > 1
+
+    def uses_peer_backend(self, bucket) -> bool:
+        return self._peer is not None and self._peer.handles(bucket)
+
+    def execute(self, normalization_scale=1.0, skip=()):
+        """Run all buckets of this rank in plan order, except those in `skip` (already reduced)."""
         if self._evidence is not None:
             self._evidence.begin_execution(normalization_scale)
         for bucket in self._my_buckets:
-            self.execute_bucket(bucket, normalization_scale)
+            if bucket.bucket_id not in skip:
+                self.execute_bucket(bucket, normalization_scale)
         if self._evidence is not None:
             self._evidence.finish_execution()

@@ -170,6 +170,37 @@ class TrainEngine:
         self.grad_sync.synchronize_parameters(lambda t, src, handle: self.coll.broadcast(t, src, group=handle))
         groups = {g.process_group_id: g for g in self.grad_sync.plan.process_groups}
         self._needs_reduction = any(len(groups[b.process_group_id].ranks) > 1 for b in self.grad_sync.executor.buckets)
+        self._setup_grad_overlap()
+
+    # ------------------------------------------------------------------ gradient sync overlapped with backward
+    def _setup_grad_overlap(self):
+        """Buckets whose reduction runs on a side stream as soon as the last micro-batch's backward
+        has passed their first op (reference: strictly after backward, grad_sync/executor.py:199-261).
+        Only buckets served by the peer-memory kernel take part: a library collective launched from a
+        second stream could interleave differently with the main stream's collectives on other ranks."""
+        a, ex = self.args, self.grad_sync.executor
+        self._overlap_by_op, self._overlap_done = {}, set()
+        self._sync_stream = None
+        if (not getattr(a, "overlap_grad_sync", True) or self.device.type != "cuda"
+                or getattr(a, "grad_sync_evidence_dir", None) or getattr(a, "grad_sync_runtime_evidence_dir", None)):
+            return
+        for b in ex.buckets:
+            if ex.needs_reduction(b) and ex.uses_peer_backend(b):
+                self._overlap_by_op.setdefault(ex.bucket_first_op(b), []).append(b)
+        if self._overlap_by_op:
+            self._sync_stream = torch.cuda.Stream(device=self.device)
+
+    def _reduce_ready_buckets(self, op_index: int) -> None:
+        buckets = self._overlap_by_op.get(op_index)
+        if not buckets:
+            return
+        ready = torch.cuda.Event()
+        ready.record()
+        self._sync_stream.wait_event(ready)
+        with torch.cuda.stream(self._sync_stream):
+            for b in buckets:
+                self.grad_sync.executor.execute_bucket(b, 1.0)
+                self._overlap_done.add(b.bucket_id)
 
     def _owned_ranges(self):
         """(offset, numel) ranges of the flat gradient buffer whose norm this rank is responsible for."""
@@ -252,7 +283,14 @@ class TrainEngine:
             rec = self.stage._contexts[mb_index]["mb"]
             scale = self.scaler.value() if self.scaler is not None else 1.0
             grad_outputs = {"output": rec.loss_mask * (scale / self.args.nominal_global_loss_scale)}
-        return self.stage.backward(mb_index, grad_outputs or {})
+        last = self._sync_stream is not None and mb_index == self.pstate.num_microbatches - 1
+        if last:
+            self.stage.after_op_backward = self._reduce_ready_buckets
+        try:
+            return self.stage.backward(mb_index, grad_outputs or {})
+        finally:
+            if last:
+                self.stage.after_op_backward = None
 
     # ------------------------------------------------------------------ one iteration
     def train_step(self, sync: Optional[bool] = None) -> Dict[str, object]:
@@ -275,7 +313,10 @@ class TrainEngine:
         if evidence_dir:
             self._evidence("pre_sync", evidence_dir)
         if self._needs_reduction:
-            self.grad_sync.execute(1.0)
+            if self._sync_stream is not None:
+                torch.cuda.current_stream().wait_stream(self._sync_stream)
+            self.grad_sync.executor.execute(1.0, skip=self._overlap_done)
+            self._overlap_done = set()
         self.optimizer.set_grad_factor(normalization)
         if evidence_dir:
             self._evidence("post_sync", evidence_dir, grad_factor=float(self.optimizer.ctrl[2]))
