@@ -23,6 +23,23 @@ MAX_TILES = 8192
 RING = 4
 
 
+def reduce_scatter_schedule(cta: int, grid: int, it: int, tiles_m: int, tiles_n: int, world: int, group_m: int = 16):
+    """Host mirror of the device tile schedule of the fused GEMM + reduce-scatter (`sched_tile` in
+    csrc/gemm_sm100.cu): the it-th tile of CTA `cta` as (owner, tile row, tile column), or None past
+    the end. Within one `it`, the CTAs W * j + r cover, for every owner, G / W consecutive tiles of
+    that owner's row block, so a CTA's tiles alternate between owners and every tile is visited once."""
+    rows_per = tiles_m // world
+    vp = it * (grid // world) + cta // world
+    if vp >= rows_per * tiles_n:
+        return None
+    per_band = group_m * tiles_n
+    band, r = divmod(vp, per_band)
+    rows = min(group_m, rows_per - band * group_m)
+    tn, rr = divmod(r, rows)
+    owner = (cta + it) % world
+    return owner, owner * rows_per + band * group_m + rr, tn
+
+
 class FusedTPBackend:
     def __init__(self, group_ranks, my_rank, group, device, max_tokens: int, hidden: int, dtype):
         self.group, self.device, self.dtype = group, torch.device(device), dtype
