@@ -578,3 +578,27 @@ def flash_attention(q, k, v, scale=None, causal=True):
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     return _FlashAttnFn.apply(q, k, v, float(scale), bool(causal))
+
+
+def unfused_attention(q, k, v, scale=None, causal=True, dropout_p=0.0, seed=0, offset=0):
+    """Attention as the four ops of the 13-op layer manifest: scores (batched GEMM) -> fused
+    scale + causal-mask softmax -> dropout -> context (batched GEMM). q, k, v: [b, s, h, d]; returns
+    [b, s, h, d]. The softmax is this library's kernel; the two batched GEMMs are torch.baddbmm /
+    torch.bmm, as in the reference (eth/runtime/megatron/model/flex_ops.py:1229-1233 scores,
+    :1246-1330 softmax, :1332-1374 dropout, :1502 context). The 10-op manifest replaces all four by
+    `flash_attention`; this path exists for configs and profiles written against the older manifest."""
+    b, s, h, d = q.shape
+    scale = float(scale) if scale is not None else d ** -0.5
+    qh = q.permute(0, 2, 1, 3).reshape(b * h, s, d)
+    kh = k.permute(0, 2, 1, 3).reshape(b * h, s, d)
+    vh = v.permute(0, 2, 1, 3).reshape(b * h, s, d)
+    scores = torch.bmm(qh, kh.transpose(1, 2))
+    if causal:
+        probs = scaled_upper_triang_masked_softmax(scores, scale)
+    else:
+        probs = scaled_softmax(scores.view(b, h, s, s), scale).view(b * h, s, s)
+    if dropout_p > 0:
+        keep = _keep_mask_ref(probs.shape, dropout_p, seed, offset, probs.device)
+        probs = torch.where(keep, probs / (1.0 - dropout_p), torch.zeros_like(probs))
+    ctx = torch.bmm(probs, vh)
+    return ctx.view(b, h, s, d).permute(0, 2, 1, 3).contiguous()
