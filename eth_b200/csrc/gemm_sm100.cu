@@ -501,6 +501,179 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, uint32_t taddr,
   }
 }
 
+// Tile schedule of one CTA as the fused all-reduce sees it. `vcta` numbers the CTAs of the grid; in
+// the CTA-pair kernel each CTA of a pair is its own virtual CTA (it publishes and reduces the
+// 128-row half tiles it computes).
+struct CommSched {
+  int vcta, G, tiles_m, tiles_n;   // tiles_m in 128-row units
+  bool pair;
+  int pair_index, num_pairs, cta_in_pair;
+  __device__ __forceinline__ int count(const GemmArgs& p) const {
+    if (pair) {
+      const int n2 = ((tiles_m + 1) / 2) * tiles_n;
+      return pair_index < n2 ? (n2 - pair_index + num_pairs - 1) / num_pairs : 0;
+    }
+    return sched_count(p, vcta, G, tiles_m, tiles_n);
+  }
+  __device__ __forceinline__ bool tile(const GemmArgs& p, int it, int& tm, int& tn) const {
+    if (pair) {
+      const int tiles_m2 = (tiles_m + 1) / 2;
+      const int t2 = pair_index + it * num_pairs;
+      if (t2 >= tiles_m2 * tiles_n) return false;
+      int tm2;
+      tile_coords(t2, tiles_m2, tiles_n, tm2, tn);
+      tm = 2 * tm2 + cta_in_pair;
+      return true;
+    }
+    return sched_tile(p, vcta, G, it, tiles_m, tiles_n, tm, tn);
+  }
+};
+
+// Publisher of the fused all-reduce / reduce-scatter (one thread). System-scope fences wait for every
+// outstanding NVLink store of the SM (microseconds); the epilogue warps therefore never fence: they
+// bump a shared-memory counter after the stores of a tile and carry on, and this thread issues the
+// (cumulative) fence and writes the flags.
+__device__ __forceinline__ void comm_publisher(const GemmArgs& p, const CommSched& cs, Barriers* bars) {
+  const GemmComm& cm = p.comm;
+  const int W = cm.world, me = cm.rank;
+  const int n_my = cs.count(p);
+  const int first_owned = ((me - (cs.vcta % W)) + W) % W;
+  const int n_red = n_my > first_owned ? (n_my - first_owned + W - 1) / W : 0;
+  int pa = 0, pr = 0;
+  uint64_t t0 = globaltimer_ns();
+  while (pa < n_my || pr < n_red) {
+    bool progressed = false;
+    if (pa < n_my && counter_reached(&bars->pub_count, (kEpiThreads / 32) * (pa + 1))) {
+      const int o = (cs.vcta + pa) % W;
+      if (o != me) {
+        if (!(cm.debug & 1)) __threadfence_system();
+        st_release_sys(cm.flags[o] + (cs.vcta + pa * cs.G) * kGemmMaxPeers + me, cm.epoch);
+      }
+      ++pa;
+      progressed = true;
+    }
+    if (pr < n_red && counter_reached(&bars->rpub_count, (kEpiThreads / 32) * (pr + 1))) {
+      const int it = first_owned + pr * W;
+      if (!(cm.debug & 1)) __threadfence_system();
+      for (int d = 0; d < W; ++d)
+        if (d != me)
+          st_release_sys(cm.flags[d] + cm.max_tiles * kGemmMaxPeers + (cs.vcta + it * cs.G), cm.epoch);
+      ++pr;
+      progressed = true;
+    }
+    if (progressed) {
+      t0 = globaltimer_ns();
+    } else {
+      __nanosleep(64);
+      if (globaltimer_ns() - t0 > ETHB_WAIT_NS) {
+        if (p.status) atomicCAS(p.status, 0, kStatusTimeoutGridFlag);
+        break;
+      }
+    }
+  }
+}
+
+// Epilogue of the fused all-reduce / reduce-scatter (the 8 epilogue warps of a CTA). Ownership
+// alternates along each CTA's own tile list (tile index it -> rank (vcta + it) % W), so every CTA
+// reduces 1 / W of what it computes. Publishing (fence + flag) is left to the publisher thread;
+// `pub_count` counts partial tiles stored, `rpub_count` owned tiles reduced.
+template <int BN>
+__device__ __forceinline__ void comm_epilogue(const GemmArgs& p, const CommSched& cs, Barriers* bars,
+                                              uint32_t tmem_base, uint8_t* epi_smem, int warp, int lane) {
+  const GemmComm& cm = p.comm;
+  const int quarter = warp & 3;
+  const int col_half = (warp - 2) >> 2;
+  const int row_in_tile = quarter * 32 + lane;
+  const int tid_e = threadIdx.x - 64;
+  const int W = cm.world, me = cm.rank;
+  const int slots = (cs.tiles_m * cs.tiles_n + W - 1) / W + cs.G;
+  int* my_flags = cm.flags[me];
+  __shared__ int s_ready;
+  const int n_my = cs.count(p);
+  auto owner_of = [&](int it) { return (cs.vcta + it) % W; };
+  // staging slot of the it-th tile of this CTA inside its owner's area: slots are per CTA
+  auto slot_of = [&](int it) { return cs.vcta + (it / W) * cs.G; };
+  int red = 0, drained = 0;
+  bool ok = true;
+  auto reduce_one = [&](int it) {
+    int rtm, rtn;
+    if (!(cm.debug & 4) && cs.tile(p, it, rtm, rtn))
+      comm_reduce_tile<BN>(p, rtm, rtn, slot_of(it), slots, quarter, col_half, lane,
+                           epi_smem + (warp - 2) * 4096);
+    warp_arrive(&bars->rpub_count, lane);
+  };
+  for (int it = 0; it < n_my && ok; ++it) {
+    const int owner = owner_of(it), slot = slot_of(it);
+    const int acc = it & 1;
+    const uint32_t acc_phase = (it >> 1) & 1;
+    if (!mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) {
+      ok = false;
+      break;
+    }
+    tc_fence_after();
+    // phase A: this rank's partial tile -> the owner's staging area (a peer store unless owned)
+    uint16_t* dst = reinterpret_cast<uint16_t*>(cm.stage[owner]) +
+                    (static_cast<int64_t>(me) * slots + slot) * (BM * BN);
+    const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+    for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
+      uint32_t r[32];
+      __syncwarp();
+      tmem_ld_32x32b_x32(taddr + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack2(__uint_as_float(r[q * 8 + 0]) * p.alpha, __uint_as_float(r[q * 8 + 1]) * p.alpha, p.ab_dtype);
+        o.y = pack2(__uint_as_float(r[q * 8 + 2]) * p.alpha, __uint_as_float(r[q * 8 + 3]) * p.alpha, p.ab_dtype);
+        o.z = pack2(__uint_as_float(r[q * 8 + 4]) * p.alpha, __uint_as_float(r[q * 8 + 5]) * p.alpha, p.ab_dtype);
+        o.w = pack2(__uint_as_float(r[q * 8 + 6]) * p.alpha, __uint_as_float(r[q * 8 + 7]) * p.alpha, p.ab_dtype);
+        *reinterpret_cast<uint4*>(dst + stage_piece_offset(c, q, row_in_tile)) = o;
+      }
+    }
+    warp_arrive(&bars->pub_count, lane);
+    tc_fence_before();
+    if (cs.pair)
+      mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
+    else
+      mbar_arrive(&bars->tmem_empty[acc]);
+    drained = it + 1;
+    // phase B (opportunistic): reduce owned tiles whose peer partials have all arrived
+    while (red < drained) {
+      if (owner_of(red) != me) { ++red; continue; }
+      const int t2 = cs.vcta + red * cs.G;
+      if (tid_e == 0) {
+        int ready = 1;
+        for (int s = 0; s < W; ++s)
+          if (s != me && ld_acquire_sys(my_flags + t2 * kGemmMaxPeers + s) < cm.epoch) ready = 0;
+        s_ready = ready;
+      }
+      epi_bar_sync();
+      const int ready = s_ready;
+      epi_bar_sync();
+      if (!ready) break;
+      reduce_one(red);
+      ++red;
+    }
+  }
+  // drain: remaining owned tiles, now with (bounded) blocking waits
+  while (ok && red < n_my) {
+    if (owner_of(red) == me) {
+      const int t2 = cs.vcta + red * cs.G;
+      if (tid_e < W && tid_e != me)
+        wait_flag_ge(my_flags + t2 * kGemmMaxPeers + tid_e, cm.epoch, p.status);
+      epi_bar_sync();
+      reduce_one(red);
+    }
+    ++red;
+  }
+  // the tiles owned by peers must have landed in this rank's output before the kernel ends
+  for (int i = tid_e; i < n_my && ok; i += kEpiThreads) {
+    if (owner_of(i) != me && !(cm.debug & 4))
+      wait_flag_ge(my_flags + cm.max_tiles * kGemmMaxPeers + (cs.vcta + i * cs.G), cm.epoch, p.status);
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
@@ -693,144 +866,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
     }
   } else if (warp == kPublisherWarp) {
-    // ---------------------------------------------- publisher of the fused all-reduce
-    // System-scope fences wait for every outstanding NVLink store of the SM (microseconds). The
-    // epilogue warps therefore never fence: they arrive on a CTA-local mbarrier after the stores of
-    // a tile and carry on (one counter increment per warp); this thread then issues the (cumulative)
-    // fence and writes the flags.
     if (p.comm.world > 1 && elect_one()) {
-      const GemmComm& cm = p.comm;
-      const int W = cm.world, me = cm.rank;
-      const int n_my = sched_count(p, blockIdx.x, gridDim.x, tiles_m, tiles_n);
-      const int first_owned = ((me - static_cast<int>(blockIdx.x % W)) + W) % W;
-      const int n_red = n_my > first_owned ? (n_my - first_owned + W - 1) / W : 0;
-      int pa = 0, pr = 0;
-      uint64_t t0 = globaltimer_ns();
-      while (pa < n_my || pr < n_red) {
-        bool progressed = false;
-        if (pa < n_my && counter_reached(&bars->pub_count, (kEpiThreads / 32) * (pa + 1))) {
-          const int o = (blockIdx.x + pa) % W;
-          if (o != me) {
-            if (!(cm.debug & 1)) __threadfence_system();
-            st_release_sys(cm.flags[o] + (blockIdx.x + pa * gridDim.x) * kGemmMaxPeers + me, cm.epoch);
-          }
-          ++pa;
-          progressed = true;
-        }
-        if (pr < n_red && counter_reached(&bars->rpub_count, (kEpiThreads / 32) * (pr + 1))) {
-          const int it = first_owned + pr * W;
-          if (!(cm.debug & 1)) __threadfence_system();
-          for (int d = 0; d < W; ++d)
-            if (d != me)
-              st_release_sys(cm.flags[d] + cm.max_tiles * kGemmMaxPeers + (blockIdx.x + it * gridDim.x), cm.epoch);
-          ++pr;
-          progressed = true;
-        }
-        if (progressed) {
-          t0 = globaltimer_ns();
-        } else {
-          __nanosleep(64);
-          if (globaltimer_ns() - t0 > ETHB_WAIT_NS) {
-            if (p.status) atomicCAS(p.status, 0, kStatusTimeoutGridFlag);
-            break;
-          }
-        }
-      }
+      const CommSched cs{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), tiles_m, tiles_n, false, 0, 0, 0};
+      comm_publisher(p, cs, bars);
     }
   } else if (p.comm.world > 1 && p.comm.mode != 2) {
-    // ---------------------------------------------- epilogue fused with the TP all-reduce
-    // Ownership alternates along each CTA's own tile list (tile index it -> rank (cta + it) % W),
-    // so every CTA reduces 1/W of what it computes. Publishing (fence + flag) is left to the
-    // publisher warp; `pub_count` counts partial tiles stored, `rpub_count` owned tiles reduced.
-    const GemmComm& cm = p.comm;
-    const int quarter = warp & 3;
-    const int col_half = (warp - 2) >> 2;
-    const int row_in_tile = quarter * 32 + lane;
-    const int tid_e = threadIdx.x - 64;
-    const int W = cm.world, me = cm.rank;
-    const int slots = (num_tiles + W - 1) / W + static_cast<int>(gridDim.x);
-    int* my_flags = cm.flags[me];
-    __shared__ int s_ready;
-    const int n_my = sched_count(p, blockIdx.x, gridDim.x, tiles_m, tiles_n);
-    auto owner_of = [&](int it) { return static_cast<int>((blockIdx.x + it) % W); };
-    // staging slot of the it-th tile of this CTA inside its owner's area: slots are per CTA
-    auto slot_of = [&](int it) { return static_cast<int>(blockIdx.x) + (it / W) * static_cast<int>(gridDim.x); };
-    int red = 0, drained = 0;
-    bool ok = true;
-    auto reduce_one = [&](int it) {
-      int rtm, rtn;
-      if (!(cm.debug & 4) && sched_tile(p, blockIdx.x, gridDim.x, it, tiles_m, tiles_n, rtm, rtn))
-        comm_reduce_tile<BN>(p, rtm, rtn, slot_of(it), slots, quarter, col_half, lane,
-                             epi_smem + (warp - 2) * 4096);
-      warp_arrive(&bars->rpub_count, lane);
-    };
-    for (int it = 0; it < n_my && ok; ++it) {
-      const int owner = owner_of(it), slot = slot_of(it);
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      // phase A: this rank's partial tile -> the owner's staging area (a peer store unless owned)
-      uint16_t* dst = reinterpret_cast<uint16_t*>(cm.stage[owner]) +
-                      (static_cast<int64_t>(me) * slots + slot) * (BM * BN);
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 o;
-          o.x = pack2(__uint_as_float(r[q * 8 + 0]) * p.alpha, __uint_as_float(r[q * 8 + 1]) * p.alpha, p.ab_dtype);
-          o.y = pack2(__uint_as_float(r[q * 8 + 2]) * p.alpha, __uint_as_float(r[q * 8 + 3]) * p.alpha, p.ab_dtype);
-          o.z = pack2(__uint_as_float(r[q * 8 + 4]) * p.alpha, __uint_as_float(r[q * 8 + 5]) * p.alpha, p.ab_dtype);
-          o.w = pack2(__uint_as_float(r[q * 8 + 6]) * p.alpha, __uint_as_float(r[q * 8 + 7]) * p.alpha, p.ab_dtype);
-          *reinterpret_cast<uint4*>(dst + stage_piece_offset(c, q, row_in_tile)) = o;
-        }
-      }
-      warp_arrive(&bars->pub_count, lane);
-      tc_fence_before();
-      mbar_arrive(&bars->tmem_empty[acc]);
-      drained = it + 1;
-      // phase B (opportunistic): reduce owned tiles whose peer partials have all arrived
-      while (red < drained) {
-        if (owner_of(red) != me) { ++red; continue; }
-        const int t2 = blockIdx.x + red * gridDim.x;
-        if (tid_e == 0) {
-          int ready = 1;
-          for (int s = 0; s < W; ++s)
-            if (s != me && ld_acquire_sys(my_flags + t2 * kGemmMaxPeers + s) < cm.epoch) ready = 0;
-          s_ready = ready;
-        }
-        epi_bar_sync();
-        const int ready = s_ready;
-        epi_bar_sync();
-        if (!ready) break;
-        reduce_one(red);
-        ++red;
-      }
-    }
-    // drain: remaining owned tiles, now with (bounded) blocking waits
-    while (ok && red < n_my) {
-      if (owner_of(red) == me) {
-        const int t2 = blockIdx.x + red * gridDim.x;
-        if (tid_e < W && tid_e != me)
-          wait_flag_ge(my_flags + t2 * kGemmMaxPeers + tid_e, cm.epoch, p.status);
-        epi_bar_sync();
-        reduce_one(red);
-      }
-      ++red;
-    }
-    // the tiles owned by peers must have landed in this rank's output before the kernel ends
-    for (int i = tid_e; i < n_my && ok; i += kEpiThreads) {
-      if (owner_of(i) != me && !(cm.debug & 4))
-        wait_flag_ge(my_flags + cm.max_tiles * kGemmMaxPeers + (blockIdx.x + i * gridDim.x), cm.epoch, p.status);
-    }
+    const CommSched cs{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), tiles_m, tiles_n, false, 0, 0, 0};
+    comm_epilogue<BN>(p, cs, bars, tmem_base, epi_smem, warp, lane);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
@@ -880,7 +922,7 @@ template <int BN> struct PairCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kEpiBytes;
 };
 
-constexpr int kPairThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
+constexpr int kPairThreads = 352;      // producer warp, MMA warp, 8 epilogue warps, publisher warp
 constexpr int kPairEpiThreads = 256;
 
 template <int BN>
@@ -912,6 +954,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       mbar_init(&bars->tmem_full[a], 1);
       mbar_init(&bars->tmem_empty[a], 2 * kPairEpiThreads);
     }
+    bars->pub_count = 0;
+    bars->rpub_count = 0;
     fence_mbar_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_b);
@@ -1007,6 +1051,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
         if (ok) tc_commit_pair(&bars->tmem_full[acc], 3);
       }
     }
+  } else if (warp == kPublisherWarp) {
+    if (p.comm.world > 1 && elect_one()) {
+      const CommSched cs{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), (p.M + BM - 1) / BM, tiles_n,
+                         true, pair, num_pairs, static_cast<int>(cta)};
+      comm_publisher(p, cs, bars);
+    }
+  } else if (p.comm.world > 1) {
+    // ------------------------------------------------------------------ fused all-reduce epilogue: every CTA of
+    // the pair publishes and reduces the 128-row half tiles it computes, as its own virtual CTA
+    const CommSched cs{static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), (p.M + BM - 1) / BM, tiles_n,
+                       true, pair, num_pairs, static_cast<int>(cta)};
+    comm_epilogue<BN>(p, cs, bars, tmem_base, smem + C::kStages * C::kStageBytes + 256, warp, lane);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
     // A warp may only touch the TMEM lane quarter (warp % 4); two warps share each quarter and
@@ -1214,6 +1270,16 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
                                        : resident_pairs<BN>();
   if (max_pairs <= 0) return cudaErrorLaunchOutOfResources;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  if (a.comm.world > 1) {
+    const int W = a.comm.world;
+    const int half_tiles = 2 * tiles;
+    const int64_t slots = (half_tiles + W - 1) / W + 2 * pairs;
+    ETHB_RETURN_IF(a.comm.mode != 0, cudaErrorInvalidValue, "CTA-pair kernel: only the all-reduce mode is fused");
+    ETHB_RETURN_IF(half_tiles + 2 * pairs > a.comm.max_tiles, cudaErrorInvalidValue,
+                   "fused all-reduce: more tiles than flags");
+    ETHB_RETURN_IF(slots * W * BM * BN > a.comm.stage_elems, cudaErrorInvalidValue,
+                   "fused all-reduce: staging area too small");
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kPairThreads);
@@ -1245,12 +1311,14 @@ cudaError_t gemm_tcgen05(const GemmArgs& a, cudaStream_t stream) {
                    cudaErrorInvalidValue, "fused all-reduce: unsupported epilogue");
   }
   const int variant = g_gemm_variant.load();
-  if (a.comm.world <= 1 && variant >= 3) return variant == 3 ? launch_pair<128>(a, stream) : launch_pair<256>(a, stream);
+  if ((a.comm.world <= 1 || a.comm.mode == 0) && variant >= 3)
+    return variant == 3 ? launch_pair<128>(a, stream) : launch_pair<256>(a, stream);
   if (variant == 1) return launch<128>(a, stream);
   if (variant == 2 && a.N > 128) return launch<256>(a, stream);
   // Plain GEMMs wider than one 128-column tile run on CTA pairs (256 x 256 tiles): measured faster
   // than either single-CTA tile on every shape of the GPT layers.
-  if (variant == 0 && a.comm.world <= 1 && a.N > 128 && a.M > 128 && resident_pairs<256>() > 0)
+  if (variant == 0 && (a.comm.world <= 1 || a.comm.mode == 0) && a.N > 128 && a.M > 128 &&
+      resident_pairs<256>() > 0)
     return launch_pair<256>(a, stream);
   // Pick the tile width that minimises (waves x cost per wave).
   const int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
