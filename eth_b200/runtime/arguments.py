@@ -117,9 +117,12 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--grad-sync-mode", default="tensor", choices=["tensor", "block"],
                    help="One collective per gradient fragment, or block-wise buckets.")
     g.add_argument("--grad-sync-bucket-size-mb", type=int, default=32, help="Bucket cap in MiB for block mode.")
-    g.add_argument("--no-overlap-grad-sync", dest="overlap_grad_sync", action="store_false",
-                   help="Reduce gradient buckets only after the whole backward pass (default: buckets served by the "
-                        "peer-memory kernel start as soon as the last micro-batch's backward has produced them).")
+    g.add_argument("--overlap-grad-sync", action="store_true",
+                   help="Start the reduction of a gradient bucket on a side stream as soon as the last micro-batch's "
+                        "backward has produced it (peer-memory buckets only). Off by default: the reduction kernel "
+                        "waits for its data-parallel peer while it holds SM resources, and when it cannot share an SM "
+                        "with the persistent GEMM kernels, tensor-parallel and pipeline waits of other ranks can close "
+                        "a cycle that only the bounded waits break. Safe for pure data parallelism.")
     g.add_argument("--grad-sync-backend", default="auto", choices=["auto", "collective", "peer"],
                    help="Reduction backend: torch.distributed all-reduce or the peer-memory kernel.")
     g.add_argument("--grad-sync-dump-plan", type=str, default=None, help="Write the gradient sync plan as JSON.")

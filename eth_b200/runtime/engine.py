@@ -177,11 +177,14 @@ class TrainEngine:
         """Buckets whose reduction runs on a side stream as soon as the last micro-batch's backward
         has passed their first op (reference: strictly after backward, grad_sync/executor.py:199-261).
         Only buckets served by the peer-memory kernel take part: a library collective launched from a
-        second stream could interleave differently with the main stream's collectives on other ranks."""
+        second stream could interleave differently with the main stream's collectives on other ranks.
+        Opt-in (`--overlap-grad-sync`): with tensor or pipeline parallelism a reduction kernel spinning
+        for its data-parallel peer can keep the next GEMM of its own rank off the SMs while that peer
+        transitively waits for this rank -- measured on PP2 x TP2 x DP2 as bounded-wait timeouts."""
         a, ex = self.args, self.grad_sync.executor
         self._overlap_by_op, self._overlap_done = {}, set()
         self._sync_stream = None
-        if (not getattr(a, "overlap_grad_sync", True) or self.device.type != "cuda"
+        if (not getattr(a, "overlap_grad_sync", False) or self.device.type != "cuda"
                 or getattr(a, "grad_sync_evidence_dir", None) or getattr(a, "grad_sync_runtime_evidence_dir", None)):
             return
         for b in ex.buckets:
