@@ -146,7 +146,8 @@ class TrainEngine:
                     from ..parallel.grad_sync.peer_backend import PeerReduceBackend
                     if not any(len(g.ranks) > 1 for g in plan.process_groups):
                         return None
-                    return PeerReduceBackend(plan, rank, self.coll, self.device)
+                    return PeerReduceBackend(plan, rank, self.coll, self.device,
+                                             max_group=8 if backend == "peer" else 2)
                 except Exception:
                     if backend == "peer":
                         raise
