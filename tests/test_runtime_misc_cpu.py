@@ -66,3 +66,15 @@ def test_eval_step_leaves_training_state_alone():
     assert torch.equal(params, eng.stage.param_buf)
     assert (eng.clock.global_data_cursor, eng.iteration) == (cursor, it)
     assert not eng.stage._contexts
+
+
+def test_unfused_attention_matches_reference_on_cpu():
+    from eth_b200.ops import functional as Fn
+    torch.manual_seed(3)
+    q, k, v = (torch.randn(2, 24, 3, 16) for _ in range(3))
+    for causal in (True, False):
+        got = Fn.unfused_attention(q, k, v, causal=causal)
+        ref = Fn.attention_ref(q, k, v, 16 ** -0.5, causal)
+        torch.testing.assert_close(got, ref, rtol=1e-5, atol=1e-5)
+    dropped = Fn.unfused_attention(q, k, v, dropout_p=0.5, seed=1, offset=2)
+    assert dropped.shape == q.shape and not torch.equal(dropped, Fn.unfused_attention(q, k, v))
