@@ -27,8 +27,10 @@ _WS = {}
 
 
 def _workspace(device, numel: int) -> torch.Tensor:
-    """Grow-only fp32 scratch per device (partial sums of LayerNorm-backward and column sums)."""
-    key = (device.type, device.index)
+    """Grow-only fp32 scratch per device and stream (partial sums of LayerNorm-backward and column sums)."""
+    # one scratch per (device, stream): kernels of different streams may run concurrently
+    stream = torch.cuda.current_stream(device).cuda_stream if device.type == "cuda" else 0
+    key = (device.type, device.index, stream)
     ws = _WS.get(key)
     if ws is None or ws.numel() < numel:
         ws = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)

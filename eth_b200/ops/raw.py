@@ -88,11 +88,50 @@ def linear_dgrad(dy, weight, gelu_pre=None):
     return gemm(dy, weight, b_mn=True)
 
 
-def linear_wgrad(dy, x, weight, bias=None):
-    """main_grad(W) += dy^T x ; main_grad(b) += colsum(dy)."""
+_WGRAD_STREAM = {}   # device index -> side stream for weight gradients (see enable_async_wgrad)
+
+
+def enable_async_wgrad(device, on: bool = True) -> None:
+    """Run weight-gradient GEMMs on a side stream. Nothing on the critical path of backward reads a
+    weight gradient, while the data-gradient GEMM of the same layer does lie on it; both are
+    persistent kernels of 3-4 waves, so when they may overlap the last, partly filled wave of one
+    runs beside the first wave of the other. Accumulation order per weight is kept (one side stream).
+    Call `join_async_wgrad` before anything reads `main_grad`."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        return
+    if on:
+        _WGRAD_STREAM.setdefault(dev.index, torch.cuda.Stream(device=dev))
+    else:
+        _WGRAD_STREAM.pop(dev.index, None)
+
+
+def join_async_wgrad(device) -> None:
+    dev = torch.device(device)
+    side = _WGRAD_STREAM.get(dev.index) if dev.type == "cuda" else None
+    if side is not None:
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+
+def _wgrad_now(dy, x, weight, bias):
     gemm(dy, x, a_mn=True, b_mn=True, out=_grad_of(weight).view(weight.shape), accumulate=True)
     if bias is not None:
         colsum(dy, out=_grad_of(bias).view(-1), accumulate=True)
+
+
+def linear_wgrad(dy, x, weight, bias=None):
+    """main_grad(W) += dy^T x ; main_grad(b) += colsum(dy)."""
+    side = _WGRAD_STREAM.get(dy.device.index) if dy.is_cuda else None
+    if side is None or getattr(dy, "_ethb_ring", False) or getattr(x, "_ethb_ring", False):
+        return _wgrad_now(dy, x, weight, bias)
+    ready = torch.cuda.Event()
+    ready.record()
+    side.wait_event(ready)
+    with torch.cuda.stream(side):
+        _wgrad_now(dy, x, weight, bias)
+    # the caching allocator must not hand these buffers out again before the side stream is done
+    dy.record_stream(side)
+    x.record_stream(side)
 
 
 # ---------------------------------------------------------------------------------- GeLU / dropout

@@ -117,6 +117,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--grad-sync-mode", default="tensor", choices=["tensor", "block"],
                    help="One collective per gradient fragment, or block-wise buckets.")
     g.add_argument("--grad-sync-bucket-size-mb", type=int, default=32, help="Bucket cap in MiB for block mode.")
+    g.add_argument("--no-async-wgrad", dest="async_wgrad", action="store_false",
+                   help="Run weight-gradient GEMMs on the main stream (default: on a side stream, so that their "
+                        "partly filled last wave overlaps the data-gradient GEMM of the same layer).")
     g.add_argument("--overlap-grad-sync", action="store_true",
                    help="Start the reduction of a gradient bucket on a side stream as soon as the last micro-batch's "
                         "backward has produced it (peer-memory buckets only). Off by default: the reduction kernel "

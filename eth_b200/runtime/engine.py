@@ -23,6 +23,7 @@ import torch.distributed as dist
 
 from ..models.gpt_ops import GPTModelConfig, TPComm
 from ..models.stage import GPTStage, MicroBatch
+from ..ops import raw as raw_ops
 from ..optim.grad_scaler import ConstantGradScaler, DynamicGradScaler
 from ..optim.lr import AnnealingLR
 from ..optim.optimizer import FlatMixedPrecisionAdam, coalesce_ranges
@@ -113,6 +114,8 @@ class TrainEngine:
         self.iteration = 0
         self._setup_grad_sync()
         self._setup_optimizer()
+        evidence = getattr(args, "grad_sync_evidence_dir", None) or getattr(args, "grad_sync_runtime_evidence_dir", None)
+        raw_ops.enable_async_wgrad(self.device, on=getattr(args, "async_wgrad", True) and not evidence)
         self.loss_acc = torch.zeros(2, dtype=torch.float32, device=self.device)
         self.last_stats: Dict[str, object] = {}
 
@@ -311,6 +314,7 @@ class TrainEngine:
             schedules.forward_backward_no_pipelining(self, n_mb)
         else:
             schedules.forward_backward_1f1b(self, n_mb)
+        raw_ops.join_async_wgrad(self.device)
         # global loss weight -> normalisation factor (device scalar)
         self.coll.all_reduce_sum(self.loss_acc)
         normalization = a.nominal_global_loss_scale / self.loss_acc[1]
