@@ -525,6 +525,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_bwd", &attn_bwd);
   m.def("launch_count", [] { return ethb::launch_count(); });
   m.def("set_gemm_variant", [](int v) { ethb::set_gemm_variant(v); });
+  m.def("set_gemm_tail_split", [](int on) { ethb::set_gemm_tail_split(on); });
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_open", &peer_open);
   m.def("peer_close", &peer_close);

@@ -35,6 +35,8 @@ int64_t launch_count() { return g_launches.load(); }
 void count_launch(int n) { g_launches.fetch_add(n); }
 static std::atomic<int> g_gemm_variant{0};
 void set_gemm_variant(int v) { g_gemm_variant.store(v); }
+static std::atomic<int> g_tail_split{1};
+void set_gemm_tail_split(int on) { g_tail_split.store(on); }
 static thread_local const char* g_error_detail = "";
 const char* last_error_detail() { return g_error_detail; }
 void set_error_detail(const char* where) { g_error_detail = where; }
@@ -925,10 +927,35 @@ template <int BN> struct PairCfg {
 constexpr int kPairThreads = 352;      // producer warp, MMA warp, 8 epilogue warps, publisher warp
 constexpr int kPairEpiThreads = 256;
 
+// Tile list of the CTA-pair kernel. The last `tail_split` tiles of the rasterised list are executed
+// as two 256 x (BN / 2) halves each: when the last wave of full tiles would leave most pairs idle,
+// the halves spread it over twice as many pairs and it takes about half as long.
+struct PairTile {
+  int tm, tn, n_off, half;
+};
+__device__ __forceinline__ bool pair_tile(int v, int num_tiles, int tail_split, int tiles_m, int tiles_n,
+                                          int half_width, PairTile& t) {
+  const int full = num_tiles - tail_split;
+  if (v >= full + 2 * tail_split) return false;
+  int tile = v;
+  t.n_off = 0;
+  t.half = 0;
+  if (v >= full) {
+    const int h = v - full;
+    tile = full + (h >> 1);
+    t.n_off = (h & 1) * half_width;
+    t.half = 1;
+  }
+  tile_coords(tile, tiles_m, tiles_n, t.tm, t.tn);
+  return true;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
-                         const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
+                         const __grid_constant__ CUtensorMap tma_b,
+                         const __grid_constant__ CUtensorMap tma_b_half, const GemmArgs p,
+                         const int tail_split) {
   using C = PairCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -974,11 +1001,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
-        const int m0 = tm * 2 * BM + static_cast<int>(cta) * BM;
-        const int n0 = tn * BN + static_cast<int>(cta) * (BN / 2);
+      PairTile t;
+      for (int v = pair; ok && pair_tile(v, num_tiles, tail_split, tiles_m, tiles_n, BN / 2, t); v += num_pairs) {
+        const int m0 = t.tm * 2 * BM + static_cast<int>(cta) * BM;
+        // this CTA's share of the B tile: BN / 2 rows of a full tile, BN / 4 rows of a half tile
+        const int n0 = t.tn * BN + t.n_off + static_cast<int>(cta) * (t.half ? BN / 4 : BN / 2);
+        const uint32_t stage_tx = t.half ? C::kABytes + C::kBBytes / 2 : C::kStageBytes;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) {
             ok = false;
@@ -986,7 +1014,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
           }
           uint8_t* sa = smem + stage * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
-          if (cta == 0) mbar_expect_tx(&bars->full[stage], 2 * C::kStageBytes);
+          if (cta == 0) mbar_expect_tx(&bars->full[stage], 2 * stage_tx);
           const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[stage]), 0);
           if (!p.a_mn) {
             tma_load_2d_pair(sa, &tma_a, full_leader, kb * BK, m0);
@@ -996,10 +1024,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
               tma_load_2d_pair(sa + j * 8192, &tma_a, full_leader, m0 + j * 64, kb * BK);
           }
           if (!p.b_mn) {
-            tma_load_2d_pair(sb, &tma_b, full_leader, kb * BK, n0);
+            tma_load_2d_pair(sb, t.half ? &tma_b_half : &tma_b, full_leader, kb * BK, n0);
           } else {
-#pragma unroll
-            for (int j = 0; j < BN / 128; ++j)
+            const int chunks = t.half ? BN / 256 : BN / 128;
+            for (int j = 0; j < chunks; ++j)
               tma_load_2d_pair(sb + j * 8192, &tma_b, full_leader, n0 + j * 64, kb * BK);
           }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
@@ -1015,12 +1043,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader only)
     if (cta == 0 && elect_one()) {
-      const uint32_t idesc = make_idesc_f16(p.ab_dtype == kBF16 ? 1 : 0, p.a_mn, p.b_mn, 2 * BM, BN);
+      const uint32_t idesc_full = make_idesc_f16(p.ab_dtype == kBF16 ? 1 : 0, p.a_mn, p.b_mn, 2 * BM, BN);
+      const uint32_t idesc_half = make_idesc_f16(p.ab_dtype == kBF16 ? 1 : 0, p.a_mn, p.b_mn, 2 * BM, BN / 2);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+      PairTile t;
+      for (int v = pair; ok && pair_tile(v, num_tiles, tail_split, tiles_m, tiles_n, BN / 2, t); v += num_pairs, ++it) {
+        const uint32_t idesc = t.half ? idesc_half : idesc_full;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutTmemEmpty)) {
@@ -1075,21 +1106,22 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     const bool staged = p.d_dtype != kF32 && !p.accumulate && (p.D2 != nullptr || p.aux_mode != kAuxNone);
     uint8_t* epi_smem = smem + C::kStages * C::kStageBytes + 256;
     int it = 0;
-    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
-      int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+    PairTile t;
+    for (int v = pair; pair_tile(v, num_tiles, tail_split, tiles_m, tiles_n, BN / 2, t); v += num_pairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait_relaxed(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      const int row_base = tm * 2 * BM + static_cast<int>(cta) * BM;
+      const int row_base = t.tm * 2 * BM + static_cast<int>(cta) * BM;
+      // 32-column chunks of the accumulator for this warp: half of the tile's (or half tile's) columns
+      const int chunks = t.half ? BN / 128 : BN / 64;
+      const int n_base = t.tn * BN + t.n_off;
       if (staged)
-        epilogue_tile_staged<BN>(p, taddr, row_base + quarter * 32, lane, tn * BN, col_half * (BN / 64),
-                                 (col_half + 1) * (BN / 64), epi_smem + (warp - 2) * 4096);
+        epilogue_tile_staged<BN>(p, taddr, row_base + quarter * 32, lane, n_base, col_half * chunks,
+                                 (col_half + 1) * chunks, epi_smem + (warp - 2) * 4096);
       else
-        epilogue_tile<BN>(p, taddr, row_base + row_in_tile, tn * BN, col_half * (BN / 64),
-                          (col_half + 1) * (BN / 64));
+        epilogue_tile<BN>(p, taddr, row_base + row_in_tile, n_base, col_half * chunks, (col_half + 1) * chunks);
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
     }
@@ -1258,6 +1290,11 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   else
     e = make_tmap_2d_16bit(&tb, a.B, a.ab_dtype, a.N, a.K, a.ldb, 64, BK);
   if (e != cudaSuccess) return e;
+  CUtensorMap tbh = tb;   // B rows of one CTA for a half tile (K-major B only; MN-major reuses `tb`)
+  if (!a.b_mn) {
+    e = make_tmap_2d_16bit(&tbh, a.B, a.ab_dtype, a.K, a.N, a.ldb, BK, BN / 4);
+    if (e != cudaSuccess) return e;
+  }
   static bool attr_set = false;
   if (!attr_set) {
     e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1280,6 +1317,12 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
     ETHB_RETURN_IF(slots * W * BM * BN > a.comm.stage_elems, cudaErrorInvalidValue,
                    "fused all-reduce: staging area too small");
   }
+  // Split the tiles of a last wave that fills at most half of the pairs into 256 x 128 halves.
+  int tail_split = 0;
+  if (BN == 256 && a.comm.world <= 1 && g_tail_split.load() && tiles > pairs) {
+    const int rest = tiles % pairs;
+    if (rest > 0 && 2 * rest <= pairs) tail_split = rest;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(kPairThreads);
@@ -1292,7 +1335,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<BN>, ta, tb, a);
+  e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<BN>, ta, tb, tbh, a, tail_split);
   count_launch();
   return e != cudaSuccess ? e : cudaGetLastError();
 }

@@ -70,6 +70,8 @@ cudaError_t gemm_tcgen05(const GemmArgs& args, cudaStream_t stream);
 // Kernel choice for plain GEMMs: 0 = automatic, 1 / 2 = one CTA per 128 x 128 / 128 x 256 tile,
 // 3 / 4 = CTA pair per 256 x 128 / 256 x 256 tile. Meant for tests and benchmarks.
 void set_gemm_variant(int v);
+// Splitting of a sparsely filled last wave of the CTA-pair kernel into half tiles (default on).
+void set_gemm_tail_split(int on);
 
 // Where the last failing launcher of this thread gave up (empty if none).
 void ensure_thread_context();

@@ -346,3 +346,39 @@ def test_dropout_bwd_colsum(rows, cols):
     assert _rel_err(db, exact) < (1e-5 if fused else 3e-3)
     zeros = (dx == 0).float().mean().item()
     assert abs(zeros - p) < 0.02
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [(8192, 2048, 256), (8192, 3072, 192), (4864, 4096, 128)])
+def test_gemm_tail_split_half_tiles(a_mn, b_mn, shape):
+    """Shapes whose last wave of 256 x 256 tiles is sparsely filled run that wave as 256 x 128 half
+    tiles; results must equal the unsplit schedule and the fp32 reference, with every epilogue."""
+    M, N, K = shape
+    torch.manual_seed(8)
+    dt = torch.bfloat16
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=dt)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=dt) * 0.1
+    bias = torch.randn(N, device=DEV, dtype=dt)
+    aux = torch.randn(M, N, device=DEV, dtype=dt)
+    outs = {}
+    for on in (1, 0):
+        native.lib().set_gemm_tail_split(on)
+        try:
+            plain = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias)
+            act = torch.empty_like(plain)
+            pre = torch.empty_like(plain)
+            ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=pre, bias=bias, gelu_out=act)
+            res = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, aux=aux, aux_mode=Fn.AUX_ADD)
+            acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
+            ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, accumulate=True)
+        finally:
+            native.lib().set_gemm_tail_split(1)
+        outs[on] = (plain, act, res, acc)
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    assert _rel_err(outs[1][0], ref + bias.float()) < 5e-3
+    assert _rel_err(outs[1][1], torch.nn.functional.gelu(ref + bias.float(), approximate="tanh")) < 1e-2
+    assert _rel_err(outs[1][2], ref + aux.float()) < 5e-3
+    assert _rel_err(outs[1][3], ref + 1.0) < 2e-3
+    for x, y in zip(outs[1], outs[0]):
+        assert torch.equal(x, y)
+    native.check_status()
