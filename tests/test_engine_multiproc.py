@@ -58,6 +58,7 @@ def _logical(results, pipeline=0, dp=0):
 LAYOUTS = {
     "tp2": (2, [make_pipe([N_OPS], [2], [1], gbs=8, mbs=4)]),
     "dp2": (2, [make_pipe([N_OPS], [1], [2], gbs=8, mbs=4)]),
+    "dp4": (4, [make_pipe([N_OPS], [1], [4], gbs=8, mbs=4)]),
     "pp2": (2, [make_pipe([11, N_OPS - 11], [1, 1], [1, 1], gbs=8, mbs=4)]),
     "pp2-midlayer-cut": (2, [make_pipe([6, N_OPS - 6], [1, 1], [1, 1], gbs=8, mbs=4)]),
     "pp2-tp2-to-dp2": (4, [make_pipe([11, N_OPS - 11], [2, 1], [1, 2], gbs=8, mbs=4)]),
