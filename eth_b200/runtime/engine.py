@@ -147,10 +147,10 @@ class TrainEngine:
             def peer_factory(plan, rank):
                 try:
                     from ..parallel.grad_sync.peer_backend import PeerReduceBackend
-                    if not any(len(g.ranks) > 1 for g in plan.process_groups):
-                        return None
-                    return PeerReduceBackend(plan, rank, self.coll, self.device,
-                                             max_group=8 if backend == "peer" else 2)
+                    max_group = 8 if backend == "peer" else 2
+                    if not any(1 < len(g.ranks) <= max_group for g in plan.process_groups):
+                        return None     # no group the peer kernel would serve: plain scratch + collectives
+                    return PeerReduceBackend(plan, rank, self.coll, self.device, max_group=max_group)
                 except Exception:
                     if backend == "peer":
                         raise
