@@ -50,7 +50,7 @@ def main(argv=None):
     from eth_b200.ops import native
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemm", "attn", "ln", "gemm_sweep"])
+    ap.add_argument("kind", choices=["gemm", "attn", "ln", "gemm_sweep", "elementwise"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -132,6 +132,28 @@ def main(argv=None):
         byts = 2.0 * x.numel() * x.element_size()
         out.append({"kernel": "ln_fwd", "rows": args.rows, "hidden": args.hidden, "ms_median": med,
                     "gbs": byts / med / 1e6, "frac_of_%s_hbm" % src: byts / med / 1e6 / hbm})
+    elif args.kind == "elementwise":
+        # the memory-bound kernels of a transformer layer on [rows, hidden]; bytes = algorithmic traffic
+        from eth_b200.ops import raw
+        rows, h = args.rows, args.hidden
+        x = torch.randn(rows, h, device="cuda", dtype=dt)
+        g = torch.ones(h, device="cuda", dtype=dt)
+        b = torch.zeros(h, device="cuda", dtype=dt)
+        g.main_grad = torch.zeros(h, device="cuda")
+        b.main_grad = torch.zeros(h, device="cuda")
+        _, mean, rstd = raw.ln_fwd(x, g, b, 1e-5)
+        dy, res = torch.randn_like(x), torch.randn_like(x)
+        bias = torch.zeros(h, device="cuda", dtype=dt)
+        nb = x.numel() * x.element_size()
+        cases = [("ln_fwd", lambda: raw.ln_fwd(x, g, b, 1e-5), 2 * nb),
+                 ("ln_bwd", lambda: raw.ln_bwd(dy, x, g, b, mean, rstd), 3 * nb),
+                 ("ln_bwd + residual gradient", lambda: raw.ln_bwd(dy, x, g, b, mean, rstd, residual_grad=res), 4 * nb),
+                 ("bias_dropout_add_fwd", lambda: raw.bias_dropout_add_fwd(x, bias, res, 0.1, 1, 2), 3 * nb),
+                 ("dropout_bwd + bias-gradient column sums", lambda: raw.dropout_bwd_colsum(dy, 0.1, 1, 2), 2 * nb)]
+        for name, fn, byts in cases:
+            med, best = time_fn(fn, args.warmup, args.repeat)
+            out.append({"kernel": name, "rows": rows, "hidden": h, "ms_median": med, "gbs": byts / med / 1e6,
+                        "frac_of_%s_hbm" % src: byts / med / 1e6 / hbm})
     for rec in out:
         print(json.dumps(rec))
     return out
