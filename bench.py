@@ -238,7 +238,7 @@ def run_ours(opts):
 
 def run_reference(opts):
     from baseline.reference_arm import run as run_ref
-    run_ref(opts, MODEL, LAYOUTS, SAMPLES_PER_GPU, MICRO_BATCH, VOCAB)
+    run_ref(opts, MODEL, LAYOUTS, SAMPLES_PER_GPU, MICRO_BATCH, VOCAB, clock_sampler_cls=ClockSampler)
 
 
 def main():

@@ -126,23 +126,30 @@ def load_checkpoint(engine, root: str) -> int:
             np.random.set_state(state["np_rng_state"])
             torch.set_rng_state(state["torch_rng_state"])
         ck = state.get("args", SimpleNamespace())
+        scaler = engine.optimizer.grad_scaler
         clock = [getattr(ck, "global_data_cursor", getattr(ck, "consumed_train_samples", 0)),
                  getattr(ck, "successful_optimizer_steps", iteration), 0 if finetune else state.get("iteration", iteration),
-                 engine.optimizer.step_count]
+                 engine.optimizer.step_count,
+                 scaler.state_dict() if scaler is not None else None,
+                 engine.lr_scheduler.state_dict()]
     else:
         clock = None
-    # every rank learns the clocks from rank 0 (a writer), then fragments are re-broadcast
+    # Every rank learns the clocks, the loss-scaler state and the schedule position from rank 0 (a
+    # writer); tensors follow through the fragment broadcasts below. Without the scaler state a
+    # resumed fp16 job would scale its loss by the saved value on the writers and by the initial
+    # value everywhere else, and the bucket sums would mix the two.
     box = [clock]
     if engine.coll.enabled:
         import torch.distributed as dist
         dist.broadcast_object_list(box, src=0)
-    cursor, steps, it, opt_steps = box[0]
+    cursor, steps, it, opt_steps, scaler_state, lr_state = box[0]
     engine.clock.global_data_cursor, engine.clock.successful_optimizer_steps = cursor, steps
     engine.optimizer.step_count = opt_steps
     engine.iteration = it
     if not is_writer(ps):
-        engine.lr_scheduler.num_steps = 0
-        engine.lr_scheduler.step(steps * args.total_gbs)
+        if engine.optimizer.grad_scaler is not None and scaler_state is not None:
+            engine.optimizer.grad_scaler.load_state_dict(scaler_state)
+        engine.lr_scheduler.load_state_dict(lr_state)
     bc = lambda t, src, handle: engine.coll.broadcast(t, src, group=handle)  # noqa: E731
     engine.grad_sync.synchronize_parameters(bc)
     engine.grad_sync.synchronize_optimizer_state(
