@@ -79,7 +79,7 @@ void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, cons
                     const OptTensor& aux, double alpha, const OptTensor& status,
                     const std::vector<int64_t>& stage_ptrs, const std::vector<int64_t>& out_ptrs,
                     const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, int64_t max_tiles,
-                    int64_t stage_elems, int64_t ldd, int64_t debug, int64_t mode) {
+                    int64_t stage_elems, int64_t ldd, int64_t mode) {
   need_cuda(a, "a"); need_cuda(b, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1);
   TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a/b dtype mismatch");
@@ -109,7 +109,6 @@ void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, cons
   g.comm.epoch = static_cast<int>(epoch);
   g.comm.max_tiles = static_cast<int>(max_tiles);
   g.comm.stage_elems = stage_elems;
-  g.comm.debug = static_cast<int>(debug);
   g.comm.mode = static_cast<int>(mode);
   for (size_t i = 0; i < w; ++i) {
     g.comm.stage[i] = reinterpret_cast<void*>(stage_ptrs[i]);

@@ -180,7 +180,8 @@ __device__ __forceinline__ int64_t stage_piece_offset(int c, int q, int row_in_t
 // through a per-warp shared-memory transpose so that global stores are 128-byte row segments.
 template <int BN>
 __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tm, int tn, int slot, int slots,
-                                                 int quarter, int col_half, int lane, uint8_t* warp_buf) {
+                                                 int quarter, int col_half, int lane, uint8_t* warp_buf,
+                                                 bool from_tmem = false, uint32_t taddr = 0) {
   const GemmComm& cm = p.comm;
   const int row_in_tile = quarter * 32 + lane;
   const int row = tm * BM + row_in_tile;
@@ -196,10 +197,20 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tm, int 
       const int c = cp * 2 + half;
       const int col0 = tn * BN + c * 32;
       float v[32];
+      if (from_tmem) {   // this rank's own partial is still in the accumulator (warp-wide load)
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+      }
 #pragma unroll 2
       for (int s = 0; s < cm.world; ++s) {
+        if (from_tmem && s == cm.rank) continue;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const uint4 u = __ldcg(reinterpret_cast<const uint4*>(base + s * src_stride +
@@ -273,9 +284,8 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tm, int 
                                     static_cast<int64_t>(grow - cm.rank * (p.M / cm.world)) * p.ldd + gcol) = o;
         } else {
           for (int dst = 0; dst < cm.world; ++dst)
-            if (!(cm.debug & 2) || dst == cm.rank)
-              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[dst]) +
-                                        static_cast<int64_t>(grow) * p.ldd + gcol) = o;
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cm.out[dst]) +
+                                      static_cast<int64_t>(grow) * p.ldd + gcol) = o;
         }
       }
     }
@@ -505,7 +515,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, uint32_t taddr,
 
 // Tile schedule of one CTA as the fused all-reduce sees it. `vcta` numbers the CTAs of the grid; in
 // the CTA-pair kernel each CTA of a pair is its own virtual CTA (it publishes and reduces the
-// 128-row half tiles it computes).
+// 128-row half tiles it computes). Ownership alternates along a CTA's tile list: tile index `it`
+// belongs to rank (okey + it) % W, where okey is the CTA number -- or the pair number, so that
+// both halves of a pair's tile have one owner and the pair can order its tiles by owner.
 struct CommSched {
   int vcta, G, tiles_m, tiles_n;   // tiles_m in 128-row units
   bool pair;
@@ -529,34 +541,66 @@ struct CommSched {
     }
     return sched_tile(p, vcta, G, it, tiles_m, tiles_n, tm, tn);
   }
+  __device__ __forceinline__ int okey() const { return pair ? pair_index : vcta; }
+  __device__ __forceinline__ int owner(int it, int W) const { return (okey() + it) % W; }
 };
+
+// Number of tiles of a list of n_my tiles that rank `me` owns, and the index of the first one.
+__device__ __forceinline__ int comm_owned(int okey, int n_my, int W, int me, int* first = nullptr) {
+  const int f = ((me - okey) % W + W) % W;
+  if (first) *first = f;
+  return n_my > f ? (n_my - f + W - 1) / W : 0;
+}
+
+// Processing order of a CTA's tile list in all-reduce mode: the j-th tile processed is list index
+// comm_order(j). Tiles owned by rank me+1 come first, then me+2, ..., and this rank's own tiles
+// last. Every rank therefore pushes its partials of a peer's tiles while that peer is still busy
+// with other ranks' tiles, and by the time a rank reaches its own tiles the peers' partials have
+// long landed in its staging area: it adds them to the accumulator it just computed and sends the
+// result out, so only that one transfer is left after the last MMA. Other modes keep list order.
+__device__ __forceinline__ int comm_order(const GemmComm& cm, int okey, int n_my, int j) {
+  if (cm.mode != 0) return j;
+  const int W = cm.world;
+  for (int g = 1; g <= W; ++g) {
+    int first;
+    const int cnt = comm_owned(okey, n_my, W, (cm.rank + g) % W, &first);
+    if (j < cnt) return first + j * W;
+    j -= cnt;
+  }
+  return n_my;
+}
 
 // Publisher of the fused all-reduce / reduce-scatter (one thread). System-scope fences wait for every
 // outstanding NVLink store of the SM (microseconds); the epilogue warps therefore never fence: they
 // bump a shared-memory counter after the stores of a tile and carry on, and this thread issues the
-// (cumulative) fence and writes the flags.
+// (cumulative) fence and writes the flags. `pub_count` counts partial tiles pushed to their owner
+// (all tiles in reduce-scatter mode, where a rank also stages its own), `rpub_count` owned tiles
+// whose result has been written.
 __device__ __forceinline__ void comm_publisher(const GemmArgs& p, const CommSched& cs, Barriers* bars) {
   const GemmComm& cm = p.comm;
   const int W = cm.world, me = cm.rank;
+  const bool ordered = cm.mode == 0;
   const int n_my = cs.count(p);
-  const int first_owned = ((me - (cs.vcta % W)) + W) % W;
-  const int n_red = n_my > first_owned ? (n_my - first_owned + W - 1) / W : 0;
+  int first_owned;
+  const int n_red = comm_owned(cs.okey(), n_my, W, me, &first_owned);
+  const int n_push = ordered ? n_my - n_red : n_my;
   int pa = 0, pr = 0;
   uint64_t t0 = globaltimer_ns();
-  while (pa < n_my || pr < n_red) {
+  while (pa < n_push || pr < n_red) {
     bool progressed = false;
-    if (pa < n_my && counter_reached(&bars->pub_count, (kEpiThreads / 32) * (pa + 1))) {
-      const int o = (cs.vcta + pa) % W;
+    if (pa < n_push && counter_reached(&bars->pub_count, (kEpiThreads / 32) * (pa + 1))) {
+      const int it = ordered ? comm_order(cm, cs.okey(), n_my, pa) : pa;
+      const int o = cs.owner(it, W);
       if (o != me) {
-        if (!(cm.debug & 1)) __threadfence_system();
-        st_release_sys(cm.flags[o] + (cs.vcta + pa * cs.G) * kGemmMaxPeers + me, cm.epoch);
+        __threadfence_system();
+        st_release_sys(cm.flags[o] + (cs.vcta + it * cs.G) * kGemmMaxPeers + me, cm.epoch);
       }
       ++pa;
       progressed = true;
     }
     if (pr < n_red && counter_reached(&bars->rpub_count, (kEpiThreads / 32) * (pr + 1))) {
-      const int it = first_owned + pr * W;
-      if (!(cm.debug & 1)) __threadfence_system();
+      const int it = first_owned + pr * W;   // own tiles are processed in list order in every mode
+      __threadfence_system();
       for (int d = 0; d < W; ++d)
         if (d != me)
           st_release_sys(cm.flags[d] + cm.max_tiles * kGemmMaxPeers + (cs.vcta + it * cs.G), cm.epoch);
@@ -575,10 +619,13 @@ __device__ __forceinline__ void comm_publisher(const GemmArgs& p, const CommSche
   }
 }
 
-// Epilogue of the fused all-reduce / reduce-scatter (the 8 epilogue warps of a CTA). Ownership
-// alternates along each CTA's own tile list (tile index it -> rank (vcta + it) % W), so every CTA
-// reduces 1 / W of what it computes. Publishing (fence + flag) is left to the publisher thread;
-// `pub_count` counts partial tiles stored, `rpub_count` owned tiles reduced.
+// Epilogue of the fused all-reduce / reduce-scatter (the 8 epilogue warps of a CTA). Every CTA
+// reduces 1 / W of what it computes. Publishing (fence + flag) is left to the publisher thread.
+//   all-reduce: tiles are processed in `comm_order`. A peer's tile: the accumulator goes to the
+//     owner's staging area. An own tile: wait (bounded; normally not at all) for the peers'
+//     partials, add them to the accumulator and write the result into every rank's output.
+//   reduce-scatter: list order; every partial, the own one too, is staged, and owned tiles are
+//     reduced from the staging area as soon as the peers' flags are seen.
 template <int BN>
 __device__ __forceinline__ void comm_epilogue(const GemmArgs& p, const CommSched& cs, Barriers* bars,
                                               uint32_t tmem_base, uint8_t* epi_smem, int warp, int lane) {
@@ -588,35 +635,63 @@ __device__ __forceinline__ void comm_epilogue(const GemmArgs& p, const CommSched
   const int row_in_tile = quarter * 32 + lane;
   const int tid_e = threadIdx.x - 64;
   const int W = cm.world, me = cm.rank;
+  const bool ordered = cm.mode == 0;
   const int slots = (cs.tiles_m * cs.tiles_n + W - 1) / W + cs.G;
   int* my_flags = cm.flags[me];
   __shared__ int s_ready;
   const int n_my = cs.count(p);
-  auto owner_of = [&](int it) { return (cs.vcta + it) % W; };
   // staging slot of the it-th tile of this CTA inside its owner's area: slots are per CTA
   auto slot_of = [&](int it) { return cs.vcta + (it / W) * cs.G; };
+  auto release_acc = [&](int acc) {
+    tc_fence_before();
+    if (cs.pair)
+      mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
+    else
+      mbar_arrive(&bars->tmem_empty[acc]);
+  };
   int red = 0, drained = 0;
   bool ok = true;
   auto reduce_one = [&](int it) {
     int rtm, rtn;
-    if (!(cm.debug & 4) && cs.tile(p, it, rtm, rtn))
+    if (cs.tile(p, it, rtm, rtn))
       comm_reduce_tile<BN>(p, rtm, rtn, slot_of(it), slots, quarter, col_half, lane,
                            epi_smem + (warp - 2) * 4096);
     warp_arrive(&bars->rpub_count, lane);
   };
-  for (int it = 0; it < n_my && ok; ++it) {
-    const int owner = owner_of(it), slot = slot_of(it);
-    const int acc = it & 1;
-    const uint32_t acc_phase = (it >> 1) & 1;
+  for (int j = 0; j < n_my && ok; ++j) {
+    const int it = ordered ? comm_order(cm, cs.okey(), n_my, j) : j;
+    const int owner = cs.owner(it, W), slot = slot_of(it);
+    const int acc = j & 1;
+    const uint32_t acc_phase = (j >> 1) & 1;
     if (!mbar_wait(&bars->tmem_full[acc], acc_phase, p.status, kStatusTimeoutTmemFull)) {
       ok = false;
       break;
     }
     tc_fence_after();
-    // phase A: this rank's partial tile -> the owner's staging area (a peer store unless owned)
+    const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+    if (ordered && owner == me) {
+      // own tile: accumulator + the peers' staged partials -> every rank's output
+      const int t2 = cs.vcta + it * cs.G;
+      if (tid_e == 0) s_ready = 1;
+      epi_bar_sync();
+      if (tid_e < W && tid_e != me && !wait_flag_ge(my_flags + t2 * kGemmMaxPeers + tid_e, cm.epoch, p.status))
+        s_ready = 0;
+      epi_bar_sync();
+      if (!s_ready) {
+        ok = false;
+        break;
+      }
+      int rtm, rtn;
+      if (cs.tile(p, it, rtm, rtn))
+        comm_reduce_tile<BN>(p, rtm, rtn, slot, slots, quarter, col_half, lane, epi_smem + (warp - 2) * 4096,
+                             true, taddr);
+      release_acc(acc);
+      warp_arrive(&bars->rpub_count, lane);
+      continue;
+    }
+    // this rank's partial tile -> the owner's staging area (a peer store unless owned)
     uint16_t* dst = reinterpret_cast<uint16_t*>(cm.stage[owner]) +
                     (static_cast<int64_t>(me) * slots + slot) * (BM * BN);
-    const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
     for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
       uint32_t r[32];
@@ -634,15 +709,12 @@ __device__ __forceinline__ void comm_epilogue(const GemmArgs& p, const CommSched
       }
     }
     warp_arrive(&bars->pub_count, lane);
-    tc_fence_before();
-    if (cs.pair)
-      mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
-    else
-      mbar_arrive(&bars->tmem_empty[acc]);
-    drained = it + 1;
-    // phase B (opportunistic): reduce owned tiles whose peer partials have all arrived
+    release_acc(acc);
+    if (ordered) continue;
+    drained = j + 1;
+    // reduce-scatter, opportunistic: reduce owned tiles whose peer partials have all arrived
     while (red < drained) {
-      if (owner_of(red) != me) { ++red; continue; }
+      if (cs.owner(red, W) != me) { ++red; continue; }
       const int t2 = cs.vcta + red * cs.G;
       if (tid_e == 0) {
         int ready = 1;
@@ -658,9 +730,9 @@ __device__ __forceinline__ void comm_epilogue(const GemmArgs& p, const CommSched
       ++red;
     }
   }
-  // drain: remaining owned tiles, now with (bounded) blocking waits
-  while (ok && red < n_my) {
-    if (owner_of(red) == me) {
+  // reduce-scatter drain: remaining owned tiles, now with (bounded) blocking waits
+  while (!ordered && ok && red < n_my) {
+    if (cs.owner(red, W) == me) {
       const int t2 = cs.vcta + red * cs.G;
       if (tid_e < W && tid_e != me)
         wait_flag_ge(my_flags + t2 * kGemmMaxPeers + tid_e, cm.epoch, p.status);
@@ -671,7 +743,7 @@ __device__ __forceinline__ void comm_epilogue(const GemmArgs& p, const CommSched
   }
   // the tiles owned by peers must have landed in this rank's output before the kernel ends
   for (int i = tid_e; i < n_my && ok; i += kEpiThreads) {
-    if (owner_of(i) != me && !(cm.debug & 4))
+    if (cs.owner(i, W) != me)
       wait_flag_ge(my_flags + cm.max_tiles * kGemmMaxPeers + (cs.vcta + i * cs.G), cm.epoch, p.status);
   }
 }
@@ -693,7 +765,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   const int tiles_m = (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -726,7 +797,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       uint32_t phase = 0;
       bool ok = true;
       int tm, tn;
-      for (int it = 0; ok && sched_tile(p, blockIdx.x, gridDim.x, it, tiles_m, tiles_n, tm, tn); ++it) {
+      const int n_my = sched_count(p, blockIdx.x, gridDim.x, tiles_m, tiles_n);
+      for (int j = 0; ok && j < n_my; ++j) {
+        // fused all-reduce: tiles owned by peers first, this rank's own tiles last
+        const int it = p.comm.world > 1 ? comm_order(p.comm, blockIdx.x, n_my, j) : j;
+        if (!sched_tile(p, blockIdx.x, gridDim.x, it, tiles_m, tiles_n, tm, tn)) break;
         const int m0 = tm * BM, n0 = tn * BN;
         if (p.comm.world > 1 && p.comm.mode == 2 && tm / (tiles_m / p.comm.world) != p.comm.rank) {
           // rows gathered from a peer: all 16 eight-row units of this 128-row block must have landed
@@ -1002,7 +1077,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       uint32_t phase = 0;
       bool ok = true;
       PairTile t;
-      for (int v = pair; ok && pair_tile(v, num_tiles, tail_split, tiles_m, tiles_n, BN / 2, t); v += num_pairs) {
+      const bool fused = p.comm.world > 1;   // tiles owned by peers first, own tiles last (no tail split then)
+      const int n_list = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
+      for (int j = 0; ok; ++j) {
+        if (fused && j >= n_list) break;
+        const int v = pair + (fused ? comm_order(p.comm, pair, n_list, j) : j) * num_pairs;
+        if (!pair_tile(v, num_tiles, tail_split, tiles_m, tiles_n, BN / 2, t)) break;
         const int m0 = t.tm * 2 * BM + static_cast<int>(cta) * BM;
         // this CTA's share of the B tile: BN / 2 rows of a full tile, BN / 4 rows of a half tile
         const int n0 = t.tn * BN + t.n_off + static_cast<int>(cta) * (t.half ? BN / 4 : BN / 2);

@@ -20,16 +20,17 @@ constexpr int kGemmMaxPeers = 8;
 //   out[r]   : r's copy of the reduced result D (row stride GemmArgs::ldd)
 //   flags[r] : r's int32 flags: arrive[tile * kGemmMaxPeers + source] then done[tile] at
 //              offset max_tiles * kGemmMaxPeers
-// Tile T is owned by rank T % world: every rank writes its partial of T into the owner's staging
-// area, the owner sums the partials in fp32, applies bias / residual, and writes the result into
-// every rank's `out`. `epoch` must increase with every call that uses the same flags.
+// Tiles are owned round-robin along each CTA's tile list. All-reduce: every rank first computes the
+// tiles its peers own and stores those partials into the owners' staging areas, then its own tiles,
+// whose accumulators it sums in fp32 with the partials that have arrived meanwhile, applies
+// bias / residual, and writes the result into every rank's `out`. `epoch` must increase with every
+// call that uses the same flags.
 struct GemmComm {
   int world, rank, epoch, max_tiles;
   void* stage[kGemmMaxPeers];
   void* out[kGemmMaxPeers];
   int* flags[kGemmMaxPeers];
   int64_t stage_elems;  // capacity of one rank's staging area in 16-bit elements
-  int debug;            // timing experiments only: 1 no system fences, 2 no peer output stores, 4 no reduce
   // 0: all-reduce (every rank receives the full [M, N] result).
   // 1: reduce-scatter along rows: rank r receives rows [r * M / world, (r + 1) * M / world) of the sum
   //    in its own `out[rank]` buffer of M / world rows; M must be a multiple of 128 * world. Tiles of a

@@ -1,10 +1,12 @@
 """Tensor-parallel linears fused with their all-reduce over NVLink peer memory.
 
 Row-parallel forward (`Y = sum_r X_r W_r^T`) and column-parallel data-gradient
-(`dX = sum_r dY_r W_r`) are each ONE launch of the tcgen05 GEMM whose epilogue pushes partial tiles
-into the owning peer's staging area, reduces owned tiles in fp32 as soon as the peers' partials have
-arrived, and writes the result into every rank's output buffer -- the transfer of tile i overlaps
-the MMAs of tile i+1 (reference: a cuBLAS GEMM followed by an exposed NCCL all-reduce,
+(`dX = sum_r dY_r W_r`) are each ONE launch of the tcgen05 GEMM. Tiles are owned round-robin; every
+rank computes the tiles its peers own first and pushes those partials into the owners' staging areas
+while the tensor cores already work on the next tile, and computes its own tiles last: by then the
+peers' partials have arrived, so the epilogue adds them to the accumulator in fp32 and writes the
+result into every rank's output buffer. Only that last transfer is exposed after the final MMA
+(reference: a cuBLAS GEMM followed by an exposed NCCL all-reduce,
 eth/runtime/megatron/mpu/layers.py:459-461, mappings.py:84-97).
 
 The outputs live in a small ring of symmetric buffers (peers write into them directly), so a
@@ -40,6 +42,19 @@ def reduce_scatter_schedule(cta: int, grid: int, it: int, tiles_m: int, tiles_n:
     return owner, owner * rows_per + band * group_m + rr, tn
 
 
+def all_reduce_order(okey: int, n_tiles: int, world: int, rank: int):
+    """Host mirror of `comm_order` in csrc/gemm_sm100.cu: the order in which a CTA (or CTA pair)
+    with ownership key `okey` walks its list of `n_tiles` tiles in the fused all-reduce. List index
+    `it` is owned by rank (okey + it) % world; tiles of rank+1 come first, then rank+2, ..., and the
+    rank's own tiles last."""
+    order = []
+    for g in range(1, world + 1):
+        owner = (rank + g) % world
+        first = (owner - okey) % world
+        order.extend(range(first, n_tiles, world))
+    return order
+
+
 class FusedTPBackend:
     def __init__(self, group_ranks, my_rank, group, device, max_tokens: int, hidden: int, dtype):
         self.group, self.device, self.dtype = group, torch.device(device), dtype
@@ -65,7 +80,6 @@ class FusedTPBackend:
         self.rank = self.stage.index
         self.epoch = 0
         self.slot = 0
-        self.debug = 0   # timing experiments only (see GemmComm::debug)
 
     @classmethod
     def create(cls, pstate, coll, device, args):
@@ -90,7 +104,7 @@ class FusedTPBackend:
         off = slot * self.out_slot_bytes
         native.lib().gemm_allreduce(a, False, b, b_mn, bias, residual, float(alpha), native.status(a.device),
                                     self.stage.ptrs, self.out.offset_ptrs(off), self.flags.ptrs, self.rank,
-                                    self.epoch, MAX_TILES, self.stage_elems, n, self.debug, 0)
+                                    self.epoch, MAX_TILES, self.stage_elems, n, 0)
         out = self.out.tensor((m, n), self.dtype, off)
         out._ethb_ring = True   # short-lived: valid until RING further fused calls
         return out
@@ -113,7 +127,7 @@ class FusedTPBackend:
         off = slot * self.out_slot_bytes
         native.lib().gemm_allreduce(a, False, b, b_mn, bias, residual, float(alpha), native.status(a.device),
                                     self.stage.ptrs, self.out.offset_ptrs(off), self.flags.ptrs, self.rank,
-                                    self.epoch, MAX_TILES, self.stage_elems, n, self.debug, 1)
+                                    self.epoch, MAX_TILES, self.stage_elems, n, 1)
         out = self.out.tensor((m // self.world, n), self.dtype, off)
         out._ethb_ring = True
         return out

@@ -24,3 +24,29 @@ def test_reduce_scatter_schedule_is_a_partition(world, grid, tiles_m, tiles_n):
             it += 1
         assert all(a != b for a, b in zip(owners, owners[1:])) or world == 1
     assert len(seen) == tiles_m * tiles_n
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("n_tiles", [0, 1, 2, 5, 8, 13])
+def test_all_reduce_order_puts_own_tiles_last(world, n_tiles):
+    from eth_b200.parallel.fused_tp import all_reduce_order
+    for okey in range(2 * world):
+        for rank in range(world):
+            order = all_reduce_order(okey, n_tiles, world, rank)
+            assert sorted(order) == list(range(n_tiles))          # a permutation of the list
+            owners = [(okey + it) % world for it in order]
+            dist = [(o - rank - 1) % world for o in owners]       # 0 for rank+1, ..., world-1 for own
+            assert dist == sorted(dist)
+            own = [it for it in order if (okey + it) % world == rank]
+            assert own == sorted(own) and order[len(order) - len(own):] == own
+        # a rank reaches its k-th own tile no earlier than any peer has pushed its partial of that
+        # tile: position of the tile in the peer's order < number of peer-owned tiles of the owner
+        for owner in range(world):
+            own_pos = {it: pos for pos, it in enumerate(all_reduce_order(okey, n_tiles, world, owner))}
+            for peer in range(world):
+                if peer == owner:
+                    continue
+                peer_pos = {it: pos for pos, it in enumerate(all_reduce_order(okey, n_tiles, world, peer))}
+                for it in range(n_tiles):
+                    if (okey + it) % world == owner:
+                        assert peer_pos[it] <= own_pos[it]
