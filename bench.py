@@ -200,6 +200,12 @@ def run_ours(opts):
         sampler.start()
     ms, launches, _ = timed(opts.steps, e2e=False)
     clocks = sampler.stop() if sampler else None
+    # exposed gradient-sync time: what the main stream spends reducing gradients after the last
+    # backward of an iteration (CUDA events inside the engine), mean over the timed steps, max over ranks
+    gs = torch.tensor([engine.exposed_grad_sync_ms(last=opts.steps)], device="cuda")
+    if world > 1:
+        dist.all_reduce(gs, op=dist.ReduceOp.MAX)
+    exposed_ms = float(gs.item())
     native.check_status()
     tokens = gbs * MODEL["seq_length"] * opts.steps
     value = tokens / (ms / 1e3)
@@ -228,6 +234,7 @@ def run_ours(opts):
                     "h2d_bytes_per_step": counter["h2d"] // opts.steps, "d2h_bytes_per_step": 8,
                     "final_loss": losses[-1] if losses else None},
             "gpu_launches": launches,
+            "exposed_grad_sync_ms_per_step": exposed_ms,
         }
         if warmup_status:
             out["warmup_status"] = warmup_status

@@ -489,6 +489,33 @@ void peer_allreduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>
   check(ethb::peer_allreduce(a, cur_stream()), "peer_allreduce");
 }
 
+// pieces: int64 CUDA tensor [P, 4] = (element offset, rows, run, stride); bases / flags: per-rank addresses
+void peer_reduce_pieces(const std::vector<int64_t>& bases, const std::vector<int64_t>& flags, int64_t rank,
+                        int64_t epoch, const Tensor& pieces, int64_t dtype, double scale) {
+  c10::cuda::CUDAGuard guard(pieces.device());
+  TORCH_CHECK(pieces.is_cuda() && pieces.dim() == 2 && pieces.size(1) == 4 && pieces.is_contiguous() &&
+              pieces.scalar_type() == at::kLong, "pieces must be a contiguous int64 CUDA tensor [P, 4]");
+  TORCH_CHECK(bases.size() == flags.size() && bases.size() >= 1 && bases.size() <= ethb::kMaxPeers);
+  ethb::PieceReduceArgs a{};
+  a.bases = to_peers(bases);
+  a.flags = to_peers(flags);
+  a.pieces = pieces.data_ptr<int64_t>();
+  a.num_pieces = static_cast<int>(pieces.size(0));
+  a.rank = static_cast<int>(rank);
+  a.world = static_cast<int>(bases.size());
+  a.epoch = static_cast<int>(epoch);
+  a.dtype = static_cast<int>(dtype);
+  a.scale = static_cast<float>(scale);
+  check(ethb::peer_reduce_pieces(a, cur_stream()), "peer_reduce_pieces");
+}
+void peer_flags(const std::vector<int64_t>& flags, int64_t rank, int64_t epoch, int64_t signal_base,
+                int64_t wait_base, const Tensor& status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  check(ethb::peer_flags(to_peers(flags), static_cast<int>(rank), static_cast<int>(flags.size()),
+                         static_cast<int>(epoch), static_cast<int>(signal_base), static_cast<int>(wait_base),
+                         status.data_ptr<int>(), cur_stream()), "peer_flags");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -532,4 +559,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_allreduce", &peer_allreduce);
+  m.def("peer_reduce_pieces", &peer_reduce_pieces);
+  m.def("peer_flags", &peer_flags);
 }

@@ -184,7 +184,91 @@ __global__ void peer_allreduce_kernel(ReduceArgs a) {
   }
 }
 
+// One warp: optionally tell every peer `epoch` at flags[peer][signal_base + rank], optionally wait
+// (bounded) until flags[rank][wait_base + p] >= epoch for every p.
+__global__ void __launch_bounds__(32, 1)
+peer_flags_kernel(PeerPtrs flags, int rank, int world, int epoch, int signal_base, int wait_base, int* status) {
+  const int p = threadIdx.x;
+  if (p >= world) return;
+  if (signal_base >= 0) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flags.ptrs[p]) + signal_base + rank, epoch);
+  }
+  if (wait_base >= 0)
+    wait_flag_ge(reinterpret_cast<const int*>(flags.ptrs[rank]) + wait_base + p, epoch, status);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+peer_reduce_pieces_kernel(PieceReduceArgs a) {
+  const int W = a.world;
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthr = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int j = 0; j < a.num_pieces; ++j) {
+    const int64_t off = a.pieces[j * 4 + 0], rows = a.pieces[j * 4 + 1];
+    const int64_t run = a.pieces[j * 4 + 2], stride = a.pieces[j * 4 + 3];
+    const int64_t vpr = run >> 3;                 // 8-element vectors per row
+    const int64_t nvec = rows * vpr;
+    const int64_t per = (nvec + W - 1) / W;       // this rank's share of the piece
+    const int64_t lo = a.rank * per;
+    const int64_t hi = lo + per < nvec ? lo + per : nvec;
+    for (int64_t i = lo + tid; i < hi; i += nthr) {
+      const int64_t row = i / vpr;
+      const int64_t e = off + row * stride + (i - row * vpr) * 8;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < W; ++r) {
+        float v[8];
+        ld8(reinterpret_cast<const T*>(a.bases.ptrs[r]) + e, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += v[k];
+      }
+      if (a.scale != 1.0f) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] *= a.scale;
+      }
+      for (int d = 0; d < W; ++d) st8(reinterpret_cast<T*>(a.bases.ptrs[d]) + e, acc);
+    }
+  }
+  // the last block to finish publishes "my share is in your buffer, and I no longer read yours"
+  __shared__ int last_s;
+  int* my_flags = reinterpret_cast<int*>(a.flags.ptrs[a.rank]);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int done = atomicAdd(my_flags + kFlagCounter, 1);
+    last_s = (done == static_cast<int>(gridDim.x) - 1);
+  }
+  __syncthreads();
+  if (last_s) {
+    if (threadIdx.x == 0) my_flags[kFlagCounter] = 0;
+    if (threadIdx.x < W) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<int*>(a.flags.ptrs[threadIdx.x]) + kFlagDone + a.rank, a.epoch);
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t peer_flags(const PeerPtrs& flags, int rank, int world, int epoch, int signal_base,
+                       int wait_base, int* status, cudaStream_t st) {
+  if (world > kMaxPeers || world < 1) return cudaErrorInvalidValue;
+  peer_flags_kernel<<<1, 32, 0, st>>>(flags, rank, world, epoch, signal_base, wait_base, status);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t peer_reduce_pieces(const PieceReduceArgs& a, cudaStream_t st) {
+  if (a.world > kMaxPeers || a.world < 1 || a.num_pieces <= 0 || a.pieces == nullptr) return cudaErrorInvalidValue;
+  // enough blocks to keep NVLink busy in both directions, few enough to leave SMs to compute kernels
+  const int grid = 148 * 2;
+  if (a.dtype == kBF16) peer_reduce_pieces_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
+  else if (a.dtype == kF16) peer_reduce_pieces_kernel<__half><<<grid, 256, 0, st>>>(a);
+  else if (a.dtype == kF32) peer_reduce_pieces_kernel<float><<<grid, 256, 0, st>>>(a);
+  else return cudaErrorInvalidValue;
+  count_launch();
+  return cudaGetLastError();
+}
 
 cudaError_t peer_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status,
                          cudaStream_t st) {

@@ -42,4 +42,33 @@ struct ReduceArgs {
 };
 cudaError_t peer_allreduce(const ReduceArgs& a, cudaStream_t st);
 
+// ---- two-shot in-place all-reduce of gradient pieces, without device-side waiting ---------------
+// The gradients of a bucket are a list of pieces (rows x run elements, row stride `stride`, at
+// element offset `off`) that sit at the SAME offsets in every rank's symmetric gradient buffer.
+// Rank r sums, for its 1 / world share of every piece, the values of all ranks (peer loads, fp32,
+// rank order), scales, and stores the result into every rank's buffer (peer stores): a
+// reduce-scatter followed by an all-gather that uses both NVLink directions and never packs.
+// The kernel itself waits for nobody. Synchronisation is done by `peer_flags`, a one-warp kernel
+// small enough to share an SM with a resident GEMM CTA, so that a rank waiting for a peer does
+// not keep compute kernels off the SMs:
+//   peer_flags(signal arrive, wait arrive)  ->  peer_reduce_pieces (ends with signal done)
+//   ... and before the gradients are consumed:  peer_flags(wait done).
+// Flag block of one process group (int32, symmetric): [0, 8) arrive, [8, 16) done, [16] counter.
+constexpr int kFlagArrive = 0;
+constexpr int kFlagDone = kMaxPeers;
+constexpr int kFlagCounter = 2 * kMaxPeers;
+struct PieceReduceArgs {
+  PeerPtrs bases;          // per rank: address that piece offsets are relative to
+  PeerPtrs flags;          // per rank: the group's flag block
+  const int64_t* pieces;   // device, [num_pieces][4] = element offset, rows, run, stride (run % 8 == 0)
+  int num_pieces;
+  int rank, world, epoch;
+  int dtype;               // kF32 / kF16 / kBF16
+  float scale;
+};
+cudaError_t peer_reduce_pieces(const PieceReduceArgs& a, cudaStream_t st);
+// signal_base / wait_base: flag offset (kFlagArrive / kFlagDone) or -1 to skip that half.
+cudaError_t peer_flags(const PeerPtrs& flags, int rank, int world, int epoch, int signal_base,
+                       int wait_base, int* status, cudaStream_t st);
+
 }  // namespace ethb

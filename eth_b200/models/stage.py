@@ -120,6 +120,16 @@ class GPTStage:
             op.params[spec.local_name] = by_uniq[i].param
             self.entries.append(ParamEntry(op, spec, by_uniq[i].param, by_uniq[i].offset, by_uniq[i].numel, True))
 
+    def rebind_grad_buffer(self, buf: torch.Tensor) -> None:
+        """Move the flat gradient buffer into `buf` (same numel and dtype, e.g. a symmetric
+        allocation that peers can address) and re-create every parameter's `main_grad` view."""
+        if buf.numel() != self.grad_buf.numel() or buf.dtype != self.grad_buf.dtype:
+            raise ValueError("replacement gradient buffer must match the flat buffer's size and dtype")
+        buf.copy_(self.grad_buf)
+        self.grad_buf = buf
+        for e in self.entries:
+            e.param.main_grad = buf[e.offset:e.offset + e.numel].view(e.param.shape)
+
     def unique_entries(self) -> List[ParamEntry]:
         return [e for e in self.entries if not e.tied_alias]
 

@@ -113,6 +113,19 @@ def join_async_wgrad(device) -> None:
         torch.cuda.current_stream(dev).wait_stream(side)
 
 
+def async_wgrad_event(device):
+    """An event recorded now on the weight-gradient side stream (None when weight gradients run on
+    the main stream). A consumer of `main_grad` on a third stream waits for it to see every weight
+    gradient enqueued so far."""
+    dev = torch.device(device)
+    side = _WGRAD_STREAM.get(dev.index) if dev.type == "cuda" else None
+    if side is None:
+        return None
+    ev = torch.cuda.Event()
+    ev.record(side)
+    return ev
+
+
 def _wgrad_now(dy, x, weight, bias):
     gemm(dy, x, a_mn=True, b_mn=True, out=_grad_of(weight).view(weight.shape), accumulate=True)
     if bias is not None:

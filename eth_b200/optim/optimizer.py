@@ -25,6 +25,9 @@ import torch
 from ..ops import native
 
 
+DEVICE_FAULT_MARK = 1024.0   # added to the overflow flag by a rank whose device status word is set
+
+
 class FlatMixedPrecisionAdam:
     def __init__(self, stage, lr=1.5e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, clip_grad=1.0,
                  grad_scaler=None, owned_ranges: Optional[Sequence[Tuple[int, int]]] = None,
@@ -49,6 +52,7 @@ class FlatMixedPrecisionAdam:
         self.owned_ranges = list(owned_ranges) if owned_ranges is not None else [(0, n)]
         self.last_grad_norm = None
         self.last_found_inf = False
+        self.last_device_fault = False   # some rank's status word was set when the last step ran
 
     # -- bookkeeping used by checkpointing and state synchronisation
     def set_lr(self, lr: float) -> None:
@@ -89,6 +93,11 @@ class FlatMixedPrecisionAdam:
                 self.ctrl[0] += (v * v).sum()
                 if not torch.isfinite(v).all():
                     self.ctrl[1] = 1.0
+        if g.is_cuda:
+            # A bounded device wait that ran out on any rank (status word != 0) left stale or partial
+            # data behind: fold it into the overflow flag, so every rank skips this update, with a
+            # magnitude the host can tell from a plain overflow.
+            self.ctrl[1:2].add_((native.status(g.device) != 0).to(torch.float32), alpha=DEVICE_FAULT_MARK)
         if self.world_all_reduce is not None:
             self.world_all_reduce(self.ctrl[:2])
 
@@ -114,9 +123,10 @@ class FlatMixedPrecisionAdam:
             if self.device_grad_factor:
                 inv_scale = host[2]
             found_inf = host[1] > 0 or not math.isfinite(host[0])
+            self.last_device_fault = host[1] >= DEVICE_FAULT_MARK
             norm = math.sqrt(host[0]) * inv_scale if not found_inf else float("nan")
             self.last_grad_norm, self.last_found_inf = norm, found_inf
-            if scaler is not None:
+            if scaler is not None and not self.last_device_fault:
                 scaler.update(found_inf)
             if found_inf:
                 return False, None, None

@@ -9,10 +9,9 @@ B200 specifics:
   * pack and unpack of a bucket are each ONE launch of a table-driven strided copy kernel
     (`strided_copy_scale`); the segment tables are built once and live on the device;
   * the reduction backend is injected. `collective` uses the given all-reduce callable (NCCL, or
-    Gloo in CPU tests). `peer` runs the one-shot peer-memory kernel (`peer_allreduce`): every rank
-    reads all peers' packed buckets over NVLink, sums in a fixed order in fp32, applies the
-    normalisation scale, and accumulates the squared norm / non-finite flag of what it wrote, so
-    the optimizer needs no further pass over the gradients of synchronised buckets.
+    Gloo in CPU tests). `peer` runs the two-shot peer-memory kernel (`peer_reduce_pieces`, see
+    peer_backend.py): where the bucket's slices sit at the same offsets of every rank's symmetric
+    gradient buffer it works in place and pack / unpack disappear altogether.
 """
 from __future__ import annotations
 
@@ -54,6 +53,8 @@ class GradientBucketExecutor:
         self._evidence = (GradientRuntimeEvidenceRecorder(plan, global_rank, process_group_registry,
                                                           self._scratch, runtime_evidence_dir)
                           if runtime_evidence_dir else None)
+        if self._peer is not None and hasattr(self._peer, "attach"):
+            self._peer.attach(self)
 
     # ------------------------------------------------------------------ set-up
     @staticmethod
@@ -220,12 +221,17 @@ class GradientBucketExecutor:
                 for view, _off, _scale in self._segments(bucket):
                     view.mul_(normalization_scale)
             return
+        if self._evidence is None and self._peer is not None and self._peer.is_direct(bucket):
+            # in place on the symmetric gradient buffers: nothing to pack or unpack
+            self._peer.reduce_direct(bucket, normalization_scale)
+            self.collectives_issued += 1
+            return
         payload = self._scratch[bucket.grad_dtype][:bucket.exact_numel]
         self.pack(bucket, payload)
         if self._evidence is not None:
             self._evidence.observe_packed_bucket(bucket, payload)
         if self._peer is not None and self._peer.handles(bucket):
-            reduced = self._peer.all_reduce(bucket, payload, normalization_scale)
+            reduced = self._peer.reduce_packed(bucket, payload, normalization_scale)
             self.unpack(bucket, reduced, 1.0)
         else:
             self._all_reduce_sum(payload, self._registry.handle(bucket.process_group_id))
@@ -251,5 +257,12 @@ class GradientBucketExecutor:
         for bucket in self._my_buckets:
             if bucket.bucket_id not in skip:
                 self.execute_bucket(bucket, normalization_scale)
+        self.finish()
         if self._evidence is not None:
             self._evidence.finish_execution()
+
+    def finish(self) -> None:
+        """Make the results of in-place peer reductions issued so far (on any stream the current one
+        has joined) complete on the current stream."""
+        if self._peer is not None:
+            self._peer.finish()

@@ -120,12 +120,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--no-async-wgrad", dest="async_wgrad", action="store_false",
                    help="Run weight-gradient GEMMs on the main stream (default: on a side stream, so that their "
                         "partly filled last wave overlaps the data-gradient GEMM of the same layer).")
-    g.add_argument("--overlap-grad-sync", action="store_true",
-                   help="Start the reduction of a gradient bucket on a side stream as soon as the last micro-batch's "
-                        "backward has produced it (peer-memory buckets only). Off by default: the reduction kernel "
-                        "waits for its data-parallel peer while it holds SM resources, and when it cannot share an SM "
-                        "with the persistent GEMM kernels, tensor-parallel and pipeline waits of other ranks can close "
-                        "a cycle that only the bounded waits break. Safe for pure data parallelism.")
+    g.add_argument("--no-overlap-grad-sync", dest="overlap_grad_sync", action="store_false",
+                   help="Reduce all gradient buckets after backward. By default a bucket served by the peer-memory "
+                        "backend is reduced on a side stream as soon as the last micro-batch's backward has passed "
+                        "its first op.")
     g.add_argument("--grad-sync-backend", default="auto", choices=["auto", "collective", "peer"],
                    help="Reduction backend: torch.distributed all-reduce or the peer-memory kernel.")
     g.add_argument("--grad-sync-dump-plan", type=str, default=None, help="Write the gradient sync plan as JSON.")

@@ -64,6 +64,15 @@ def is_writer(pstate) -> bool:
 def save_checkpoint(engine, iteration: int, root: str) -> str:
     ps, args = engine.pstate, engine.args
     path = checkpoint_name(root, iteration, ps.tp_rank, ps.stage_id, ps.num_stages)
+    if engine.device.type == "cuda":
+        # A bounded device wait that ran out leaves stale gradients or partial GEMM outputs behind;
+        # nothing computed from them may reach a checkpoint. All ranks agree before anyone writes.
+        from ..ops import native
+        fault = (native.status(engine.device) != 0).to(torch.float32)
+        engine.coll.all_reduce_max(fault)
+        if float(fault.item()) != 0.0:
+            native.check_status(engine.device)   # raises with this rank's reason if it is the one
+            raise RuntimeError("checkpoint not written: another rank reported a device kernel time-out")
     if is_writer(ps):
         args.global_data_cursor = engine.clock.global_data_cursor
         args.successful_optimizer_steps = engine.clock.successful_optimizer_steps

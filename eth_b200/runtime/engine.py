@@ -14,6 +14,7 @@ scalar that the optimizer kernels read.
 from __future__ import annotations
 
 import math
+import os
 import time
 from types import SimpleNamespace
 from typing import Callable, Dict, List, Optional
@@ -117,6 +118,7 @@ class TrainEngine:
         evidence = getattr(args, "grad_sync_evidence_dir", None) or getattr(args, "grad_sync_runtime_evidence_dir", None)
         raw_ops.enable_async_wgrad(self.device, on=getattr(args, "async_wgrad", True) and not evidence)
         self.loss_acc = torch.zeros(2, dtype=torch.float32, device=self.device)
+        self._gs_pairs = []
         self.last_stats: Dict[str, object] = {}
 
     # ------------------------------------------------------------------ set-up
@@ -139,22 +141,35 @@ class TrainEngine:
     def _setup_grad_sync(self):
         args, ps = self.args, self.pstate
         topo = ps.topology
+        peer_factory = None
+        self._grad_symm = None
+        backend = getattr(args, "grad_sync_backend", "auto")
+        one_node = int(os.environ.get("LOCAL_WORLD_SIZE", args.world_size)) == args.world_size
+        use_peer = backend in ("auto", "peer") and self.device.type == "cuda" and self.coll.enabled and one_node
+        if use_peer:
+            # Every rank takes this branch together (it depends on global facts only): the flat
+            # gradient buffer moves into a symmetric allocation so peers can reduce it in place.
+            # This comes before the gradient metadata is collected, which records `main_grad` views.
+            from ..parallel.peer_memory import SymmetricBuffer
+            gb = self.stage.grad_buf
+            self._grad_symm = SymmetricBuffer(gb.numel() * gb.element_size(), tuple(range(args.world_size)),
+                                              args.rank, None, self.device)
+            self.stage.rebind_grad_buffer(self._grad_symm.tensor((gb.numel(),), gb.dtype))
         descriptors, bindings = collect_gpt_gradient_metadata(self.stage, ps, args.normalized_config)
         self.descriptors, self.bindings = descriptors, bindings
-        peer_factory = None
-        backend = getattr(args, "grad_sync_backend", "auto")
-        if backend in ("auto", "peer") and self.device.type == "cuda" and self.coll.enabled:
+        if use_peer:
+            evidence = bool(getattr(args, "grad_sync_runtime_evidence_dir", None))
+
             def peer_factory(plan, rank):
-                try:
-                    from ..parallel.grad_sync.peer_backend import PeerReduceBackend
-                    max_group = 8 if backend == "peer" else 2
-                    if not any(1 < len(g.ranks) <= max_group for g in plan.process_groups):
-                        return None     # no group the peer kernel would serve: plain scratch + collectives
-                    return PeerReduceBackend(plan, rank, self.coll, self.device, max_group=max_group)
-                except Exception:
-                    if backend == "peer":
-                        raise
-                    return None
+                from ..parallel.grad_sync.peer_backend import PeerReduceBackend
+                if not any(1 < len(g.ranks) <= 8 for g in plan.process_groups):
+                    return None     # no group the peer kernel would serve: plain scratch + collectives
+                be = PeerReduceBackend(plan, rank, self.coll, self.device, max_group=8,
+                                       grad_symm=self._grad_symm, grad_buf=self.stage.grad_buf)
+                be.force_packed = evidence
+                return be
+        elif backend == "peer":
+            raise RuntimeError("--grad-sync-backend peer needs CUDA ranks that all share one node")
 
         def group_gather(out, obj, handle):
             self.coll.all_gather_object(out, obj, group=handle)
@@ -180,15 +195,15 @@ class TrainEngine:
     def _setup_grad_overlap(self):
         """Buckets whose reduction runs on a side stream as soon as the last micro-batch's backward
         has passed their first op (reference: strictly after backward, grad_sync/executor.py:199-261).
-        Only buckets served by the peer-memory kernel take part: a library collective launched from a
-        second stream could interleave differently with the main stream's collectives on other ranks.
-        Opt-in (`--overlap-grad-sync`): with tensor or pipeline parallelism a reduction kernel spinning
-        for its data-parallel peer can keep the next GEMM of its own rank off the SMs while that peer
-        transitively waits for this rank -- measured on PP2 x TP2 x DP2 as bounded-wait timeouts."""
+        Only buckets served by the peer-memory backend take part: a library collective launched from
+        a second stream could interleave differently with the main stream's collectives on other
+        ranks. The peer backend's kernels never spin while they occupy an SM's worth of resources
+        (waiting is left to a one-warp kernel), so an early rank cannot starve the persistent GEMMs
+        of its own stage or, through a fused tensor-parallel GEMM, of its partner's."""
         a, ex = self.args, self.grad_sync.executor
         self._overlap_by_op, self._overlap_done = {}, set()
         self._sync_stream = None
-        if (not getattr(a, "overlap_grad_sync", False) or self.device.type != "cuda"
+        if (not getattr(a, "overlap_grad_sync", True) or self.device.type != "cuda"
                 or getattr(a, "grad_sync_evidence_dir", None) or getattr(a, "grad_sync_runtime_evidence_dir", None)):
             return
         for b in ex.buckets:
@@ -204,6 +219,10 @@ class TrainEngine:
         ready = torch.cuda.Event()
         ready.record()
         self._sync_stream.wait_event(ready)
+        # the weight gradients of these ops were enqueued on the side stream: wait for them too
+        wgrad_done = raw_ops.async_wgrad_event(self.device)
+        if wgrad_done is not None:
+            self._sync_stream.wait_event(wgrad_done)
         with torch.cuda.stream(self._sync_stream):
             for b in buckets:
                 self.grad_sync.executor.execute_bucket(b, 1.0)
@@ -321,14 +340,30 @@ class TrainEngine:
         if evidence_dir:
             self._evidence("pre_sync", evidence_dir)
         if self._needs_reduction:
+            gs = self._grad_sync_events()
+            if gs:
+                gs[0].record()
             if self._sync_stream is not None:
                 torch.cuda.current_stream().wait_stream(self._sync_stream)
             self.grad_sync.executor.execute(1.0, skip=self._overlap_done)
             self._overlap_done = set()
+            if gs:
+                gs[1].record()
         self.optimizer.set_grad_factor(normalization)
         if evidence_dir:
             self._evidence("post_sync", evidence_dir, grad_factor=float(self.optimizer.ctrl[2]))
         ok, grad_norm, _ = self.optimizer.step(sync=sync)
+        if getattr(self.optimizer, "last_device_fault", False):
+            # every rank sees the mark (it travels with the overflow flag), so all of them stop here
+            # before a checkpoint could be written from stale data
+            from ..ops import native
+            detail = ""
+            try:
+                native.check_status(self.device)
+            except RuntimeError as err:
+                detail = f" (this rank: {err})"
+            raise RuntimeError("a bounded device wait ran out on some rank during this iteration; the update was "
+                               f"skipped on every rank{detail}")
         if evidence_dir:
             self._evidence("post_step", evidence_dir, update_successful=bool(ok))
         increment = self.clock.after_attempt(ok)
@@ -340,6 +375,30 @@ class TrainEngine:
                  "loss_acc": self.loss_acc}
         self.last_stats = stats
         return stats
+
+    # ------------------------------------------------------------------ exposed gradient-sync time
+    def _grad_sync_events(self):
+        """A fresh CUDA event pair for this iteration's post-backward gradient sync, or None on CPU.
+        The pair brackets what the main stream spends on gradient reduction after the last backward
+        (waiting for reductions started during backward included): the exposed part, the quantity
+        the reference reports as its `backward-params-all-reduce` timer
+        (eth/runtime/megatron/training.py:935-977, 1119-1169)."""
+        if self.device.type != "cuda":
+            return None
+        pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        self._gs_pairs.append(pair)
+        if len(self._gs_pairs) > 64:
+            del self._gs_pairs[:-64]
+        return pair
+
+    def exposed_grad_sync_ms(self, last: int = 1) -> float:
+        """Mean exposed gradient-sync time (ms per iteration) over the `last` iterations;
+        synchronises on the newest event. 0.0 when nothing had to be reduced."""
+        pairs = self._gs_pairs[-last:]
+        if not pairs:
+            return 0.0
+        pairs[-1][1].synchronize()
+        return sum(a.elapsed_time(b) for a, b in pairs) / len(pairs)
 
     def eval_step(self) -> None:
         """Forward-only pass over one global batch with dropout disabled; accumulates the masked loss

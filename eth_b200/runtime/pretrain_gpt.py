@@ -61,10 +61,34 @@ def training_log(engine, stats, elapsed_ms, total_ms, log_state):
              f"lm loss: {loss:.6E} | loss scale: {stats['loss_scale']:.1f} | ")
     if stats["grad_norm"] is not None:
         line += f"grad norm: {stats['grad_norm']:.3f} | "
+    exposed = engine.exposed_grad_sync_ms()
+    line += f"exposed grad sync (ms): {exposed:.2f} | "
     line += f"number of skipped iterations: {log_state['skipped']:3d} | number of nan iterations: {log_state['nan']:3d} |"
     if a.local_rank == 0:
         print(line, flush=True)
-    return loss, tokens_per_s
+    if log_state.get("writer") is not None:
+        w = log_state["writer"]
+        samples = engine.clock.successful_optimizer_steps * a.total_gbs
+        for key, val in (("learning-rate", stats["lr"]), ("lm loss", loss), ("loss-scale", stats["loss_scale"]),
+                         ("grad-norm", stats["grad_norm"]), ("iteration-time-ms", elapsed_ms),
+                         ("tokens-per-second", tokens_per_s), ("exposed-grad-sync-ms", exposed)):
+            if val is not None:
+                w.add_scalar(key, val, it)
+                w.add_scalar(key + " vs samples", val, samples)
+    return loss, tokens_per_s, exposed
+
+
+def make_tensorboard_writer(args):
+    """SummaryWriter on the last rank when `--tensorboard-dir` is given (reference:
+    eth/runtime/megatron/global_vars.py:137-154); None elsewhere or when tensorboard is missing."""
+    if not getattr(args, "tensorboard_dir", None) or args.rank != args.world_size - 1:
+        return None
+    try:
+        from torch.utils.tensorboard import SummaryWriter
+    except Exception:
+        print("WARNING: tensorboard is not importable; no tensorboard logs will be written", flush=True)
+        return None
+    return SummaryWriter(log_dir=args.tensorboard_dir, max_queue=getattr(args, "tensorboard_queue_size", 1000))
 
 
 def write_rank_csv(engine, rows):
@@ -77,7 +101,8 @@ def write_rank_csv(engine, rows):
     res = torch.cuda.max_memory_reserved() / 2 ** 20 if torch.cuda.is_available() else 0.0
     with open(os.path.join(a.log_path, "csv", name), "w", newline="") as f:
         w = csv.writer(f)
-        w.writerow(["iteration", "ms_per_iteration", "tokens_per_s", "lm_loss", "grad_norm", "max_allocated_mb", "max_reserved_mb"])
+        w.writerow(["iteration", "ms_per_iteration", "tokens_per_s", "lm_loss", "grad_norm", "exposed_grad_sync_ms",
+                    "max_allocated_mb", "max_reserved_mb"])
         for r in rows:
             w.writerow(list(r) + [f"{mem:.1f}", f"{res:.1f}"])
 
@@ -113,7 +138,7 @@ def pretrain(argv=None):
     validate_training_clock_states(states)
     print_rank_0(f"> model and optimizer ready in {time.time() - t_start:.1f} s "
                  f"({sum(p.numel() for _, p in engine.stage.named_parameters()) / 1e6:.1f} M parameters on rank 0)")
-    log_state = {"skipped": 0, "nan": 0}
+    log_state = {"skipped": 0, "nan": 0, "writer": make_tensorboard_writer(args)}
     rows, total_ms = [], 0.0
     use_cuda = device.type == "cuda"
     while engine.iteration < args.train_iters:
@@ -131,8 +156,8 @@ def pretrain(argv=None):
         if stats["iteration"] > 1:
             total_ms += ms
         if stats["iteration"] % args.log_interval == 0:
-            loss, tps = training_log(engine, stats, ms, total_ms, log_state)
-            rows.append((stats["iteration"], f"{ms:.2f}", f"{tps:.1f}", f"{loss:.6f}", stats["grad_norm"]))
+            loss, tps, exposed = training_log(engine, stats, ms, total_ms, log_state)
+            rows.append((stats["iteration"], f"{ms:.2f}", f"{tps:.1f}", f"{loss:.6f}", stats["grad_norm"], f"{exposed:.3f}"))
         if args.eval_iters and args.eval_interval and engine.iteration % args.eval_interval == 0:
             res = evaluate(engine, args.eval_iters)
             print_rank_0(f" validation loss at iteration {engine.iteration} | lm loss value: {res['lm loss']:.6E} | "
@@ -152,6 +177,8 @@ def pretrain(argv=None):
     if args.save and (not args.save_interval or engine.iteration % args.save_interval):
         save_checkpoint(engine, engine.iteration, args.save)
     write_rank_csv(engine, rows)
+    if log_state["writer"] is not None:
+        log_state["writer"].close()
     if use_cuda:
         from ..ops import native
         native.check_status()

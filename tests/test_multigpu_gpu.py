@@ -158,3 +158,92 @@ def test_fused_reduce_scatter_and_all_gather_gemm_two_gpus():
     for r in res:
         assert max(r["rs"]) < 1e-2, r["rs"]
         assert max(r["ag"]) < 1e-2, r["ag"]
+
+
+def _peer_reduce_pieces(rank, world):
+    """Two-shot in-place reduction of pieces (whole runs and a strided 2-D slice) of a symmetric buffer."""
+    import torch.distributed as dist
+    from eth_b200.ops import native
+    from eth_b200.parallel.peer_memory import SymmetricBuffer
+    dev = torch.device("cuda", rank)
+    out = {}
+    for dt, code, tol in ((torch.float32, 0, 1e-6), (torch.float16, 1, 2e-3), (torch.bfloat16, 2, 1.6e-2)):
+        n = 1 << 20
+        esz = torch.empty((), dtype=dt).element_size()
+        buf = SymmetricBuffer(n * esz, tuple(range(world)), rank, None, dev)
+        flags = SymmetricBuffer(64 * 4, tuple(range(world)), rank, None, dev)
+        mine = buf.tensor((n,), dt)
+        # pieces: a long run, a short run, and 96 rows of 64 elements with row stride 256
+        pieces = [(0, 1, 300_000, 300_000), (400_000, 1, 4096, 4096), (500_000, 96, 64, 256)]
+        table = torch.tensor(pieces, dtype=torch.int64, device=dev)
+        errs = []
+        for epoch in (1, 2):
+            src = (torch.randn(n, device=dev) * (rank + 1)).to(dt)
+            mine.copy_(src)
+            ref = src.float().clone()
+            dist.all_reduce(ref)
+            ref *= 0.5
+            dist.barrier()
+            st = native.status(dev)
+            native.lib().peer_flags(flags.ptrs, rank, epoch, 0, 0, st)
+            native.lib().peer_reduce_pieces(buf.ptrs, flags.ptrs, rank, epoch, table, code, 0.5)
+            native.lib().peer_flags(flags.ptrs, rank, epoch, -1, 8, st)
+            got = mine.float()
+            touched = torch.zeros(n, dtype=torch.bool, device=dev)
+            for off, rows, run, stride in pieces:
+                for r in range(rows):
+                    touched[off + r * stride: off + r * stride + run] = True
+            errs.append(float((got[touched] - ref[touched]).abs().max() / ref[touched].abs().max()))
+            errs.append(float((got[~touched] - src.float()[~touched]).abs().max()))   # untouched elements intact
+            torch.cuda.synchronize()
+            dist.barrier()
+        native.check_status()
+        out[str(dt)] = (errs, tol)
+        buf.close()
+        flags.close()
+    return out
+
+
+def test_peer_reduce_pieces_two_gpus():
+    _need(2)
+    for res in run_ranks(2, _peer_reduce_pieces, backend="nccl"):
+        for name, (errs, tol) in res.items():
+            assert errs[0] <= tol and errs[2] <= tol, (name, errs)
+            assert errs[1] == 0.0 and errs[3] == 0.0, (name, errs)
+
+
+def _engine_dp2_params(rank, world, extra):
+    from eth_b200.contract.config import make_config, make_pipe, manifest_size
+    from eth_b200.ops import native
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+    layers = 2
+    cfg = make_config([make_pipe([manifest_size(layers)], [1], [world], gbs=16, mbs=8)], num_layers=layers,
+                      hidden_size=512, num_attention_heads=4, seq_length=256)
+    args = parse_args(["--bf16", "--hidden-dropout", "0.1", "--vocab-size", "2000", "--lr", "1e-3",
+                       "--lr-warmup-fraction", "0.0", "--make-vocab-size-divisible-by", "64",
+                       "--grad-sync-bucket-size-mb", "1"] + list(extra), config=cfg, rank=rank, world_size=world)
+    eng = TrainEngine(args)
+    direct = sum(1 for b in eng.grad_sync.executor.buckets
+                 if eng.grad_sync.executor.uses_peer_backend(b) and eng.grad_sync.executor._peer.is_direct(b))
+    for _ in range(3):
+        eng.train_step()
+    native.check_status()
+    flat = eng.stage.param_buf.detach().float().clone()
+    return {"params": flat.cpu(), "direct": direct, "overlapped": len(eng._overlap_by_op), "loss": eng.reduced_loss()}
+
+
+def test_engine_dp2_overlapped_peer_reduction_matches_nccl():
+    """Gradient buckets reduced in place by the peer kernel while backward still runs (the default,
+    with weight gradients on their side stream) give the parameters of the plain NCCL path."""
+    _need(2)
+    over = run_ranks(2, _engine_dp2_params, (), backend="nccl")
+    plain = run_ranks(2, _engine_dp2_params, ("--no-overlap-grad-sync",), backend="nccl")
+    nccl = run_ranks(2, _engine_dp2_params, ("--grad-sync-backend", "collective"), backend="nccl")
+    assert over[0]["direct"] > 0 and over[0]["overlapped"] > 0 and plain[0]["overlapped"] == 0
+    assert torch.equal(over[0]["params"], over[1]["params"])            # replicas stay identical
+    for a in (over, plain):
+        diff = (a[0]["params"] - nccl[0]["params"]).abs()
+        # bf16 weights: a different summation order may flip the last bit of a few values (1 ulp at 1.0 = 2^-7)
+        assert diff.max().item() <= 2 ** -7 and diff.mean().item() < 1e-5, (diff.max().item(), diff.mean().item())
+        assert abs(a[0]["loss"] - nccl[0]["loss"]) < 2e-2
