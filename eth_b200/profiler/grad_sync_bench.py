@@ -93,6 +93,7 @@ def main(argv=None):
     torch_opt = torch.optim.AdamW([torch_master], lr=1.5e-4, weight_decay=0.01, fused=True)
 
     def adam_ours():
+        ctrl[:2].zero_()
         native.lib().grad_norm_sq(mine, 1.0, ctrl)
         native.lib().fused_adam(param16, master, mine, m1, m2, ctrl, 1.5e-4, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, 1.0, True, True)
 
@@ -147,7 +148,7 @@ def main(argv=None):
             for tab in tables:
                 epoch2[0] += 1
                 native.lib().peer_flags(flags2.ptrs, rank, epoch2[0], 0, 0, st)
-                native.lib().peer_reduce_pieces(sym.ptrs, flags2.ptrs, rank, epoch2[0], tab, code, 1.0)
+                native.lib().peer_reduce_pieces(sym.ptrs, flags2.ptrs, rank, epoch2[0], tab, code, 1.0 / world)   # mean: values stay bounded over repeats
             if wait:
                 native.lib().peer_flags(flags2.ptrs, rank, epoch2[0], -1, 8, st)
 
