@@ -9,8 +9,9 @@ derived `world_size`, `total_gbs`, `pipeline_sample_offsets`, `topology_fingerpr
 (:387-432). Hashes are sha256 over compact sorted-key JSON, so a config normalized here and by the
 reference carries the same `config_hash`.
 
-The implementation is a small declarative validator (`_Field` specs + dataclass-free dict output)
-rather than a port: the output is plain JSON-serialisable dicts because that *is* the contract.
+A pipeline is read by `_PipelineReader`, which runs the clauses of the contract in a fixed order;
+the two spellings of a topology field are handled by `TopologyField`. The output is plain
+JSON-serialisable dicts because that *is* the contract.
 """
 from __future__ import annotations
 
@@ -53,7 +54,6 @@ PIPE_KEYS = frozenset({
     "model_parallel_size_of_each_stage", "node_info", "num_gpus", "num_ops_in_each_stage",
     "num_stages", "pipeline_index", "recompute_ops", "resharding_stages",
 })
-# (field stem, default when both spellings are absent -- only CP has one)
 TOPOLOGY_STEMS = ("model_parallel_size", "data_parallel_size", "context_parallel_size", "algo")
 
 
@@ -133,155 +133,192 @@ def _resolve_model_impl(config: Dict[str, Any], op_totals: Sequence[int]) -> str
     return guesses[0]
 
 
-def _stage_list(pipe, key, stages):
-    v = pipe.get(key)
-    if not isinstance(v, list) or len(v) != stages:
-        raise ConfigError(f"{key} stage list length must equal num_stages")
-    return v
+# ------------------------------------------------------------------------------------------
+# one pipeline: a reader object that turns the raw dict into the canonical one, clause by clause
+# ------------------------------------------------------------------------------------------
+class TopologyField:
+    """A per-op topology field that may be written per stage (`<stem>_of_each_stage`, one value per
+    stage) or per op (`<stem>_of_each_op`, one list per stage). Canonical form: per op. Both
+    spellings, if present, must say the same; values must not change inside a stage."""
+
+    def __init__(self, stem: str, default=None):
+        self.stem, self.default = stem, default
+        self.brief_key, self.full_key = f"{stem}_of_each_stage", f"{stem}_of_each_op"
+
+    def _expanded_brief(self, pipe, stage_ops):
+        brief = pipe.get(self.brief_key)
+        if brief is None:
+            if self.full_key in pipe or self.default is None:
+                return None
+            brief = [self.default] * len(stage_ops)
+        if not isinstance(brief, list) or len(brief) != len(stage_ops):
+            raise ConfigError(f"{self.brief_key} stage list length must equal num_stages")
+        return [[value] * count for value, count in zip(brief, stage_ops)]
+
+    def _checked_full(self, pipe, stage_ops):
+        full = pipe.get(self.full_key)
+        if full is None:
+            return None
+        if not isinstance(full, list) or len(full) != len(stage_ops):
+            raise ConfigError(f"{self.full_key} stage list length must equal num_stages")
+        for stage, (values, count) in enumerate(zip(full, stage_ops)):
+            if not isinstance(values, list) or len(values) != count:
+                raise ConfigError(f"{self.full_key} stage {stage} length must equal its op count")
+            if any(v != values[0] for v in values):
+                raise ConfigError(f"intra-stage constancy violated for {self.full_key} at stage {stage}")
+        return [list(values) for values in full]
+
+    def read(self, pipe, stage_ops):
+        brief, full = self._expanded_brief(pipe, stage_ops), self._checked_full(pipe, stage_ops)
+        if brief is None and full is None:
+            raise ConfigError(f"missing {self.brief_key} or {self.full_key}")
+        if brief is not None and full is not None and brief != full:
+            raise ConfigError(f"brief and expanded {self.stem} values conflict")
+        return full if full is not None else brief
 
 
-def _per_op_field(pipe, stem, stage_ops):
-    """Canonical per-op nested list of one topology field from either spelling."""
-    k_stage, k_op = f"{stem}_of_each_stage", f"{stem}_of_each_op"
-    by_stage, by_op = pipe.get(k_stage), pipe.get(k_op)
-    if by_stage is None and by_op is None and stem == "context_parallel_size":
-        by_stage = [1] * len(stage_ops)
-    from_stage = None
-    if by_stage is not None:
-        if not isinstance(by_stage, list) or len(by_stage) != len(stage_ops):
-            raise ConfigError(f"{k_stage} stage list length must equal num_stages")
-        from_stage = [[v] * n for v, n in zip(by_stage, stage_ops)]
-    if by_op is not None:
-        if not isinstance(by_op, list) or len(by_op) != len(stage_ops):
-            raise ConfigError(f"{k_op} stage list length must equal num_stages")
-        out = []
-        for s, (vals, n) in enumerate(zip(by_op, stage_ops)):
-            if not isinstance(vals, list) or len(vals) != n:
-                raise ConfigError(f"{k_op} stage {s} length must equal its op count")
-            if len(set(vals)) != 1:
-                raise ConfigError(f"intra-stage constancy violated for {k_op} at stage {s}")
-            out.append(list(vals))
-        if from_stage is not None and out != from_stage:
-            raise ConfigError(f"brief and expanded {stem} values conflict")
+TOPOLOGY_FIELDS = (TopologyField("model_parallel_size"), TopologyField("data_parallel_size"),
+                   TopologyField("context_parallel_size", default=1), TopologyField("algo"))
+
+
+class _PipelineReader:
+    """Reads one raw pipeline dict. `canonical()` runs the clauses of the contract in a fixed order
+    (the first violated clause is the one reported) and returns the canonical dict."""
+
+    def __init__(self, raw: Dict[str, Any], index: int, manifest_ops: int):
+        self.raw, self.index, self.manifest_ops = copy.deepcopy(raw), index, manifest_ops
+        self.stages = 0
+        self.stage_ops: List[int] = []
+        self.per_op: Dict[str, list] = {}
+
+    # -- helpers
+    def _per_stage(self, key):
+        value = self.raw.get(key)
+        if not isinstance(value, list) or len(value) != self.stages:
+            raise ConfigError(f"{key} stage list length must equal num_stages")
+        return value
+
+    def _degree(self, stem):
+        return [values[0] for values in self.per_op[f"{stem}_of_each_op"]]
+
+    # -- clauses
+    def read_stage_layout(self):
+        self.stages = self.raw.get("num_stages")
+        if not _is_pos_int(self.stages):
+            raise ConfigError(f"pipeline {self.index} num_stages must be positive")
+        self.stage_ops = self._per_stage("num_ops_in_each_stage")
+        if not all(_is_pos_int(n) for n in self.stage_ops):
+            raise ConfigError("num_ops_in_each_stage values must be positive integers")
+        if sum(self.stage_ops) != self.manifest_ops:
+            raise ConfigError(f"manifest size mismatch in pipeline {self.index}: expected {self.manifest_ops}, "
+                              f"got {sum(self.stage_ops)}")
+
+    def read_topology_fields(self):
+        for f in TOPOLOGY_FIELDS:
+            self.per_op[f.full_key] = f.read(self.raw, self.stage_ops)
+
+    def check_degrees(self):
+        tp, dp, cp = self._degree("model_parallel_size"), self._degree("data_parallel_size"), self._degree("context_parallel_size")
+        for stage, c in enumerate(cp):
+            if c != 1:
+                raise ConfigError(f"context parallel stage {stage} must be 1 for block-wise sync")
+        for label, values in (("TP", tp), ("DP", dp), ("CP", cp)):
+            if not all(_is_pos_int(v) for v in values):
+                raise ConfigError(f"{label} values must be positive integers")
+        for stage, t in enumerate(tp):
+            if t not in SUPPORTED_TP:
+                raise ConfigError(f"unsupported TP value {t} in pipeline {self.index} stage {stage}; supported TP "
+                                  "values are " + ", ".join(map(str, SUPPORTED_TP)))
+        for stage, (gpus, t, d, c) in enumerate(zip(self._per_stage("num_gpus"), tp, dp, cp)):
+            if gpus != t * d * c:
+                raise ConfigError(f"stage product mismatch in pipeline {self.index} stage {stage}: "
+                                  f"num_gpus={gpus}, TP*DP*CP={t * d * c}")
+
+    def check_batches(self):
+        mbs, gbs = self.raw.get("micro_batch_size"), self.raw.get("global_batch_size")
+        for name, value in (("micro_batch_size", mbs), ("global_batch_size", gbs)):
+            if not _is_pos_int(value):
+                raise ConfigError(f"{name} must be a positive integer")
+        if gbs % mbs:
+            raise ConfigError("micro batch divisibility requires GBS % micro_batch_size == 0")
+        for stage, d in enumerate(self._degree("data_parallel_size")):
+            if mbs % d:
+                raise ConfigError(f"micro batch divisibility failed for pipeline {self.index} stage {stage}: "
+                                  "micro_batch_size % DP != 0")
+
+    def check_recompute(self):
+        for stage, (flags, count) in enumerate(zip(self._per_stage("recompute_ops"), self.stage_ops)):
+            if not isinstance(flags, list) or len(flags) != count:
+                raise ConfigError(f"recompute_ops stage {stage} length must equal its op count")
+
+    CLAUSES = (read_stage_layout, read_topology_fields, check_degrees, check_batches, check_recompute)
+
+    def canonical(self) -> Dict[str, Any]:
+        for clause in self.CLAUSES:
+            clause(self)
+        out = {"pipeline_index": self.index, "global_batch_size": self.raw["global_batch_size"],
+               "micro_batch_size": self.raw["micro_batch_size"], "num_stages": self.stages,
+               "num_gpus": list(self.raw["num_gpus"]), "num_ops_in_each_stage": list(self.stage_ops)}
+        for key in ("checkpoint_activations", "resharding_stages"):
+            out[key] = list(self._per_stage(key))
+        out["recompute_ops"] = self.raw["recompute_ops"]
+        out.update(self.per_op)
         return out
-    if from_stage is None:
-        raise ConfigError(f"missing {k_stage} or {k_op}")
-    return from_stage
 
 
 def _normalize_pipeline(src: Dict[str, Any], index: int, n_ops: int) -> Dict[str, Any]:
-    pipe = copy.deepcopy(src)
-    stages = pipe.get("num_stages")
-    if not _is_pos_int(stages):
-        raise ConfigError(f"pipeline {index} num_stages must be positive")
-    stage_ops = _stage_list(pipe, "num_ops_in_each_stage", stages)
-    if not all(_is_pos_int(c) for c in stage_ops):
-        raise ConfigError("num_ops_in_each_stage values must be positive integers")
-    if sum(stage_ops) != n_ops:
-        raise ConfigError(
-            f"manifest size mismatch in pipeline {index}: expected {n_ops}, got {sum(stage_ops)}")
-    fields = {f"{stem}_of_each_op": _per_op_field(pipe, stem, stage_ops) for stem in TOPOLOGY_STEMS}
-    tp = [v[0] for v in fields["model_parallel_size_of_each_op"]]
-    dp = [v[0] for v in fields["data_parallel_size_of_each_op"]]
-    cp = [v[0] for v in fields["context_parallel_size_of_each_op"]]
-    for s, c in enumerate(cp):
-        if c != 1:
-            raise ConfigError(f"context parallel stage {s} must be 1 for block-wise sync")
-    for label, vals in (("TP", tp), ("DP", dp), ("CP", cp)):
-        if not all(_is_pos_int(v) for v in vals):
-            raise ConfigError(f"{label} values must be positive integers")
-    for s, t in enumerate(tp):
-        if t not in SUPPORTED_TP:
-            raise ConfigError(
-                f"unsupported TP value {t} in pipeline {index} stage {s}; supported TP values are "
-                + ", ".join(map(str, SUPPORTED_TP)))
-    gpus = _stage_list(pipe, "num_gpus", stages)
-    for s, (g, t, d, c) in enumerate(zip(gpus, tp, dp, cp)):
-        if g != t * d * c:
-            raise ConfigError(
-                f"stage product mismatch in pipeline {index} stage {s}: num_gpus={g}, TP*DP*CP={t * d * c}")
-    mbs, gbs = pipe.get("micro_batch_size"), pipe.get("global_batch_size")
-    if not _is_pos_int(mbs):
-        raise ConfigError("micro_batch_size must be a positive integer")
-    if not _is_pos_int(gbs):
-        raise ConfigError("global_batch_size must be a positive integer")
-    if gbs % mbs:
-        raise ConfigError("micro batch divisibility requires GBS % micro_batch_size == 0")
-    for s, d in enumerate(dp):
-        if mbs % d:
-            raise ConfigError(
-                f"micro batch divisibility failed for pipeline {index} stage {s}: micro_batch_size % DP != 0")
-    recompute = _stage_list(pipe, "recompute_ops", stages)
-    for s, (vals, n) in enumerate(zip(recompute, stage_ops)):
-        if not isinstance(vals, list) or len(vals) != n:
-            raise ConfigError(f"recompute_ops stage {s} length must equal its op count")
-    out = {
-        "pipeline_index": index,
-        "global_batch_size": gbs,
-        "micro_batch_size": mbs,
-        "num_stages": stages,
-        "num_gpus": list(gpus),
-        "num_ops_in_each_stage": list(stage_ops),
-        "checkpoint_activations": list(_stage_list(pipe, "checkpoint_activations", stages)),
-        "resharding_stages": list(_stage_list(pipe, "resharding_stages", stages)),
-        "recompute_ops": recompute,
-    }
-    out.update(fields)
-    return out
+    return _PipelineReader(src, index, n_ops).canonical()
+
+
+def _reject_unknown(mapping, allowed, what):
+    extra = sorted(set(mapping) - allowed)
+    if extra:
+        raise ConfigError(f"{what}: {', '.join(extra)}")
+
+
+FINGERPRINT_KEYS = ("num_gpus", "num_ops_in_each_stage", "model_parallel_size_of_each_op",
+                    "data_parallel_size_of_each_op", "context_parallel_size_of_each_op")
 
 
 def normalize_flexpipe_config(config: Dict[str, Any], world_size: Optional[int] = None) -> Dict[str, Any]:
     """Unique canonical representation of an HPP GPT config (raises ConfigError on violations)."""
     if not isinstance(config, dict):
         raise ConfigError("config must be a mapping")
-    extra = sorted(set(config) - TOP_LEVEL_KEYS)
-    if extra:
-        raise ConfigError(f"unknown top-level config field(s): {', '.join(extra)}")
-    pipes = config.get("pipe")
-    if not isinstance(pipes, list) or not pipes:
+    _reject_unknown(config, TOP_LEVEL_KEYS, "unknown top-level config field(s)")
+    raw_pipes = config.get("pipe")
+    if not isinstance(raw_pipes, list) or not raw_pipes:
         raise ConfigError("config must contain at least one pipeline")
-    totals = []
-    for i, pipe in enumerate(pipes):
-        if not isinstance(pipe, dict):
+    op_totals = []
+    for i, raw in enumerate(raw_pipes):
+        if not isinstance(raw, dict):
             raise ConfigError(f"pipeline {i} must be a mapping")
-        extra = sorted(set(pipe) - PIPE_KEYS)
-        if extra:
-            raise ConfigError(f"pipeline {i} has unknown field(s): {', '.join(extra)}")
-        counts = pipe.get("num_ops_in_each_stage")
+        _reject_unknown(raw, PIPE_KEYS, f"pipeline {i} has unknown field(s)")
+        counts = raw.get("num_ops_in_each_stage")
         if not isinstance(counts, list) or not counts:
             raise ConfigError(f"pipeline {i} is missing num_ops_in_each_stage")
-        totals.append(sum(counts))
-    impl = _resolve_model_impl(config, totals)
+        op_totals.append(sum(counts))
+    impl = _resolve_model_impl(config, op_totals)
     manifest = build_manifest(impl, config["num_layers"])
-    norm_pipes = [_normalize_pipeline(p, i, len(manifest["ordered_ops"])) for i, p in enumerate(pipes)]
+    pipes = [_normalize_pipeline(raw, i, len(manifest["ordered_ops"])) for i, raw in enumerate(raw_pipes)]
+
     hidden, heads = config.get("hidden_size"), config.get("num_attention_heads")
-    for pi, pipe in enumerate(norm_pipes):
-        for si, vals in enumerate(pipe["model_parallel_size_of_each_op"]):
-            t = vals[0]
-            if not isinstance(hidden, int) or hidden % t or not isinstance(heads, int) or heads % t:
-                raise ConfigError(
-                    f"TP constraint failed in pipeline {pi} stage {si}: hidden_size={hidden}, "
-                    f"num_attention_heads={heads}, TP={t}")
-    world = sum(sum(p["num_gpus"]) for p in norm_pipes)
+    for pi, pipe in enumerate(pipes):
+        for si, per_op in enumerate(pipe["model_parallel_size_of_each_op"]):
+            divisible = isinstance(hidden, int) and isinstance(heads, int) and hidden % per_op[0] == 0 and heads % per_op[0] == 0
+            if not divisible:
+                raise ConfigError(f"TP constraint failed in pipeline {pi} stage {si}: hidden_size={hidden}, "
+                                  f"num_attention_heads={heads}, TP={per_op[0]}")
+    world = sum(sum(p["num_gpus"]) for p in pipes)
     if world_size is not None and world_size != world:
         raise ConfigError(f"world size mismatch: expected {world}, got {world_size}")
-    offsets, running = [], 0
-    for p in norm_pipes:
-        offsets.append(running)
-        running += p["global_batch_size"]
+    batch_sizes = [p["global_batch_size"] for p in pipes]
+    offsets = [sum(batch_sizes[:i]) for i in range(len(batch_sizes))]
+
     out = {k: copy.deepcopy(v) for k, v in config.items() if k not in ("pipe", "model_impl")}
-    out.update({
-        "model_impl": impl,
-        "manifest": manifest,
-        "pipe": norm_pipes,
-        "world_size": world,
-        "total_gbs": running,
-        "pipeline_sample_offsets": offsets,
-    })
-    topo_keys = ("num_gpus", "num_ops_in_each_stage", "model_parallel_size_of_each_op",
-                 "data_parallel_size_of_each_op", "context_parallel_size_of_each_op")
+    out.update(model_impl=impl, manifest=manifest, pipe=pipes, world_size=world, total_gbs=sum(batch_sizes),
+               pipeline_sample_offsets=offsets)
     out["topology_fingerprint"] = canonical_hash(
-        {"world_size": world, "pipelines": [{k: p[k] for k in topo_keys} for p in norm_pipes]})
+        {"world_size": world, "pipelines": [{k: p[k] for k in FINGERPRINT_KEYS} for p in pipes]})
     out["config_hash"] = canonical_hash(out)
     return out
 

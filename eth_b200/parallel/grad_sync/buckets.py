@@ -1,28 +1,33 @@
 """Bucket placement of canonical fragments and the deterministic process-group registry.
 
-`tensor` mode: one bucket per fragment. `block` mode (block-wise all-reduce): consecutive
-fragments with the same (process group, dtype, reduction) are concatenated until the byte cap;
-a fragment is never split and an oversized fragment stands alone
-(reference: eth/runtime/megatron/grad_sync/bucket_plan.py:115-152). The plan records, per rank,
-the exact payload bytes and the largest bucket per dtype (the size of the persistent scratch),
-and five hashes that all ranks compare before the first step.
+A bucket is the unit of one gradient collective. Fragments are first put into *lanes*: everything
+that may share a collective has the same (process group, gradient dtype, reduction kind). Inside a
+lane, in semantic order,
+  `tensor` mode cuts after every fragment (one collective per fragment), and
+  `block` mode (block-wise all-reduce) cuts whenever the next fragment would push the running size
+  over the byte cap; a fragment is never split, so one that alone exceeds the cap becomes a bucket
+  of its own, flagged `oversized`
+(reference behaviour: eth/runtime/megatron/grad_sync/bucket_plan.py:115-152). The plan also
+records, per rank, the exact payload bytes and the largest bucket per dtype (the size of the
+persistent scratch), and the hashes that all ranks compare before the first step (:155-241).
 """
 from __future__ import annotations
 
 from dataclasses import asdict, dataclass
-from typing import Callable, Dict, Tuple
+from itertools import groupby
+from typing import Callable, Dict, Iterator, List, Sequence, Tuple
 
-from .planner import CanonicalFragmentPlan, ProcessGroupSpec, _sort_key, stable_hash
+from .planner import CanonicalFragmentPlan, ProcessGroupSpec, fragment_order, stable_hash
 
-DTYPE_BYTES = {"float16": 2, "bfloat16": 2, "float32": 4, "float64": 8}
+SYNC_MODES = ("tensor", "block")
+_ELEMENT_BYTES = {"float16": 2, "bfloat16": 2, "float32": 4, "float64": 8}
 
 
 def dtype_bytes(name: str) -> int:
-    key = name[6:] if name.startswith("torch.") else name
-    try:
-        return DTYPE_BYTES[key]
-    except KeyError as exc:
-        raise ValueError(f"unsupported gradient dtype {name!r}") from exc
+    short = name.split(".", 1)[1] if name.startswith("torch.") else name
+    if short not in _ELEMENT_BYTES:
+        raise ValueError(f"unsupported gradient dtype {name!r}")
+    return _ELEMENT_BYTES[short]
 
 
 @dataclass(frozen=True)
@@ -67,136 +72,141 @@ class GradientSyncPlan:
     global_plan_hash: str
 
     def buckets_for_rank(self, rank: int):
-        ranks_of = {g.process_group_id: g.ranks for g in self.process_groups}
-        return tuple(b for b in self.global_bucket_order if rank in ranks_of[b.process_group_id])
+        members = {g.process_group_id: g.ranks for g in self.process_groups}
+        return tuple(b for b in self.global_bucket_order if rank in members[b.process_group_id])
 
     def collective_count_for_rank(self, rank: int) -> int:
         return len(self.buckets_for_rank(rank))
 
 
-def _close_bucket(frags, cap_bytes, groups) -> CommunicationBucketSpec:
-    head = frags[0]
-    width = dtype_bytes(head.grad_dtype)
-    placements, cursor = [], 0
-    for f in frags:
-        placements.append(BucketFragmentPlacement(f.fragment_id, cursor))
-        cursor += f.numel
-    total_bytes = cursor * width
+def _lane_of(fragment) -> tuple:
+    return fragment.process_group_id, fragment.grad_dtype, fragment.reduction_semantics
+
+
+def _cut_lane(fragments: Sequence, mode: str, cap_bytes: int) -> Iterator[List]:
+    """Split one lane into runs of fragments, each run becoming a bucket."""
+    run, used = [], 0
+    for frag in fragments:
+        size = frag.numel * dtype_bytes(frag.grad_dtype)
+        if run and (mode == "tensor" or used + size > cap_bytes):
+            yield run
+            run, used = [], 0
+        run.append(frag)
+        used += size
+    if run:
+        yield run
+
+
+def _seal(run, cap_bytes: int, group_ranks) -> CommunicationBucketSpec:
+    first, last = run[0], run[-1]
+    offsets, total = [], 0
+    for frag in run:
+        offsets.append(BucketFragmentPlacement(frag.fragment_id, total))
+        total += frag.numel
+    nbytes = total * dtype_bytes(first.grad_dtype)
     digest = stable_hash({
-        "version": 1, "process_group_id": head.process_group_id,
-        "process_group_ranks": groups[head.process_group_id].ranks, "grad_dtype": head.grad_dtype,
-        "reduction_semantics": head.reduction_semantics, "fragments": [asdict(f) for f in frags],
-        "placements": [asdict(p) for p in placements], "exact_numel": cursor, "exact_bytes": total_bytes})
+        "version": 1, "process_group_id": first.process_group_id, "process_group_ranks": group_ranks,
+        "grad_dtype": first.grad_dtype, "reduction_semantics": first.reduction_semantics,
+        "fragments": [asdict(f) for f in run], "placements": [asdict(p) for p in offsets],
+        "exact_numel": total, "exact_bytes": nbytes})
     return CommunicationBucketSpec(
-        bucket_id="bucket-" + digest[:20], process_group_id=head.process_group_id,
-        grad_dtype=head.grad_dtype, reduction_semantics=head.reduction_semantics,
-        placements=tuple(placements), exact_numel=cursor, exact_bytes=total_bytes,
-        logical_region_begin=head.logical_region_key, logical_region_end=frags[-1].logical_region_key,
-        semantic_hash=digest, oversized=total_bytes > cap_bytes)
+        bucket_id="bucket-" + digest[:20], process_group_id=first.process_group_id, grad_dtype=first.grad_dtype,
+        reduction_semantics=first.reduction_semantics, placements=tuple(offsets), exact_numel=total,
+        exact_bytes=nbytes, logical_region_begin=first.logical_region_key,
+        logical_region_end=last.logical_region_key, semantic_hash=digest, oversized=nbytes > cap_bytes)
 
 
 def bucketize(fragments, sync_mode: str, cap_bytes: int, groups) -> Tuple[CommunicationBucketSpec, ...]:
-    if sync_mode not in ("tensor", "block"):
+    """`fragments` must already be ordered so that the members of a lane are adjacent."""
+    if sync_mode not in SYNC_MODES:
         raise ValueError(f"unsupported sync mode {sync_mode!r}")
     if cap_bytes <= 0:
         raise ValueError("bucket_cap_bytes must be positive")
-    if sync_mode == "tensor":
-        return tuple(_close_bucket((f,), cap_bytes, groups) for f in fragments)
-    out, run, run_bytes, run_key = [], [], 0, None
-    for f in fragments:
-        size = f.numel * dtype_bytes(f.grad_dtype)
-        key = (f.process_group_id, f.grad_dtype, f.reduction_semantics)
-        if run and (key != run_key or run_bytes + size > cap_bytes):
-            out.append(_close_bucket(tuple(run), cap_bytes, groups))
-            run, run_bytes = [], 0
-        run.append(f)
-        run_bytes += size
-        run_key = key
-        if size > cap_bytes:  # oversized fragments stand alone
-            out.append(_close_bucket(tuple(run), cap_bytes, groups))
-            run, run_bytes, run_key = [], 0, None
-    if run:
-        out.append(_close_bucket(tuple(run), cap_bytes, groups))
-    return tuple(out)
+    buckets = []
+    for lane, members in groupby(fragments, key=_lane_of):
+        for run in _cut_lane(list(members), sync_mode, cap_bytes):
+            buckets.append(_seal(run, cap_bytes, groups[lane[0]].ranks))
+    return tuple(buckets)
 
 
 def build_gradient_sync_plan(fragment_plan: CanonicalFragmentPlan, sync_mode: str, bucket_cap_bytes: int,
                              model_impl: str, manifest_hash: str, topology_hash: str) -> GradientSyncPlan:
     groups = tuple(sorted(fragment_plan.process_groups, key=lambda g: g.ranks))
-    by_id = {g.process_group_id: g for g in groups}
-    index = {g.process_group_id: i for i, g in enumerate(groups)}
-    frags = tuple(sorted(fragment_plan.fragments, key=lambda f: _sort_key(f.semantic_key)))
-    dtype_rank = {d: i for i, d in enumerate(sorted({f.grad_dtype for f in frags}))}
-    placement_order = tuple(sorted(
-        frags, key=lambda f: (index[f.process_group_id], dtype_rank[f.grad_dtype], f.reduction_semantics,
-                              _sort_key(f.semantic_key))))
-    buckets = bucketize(placement_order, sync_mode, bucket_cap_bytes, by_id)
-    payload: Dict[int, int] = {}
-    scratch: Dict[tuple, int] = {}
+    group_by_id = {g.process_group_id: g for g in groups}
+    group_pos = {g.process_group_id: i for i, g in enumerate(groups)}
+    fragments = tuple(sorted(fragment_plan.fragments, key=lambda f: fragment_order(f.semantic_key)))
+    dtype_pos = {name: i for i, name in enumerate(sorted({f.grad_dtype for f in fragments}))}
+    laned = sorted(fragments, key=lambda f: (group_pos[f.process_group_id], dtype_pos[f.grad_dtype],
+                                             f.reduction_semantics, fragment_order(f.semantic_key)))
+    buckets = bucketize(laned, sync_mode, bucket_cap_bytes, group_by_id)
+
+    payload_bytes: Dict[int, int] = {}
+    scratch_numel: Dict[tuple, int] = {}
     for b in buckets:
-        for r in by_id[b.process_group_id].ranks:
-            payload[r] = payload.get(r, 0) + b.exact_bytes
-            scratch[(r, b.grad_dtype)] = max(scratch.get((r, b.grad_dtype), 0), b.exact_numel)
-    bindings_payload = [(r, [asdict(x) for x in bs]) for r, bs in fragment_plan.local_bindings_by_rank]
-    frag_hash = stable_hash({"canonical_fragments": [asdict(f) for f in frags],
-                             "local_fragment_bindings_by_rank": bindings_payload})
+        for rank in group_by_id[b.process_group_id].ranks:
+            payload_bytes[rank] = payload_bytes.get(rank, 0) + b.exact_bytes
+            slot = (rank, b.grad_dtype)
+            scratch_numel[slot] = max(scratch_numel.get(slot, 0), b.exact_numel)
+
+    bindings_blob = [(rank, [asdict(x) for x in bound]) for rank, bound in fragment_plan.local_bindings_by_rank]
+    fragments_blob = [asdict(f) for f in fragments]
+    fragment_hash = stable_hash({"canonical_fragments": fragments_blob,
+                                 "local_fragment_bindings_by_rank": bindings_blob})
     plan_hash = stable_hash({
         "version": 1, "sync_mode": sync_mode, "bucket_cap_bytes": bucket_cap_bytes, "model_impl": model_impl,
-        "manifest_hash": manifest_hash, "topology_hash": topology_hash, "fragment_hash": frag_hash,
-        "process_groups": [asdict(g) for g in groups], "canonical_fragments": [asdict(f) for f in frags],
-        "local_fragment_bindings_by_rank": bindings_payload, "buckets": [asdict(b) for b in buckets]})
+        "manifest_hash": manifest_hash, "topology_hash": topology_hash, "fragment_hash": fragment_hash,
+        "process_groups": [asdict(g) for g in groups], "canonical_fragments": fragments_blob,
+        "local_fragment_bindings_by_rank": bindings_blob, "buckets": [asdict(b) for b in buckets]})
     return GradientSyncPlan(
         version=1, sync_mode=sync_mode, bucket_cap_bytes=bucket_cap_bytes, model_impl=model_impl,
         op_manifest_hash=manifest_hash, process_groups=groups,
-        process_group_index_by_id=tuple((g.process_group_id, i) for i, g in enumerate(groups)),
-        canonical_fragments=frags, local_fragment_bindings_by_rank=fragment_plan.local_bindings_by_rank,
-        global_bucket_order=buckets, max_scratch_numel_by_rank_and_dtype=tuple(sorted(scratch.items())),
-        exact_payload_bytes_by_rank=tuple(sorted(payload.items())), padding_payload_bytes=0,
+        process_group_index_by_id=tuple(sorted(group_pos.items(), key=lambda kv: kv[1])),
+        canonical_fragments=fragments, local_fragment_bindings_by_rank=fragment_plan.local_bindings_by_rank,
+        global_bucket_order=buckets, max_scratch_numel_by_rank_and_dtype=tuple(sorted(scratch_numel.items())),
+        exact_payload_bytes_by_rank=tuple(sorted(payload_bytes.items())), padding_payload_bytes=0,
         global_topology_hash=topology_hash, global_manifest_hash=manifest_hash,
-        global_fragment_hash=frag_hash, global_plan_hash=plan_hash)
+        global_fragment_hash=fragment_hash, global_plan_hash=plan_hash)
 
 
 class ProcessGroupRegistry:
-    """Creates every gradient-sync group exactly once, in one global order (sorted by ranks), on
-    every rank -- the order `new_group` requires -- and freezes the table afterwards."""
+    """Process groups of the plan, created once.
+
+    `torch.distributed.new_group` must be called by every rank, for every group, in the same order;
+    the registry walks the groups sorted by their rank tuples. After `initialize` the table is
+    frozen: asking for an unknown id is an error, a second `initialize` does nothing."""
 
     def __init__(self, process_groups, create_group: Callable[[Tuple[int, ...]], object]):
-        self._specs = tuple(sorted(process_groups, key=lambda g: g.ranks))
-        self._create = create_group
-        self._handles: Dict[str, object] = {}
-        self._created = 0
+        self._ranks_by_id = {}
+        order = sorted(process_groups, key=lambda g: g.ranks)
+        for g in order:
+            if g.process_group_id in self._ranks_by_id:
+                raise ValueError(f"duplicate process group id {g.process_group_id}")
+            if list(g.ranks) != sorted(set(g.ranks)):
+                raise ValueError(f"process group ranks must be sorted and unique: {g.ranks}")
+            self._ranks_by_id[g.process_group_id] = g.ranks
+        if len(set(self._ranks_by_id.values())) != len(self._ranks_by_id):
+            raise ValueError("duplicate process group ranks in the plan")
+        self._order = [g.process_group_id for g in order]
+        self._make = create_group
+        self._live: Dict[str, object] = {}
+        self.creation_count = 0
 
     def initialize(self) -> None:
-        if self._handles:
+        if self._live:
             return
-        ids, rank_sets = set(), set()
-        for g in self._specs:
-            if g.process_group_id in ids:
-                raise ValueError(f"duplicate process group id {g.process_group_id}")
-            if g.ranks in rank_sets:
-                raise ValueError(f"duplicate process group ranks {g.ranks}")
-            if g.ranks != tuple(sorted(set(g.ranks))):
-                raise ValueError(f"process group ranks must be sorted and unique: {g.ranks}")
-            ids.add(g.process_group_id)
-            rank_sets.add(g.ranks)
-            self._handles[g.process_group_id] = self._create(g.ranks)
-            self._created += 1
+        for gid in self._order:
+            self._live[gid] = self._make(self._ranks_by_id[gid])
+            self.creation_count += 1
 
     @property
     def group_count(self) -> int:
-        return len(self._handles)
-
-    @property
-    def creation_count(self) -> int:
-        return self._created
+        return len(self._live)
 
     def handle(self, process_group_id: str):
-        if process_group_id not in self._handles:
-            raise KeyError(f"process group {process_group_id} is not initialized")
-        return self._handles[process_group_id]
+        try:
+            return self._live[process_group_id]
+        except KeyError:
+            raise KeyError(f"process group {process_group_id} is not initialized") from None
 
     def ranks(self, process_group_id: str) -> Tuple[int, ...]:
-        for g in self._specs:
-            if g.process_group_id == process_group_id:
-                return g.ranks
-        raise KeyError(process_group_id)
+        return self._ranks_by_id[process_group_id]

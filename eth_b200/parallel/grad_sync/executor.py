@@ -20,7 +20,7 @@ from typing import Callable, Dict, Iterable, Optional
 
 import torch
 
-from .runtime_evidence import GradientRuntimeEvidenceRecorder
+from . import runtime_evidence
 
 
 def dtype_name(dtype) -> str:
@@ -50,9 +50,8 @@ class GradientBucketExecutor:
         self._scratch = self._allocate_scratch(scratch_factory)
         self._tables: Dict[str, dict] = {}
         self.collectives_issued = 0
-        self._evidence = (GradientRuntimeEvidenceRecorder(plan, global_rank, process_group_registry,
-                                                          self._scratch, runtime_evidence_dir)
-                          if runtime_evidence_dir else None)
+        self._evidence = (runtime_evidence.start_log(plan, global_rank, process_group_registry, self._scratch,
+                                                     runtime_evidence_dir) if runtime_evidence_dir else None)
         if self._peer is not None and hasattr(self._peer, "attach"):
             self._peer.attach(self)
 
@@ -229,7 +228,7 @@ class GradientBucketExecutor:
         payload = self._scratch[bucket.grad_dtype][:bucket.exact_numel]
         self.pack(bucket, payload)
         if self._evidence is not None:
-            self._evidence.observe_packed_bucket(bucket, payload)
+            runtime_evidence.record_bucket(self._evidence, bucket, payload)
         if self._peer is not None and self._peer.handles(bucket):
             reduced = self._peer.reduce_packed(bucket, payload, normalization_scale)
             self.unpack(bucket, reduced, 1.0)
@@ -253,13 +252,14 @@ class GradientBucketExecutor:
     def execute(self, normalization_scale=1.0, skip=()):
         """Run all buckets of this rank in plan order, except those in `skip` (already reduced)."""
         if self._evidence is not None:
-            self._evidence.begin_execution(normalization_scale)
+            runtime_evidence.open_iteration(self._evidence, normalization_scale)
         for bucket in self._my_buckets:
             if bucket.bucket_id not in skip:
                 self.execute_bucket(bucket, normalization_scale)
         self.finish()
         if self._evidence is not None:
-            self._evidence.finish_execution()
+            runtime_evidence.close_iteration(self._evidence)
+            runtime_evidence.write_report(self._evidence, self.plan)
 
     def finish(self) -> None:
         """Make the results of in-place peer reductions issued so far (on any stream the current one

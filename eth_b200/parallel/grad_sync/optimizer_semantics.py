@@ -1,160 +1,182 @@
 """Canonical parameter consistency, gradient-norm ownership and clipping.
 
-Every fragment has one owner rank (the smallest rank of its group). Quantities that must be
-counted once per *logical* element -- the global gradient norm, the zero count -- are computed
-from owned fragments only and summed over the world; operations that must agree across all
-holders of a logical element -- initial parameters, optimizer moments after a checkpoint load --
-are broadcast fragment by fragment from the owner
-(reference: eth/runtime/megatron/grad_sync/optimizer_semantics.py:258-279 parameters,
-:318-358 optimizer state, :537-604 norm / clip / zero count).
+Every fragment has one owner rank (the smallest rank of its group). Two kinds of operation build
+on that:
 
-Tied weights need no extra path here: both copies of a tied weight are holders of the same
-fragments (see planner), so the fragment broadcasts and the fragment all-reduce keep them equal.
+  * "make all holders equal": the owner's values of a fragment are broadcast to the other holders.
+    Used for the initial parameters and, after a checkpoint load, for parameters and optimizer
+    moments. One routine (`_replicate`) does it for any tensor shaped like the parameter.
+  * "count once": the global gradient norm and the zero count take each logical element from its
+    owner only and are summed over the world.
+
+(reference: eth/runtime/megatron/grad_sync/optimizer_semantics.py:258-279 parameters, :318-358
+optimizer state, :537-604 norm / clip / zero count). Tied weights need no extra path here: both
+copies of a tied weight are holders of the same fragments (see planner), so the fragment
+broadcasts and the fragment all-reduce keep them equal.
 """
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
+from typing import Callable, Iterator, List, Tuple
 
 import torch
 
 
+@dataclass(frozen=True)
+class _BoundFragment:
+    """A fragment this rank holds: where it sits in tensors shaped like the local parameter."""
+    fragment: object
+    logical_id: str
+    group_ranks: Tuple[int, ...]
+    axis: int                                    # -1: the whole tensor (replicated parameter)
+    pieces: Tuple[Tuple[int, int], ...]          # (offset, length) along `axis`
+    local_numel: int
+
+    @property
+    def owner(self) -> int:
+        return min(self.group_ranks)
+
+    def views(self, tensor: torch.Tensor) -> List[torch.Tensor]:
+        if tensor.numel() != self.local_numel:
+            raise ValueError(f"logical_param_id {self.logical_id} source shape mismatch")
+        if self.axis < 0:
+            return [tensor]
+        return [tensor.narrow(self.axis, off, n) for off, n in self.pieces]
+
+    def read(self, tensor: torch.Tensor) -> torch.Tensor:
+        flat = torch.cat([v.reshape(-1) for v in self.views(tensor)])
+        if flat.numel() != self.fragment.numel:
+            raise ValueError(f"fragment {self.fragment.fragment_id} logical_param_id {self.logical_id} "
+                             f"packed {flat.numel()}, expected {self.fragment.numel}")
+        return flat
+
+    def write(self, tensor: torch.Tensor, flat: torch.Tensor) -> None:
+        at = 0
+        for v in self.views(tensor):
+            v.copy_(flat[at:at + v.numel()].view(v.shape))
+            at += v.numel()
+
+
+def _unique_by_logical_id(items, what):
+    table = {}
+    for it in items:
+        if it.logical_param_id in table:
+            raise ValueError(f"duplicate {what} for logical_param_id {it.logical_param_id}")
+        table[it.logical_param_id] = it
+    return table
+
+
+def _parameter_shaped_state(state: dict, parameter, logical_id) -> Iterator[Tuple[str, torch.Tensor, str]]:
+    """(name, tensor, kind) of the tensor entries of one parameter's optimizer state, by name."""
+    for name in sorted(state):
+        t = state[name]
+        if not isinstance(t, torch.Tensor):
+            continue
+        if tuple(t.shape) == tuple(parameter.shape):
+            yield name, t, "parameter"
+        elif t.numel() == 1:
+            yield name, t, "scalar"
+        else:
+            raise ValueError(f"optimizer state shape mismatch for {logical_id}.{name}: {tuple(t.shape)}")
+
+
 class CanonicalOptimizerSemantics:
     def __init__(self, plan, global_rank, local_descriptors, local_runtime_bindings, control_device="cpu"):
-        self.plan = plan
-        self.global_rank = global_rank
+        self.plan, self.global_rank = plan, global_rank
         self.control_device = torch.device(control_device)
-        self._fragments = {f.fragment_id: f for f in plan.canonical_fragments}
-        self._groups = {g.process_group_id: g for g in plan.process_groups}
-        self._descriptors = self._index(local_descriptors, "descriptor")
-        self._bindings = self._index(local_runtime_bindings, "runtime binding")
-        self._by_param = {id(b.parameter): b.logical_param_id for b in local_runtime_bindings}
-        self._opt_grads = {}
-        self._specs = {b.fragment_id: b for r, bs in plan.local_fragment_bindings_by_rank if r == global_rank
-                       for b in bs}
+        descriptors = _unique_by_logical_id(local_descriptors, "descriptor")
+        self._bindings = _unique_by_logical_id(local_runtime_bindings, "runtime binding")
+        self._logical_id_of = {id(b.parameter): b.logical_param_id for b in local_runtime_bindings}
+        self._step_gradients = {}       # logical id -> the tensor the optimizer steps on, if not main_grad
+        ranks_of = {g.process_group_id: g.ranks for g in plan.process_groups}
+        mine = {b.fragment_id: b for b in dict(plan.local_fragment_bindings_by_rank).get(global_rank, ())}
+        self._bound: List[_BoundFragment] = []
+        for frag in plan.canonical_fragments:            # plan order = the order every holder walks
+            spec = mine.get(frag.fragment_id)
+            if spec is None:
+                continue
+            desc = descriptors[spec.logical_param_id]
+            local_numel = math.prod(spec.source_segments[0].source_shape) if spec.source_segments[0].source_shape else 1
+            if desc.tensor_parallel:
+                ndim = len(desc.local_shape)
+                axis = desc.partition_dim + ndim if desc.partition_dim < 0 else desc.partition_dim
+                pieces = tuple((s.source_dim_offset, s.source_dim_length) for s in spec.source_segments)
+            else:
+                if len(spec.source_segments) != 1:
+                    raise ValueError(f"logical_param_id {spec.logical_param_id} replicated binding must have one segment")
+                axis, pieces = -1, ()
+            self._bound.append(_BoundFragment(frag, spec.logical_param_id, ranks_of[frag.process_group_id], axis,
+                                              pieces, local_numel))
 
-    @staticmethod
-    def _index(items, kind):
-        out = {}
-        for it in items:
-            if it.logical_param_id in out:
-                raise ValueError(f"duplicate {kind} for logical_param_id {it.logical_param_id}")
-            out[it.logical_param_id] = it
-        return out
-
-    # -- gradient tensors the optimizer actually steps on (fp32 copies of main_grad, if any)
+    # ------------------------------------------------------------------ which gradient tensor counts
     def bind_optimizer_gradient(self, model_parameter, gradient):
-        lid = self._by_param.get(id(model_parameter))
+        """Tell the semantics layer that the optimizer steps on `gradient` (e.g. an fp32 copy) rather
+        than on the parameter's `main_grad`."""
+        lid = self._logical_id_of.get(id(model_parameter))
         if lid is None:
             raise ValueError("model parameter has no canonical gradient binding")
         if tuple(gradient.shape) != tuple(model_parameter.shape):
             raise ValueError(f"optimizer gradient shape mismatch for {lid}: expected "
                              f"{tuple(model_parameter.shape)}, got {tuple(gradient.shape)}")
-        self._opt_grads[lid] = gradient
+        self._step_gradients[lid] = gradient
 
-    def _gradient(self, lid):
-        return self._opt_grads.get(lid, self._bindings[lid].main_grad)
+    def _gradient(self, logical_id):
+        return self._step_gradients.get(logical_id, self._bindings[logical_id].main_grad)
 
-    def _views(self, tensor, spec):
-        desc = self._descriptors[spec.logical_param_id]
-        if not desc.tensor_parallel:
-            if len(spec.source_segments) != 1:
-                raise ValueError(f"logical_param_id {spec.logical_param_id} replicated binding must have one segment")
-            if spec.source_segments[0].flattened_numel != tensor.numel():
-                raise ValueError(f"logical_param_id {spec.logical_param_id} replicated source numel mismatch")
-            yield tensor
-            return
-        axis = desc.partition_dim + (tensor.dim() if desc.partition_dim < 0 else 0)
-        for seg in spec.source_segments:
-            if math.prod(seg.source_shape) != tensor.numel():
-                raise ValueError(f"logical_param_id {spec.logical_param_id} source shape mismatch")
-            yield tensor.narrow(axis, seg.source_dim_offset, seg.source_dim_length)
+    # ------------------------------------------------------------------ make all holders equal
+    # broadcast(payload, source_rank, process_group_id, group_ranks, tag, current_rank)
+    def _replicate(self, tensors_of: Callable, broadcast) -> None:
+        """For every bound fragment, in plan order, and every (tag, tensor) that `tensors_of(binding)`
+        yields: overwrite this rank's slice of the tensor with the owner's."""
+        for bf in self._bound:
+            for tag, tensor, kind in tensors_of(self._bindings[bf.logical_id], bf):
+                label = bf.fragment.fragment_id + tag
+                if kind == "scalar":
+                    box = tensor.reshape(-1).clone()
+                    broadcast(box, bf.owner, bf.fragment.process_group_id, bf.group_ranks, label, self.global_rank)
+                    tensor.copy_(box.view(tensor.shape))
+                else:
+                    flat = bf.read(tensor)
+                    broadcast(flat, bf.owner, bf.fragment.process_group_id, bf.group_ranks, label, self.global_rank)
+                    bf.write(tensor, flat)
 
-    def _gather(self, tensor, spec, frag):
-        out = torch.empty(frag.numel, dtype=tensor.dtype, device=tensor.device)
-        cur = 0
-        for v in self._views(tensor, spec):
-            out[cur:cur + v.numel()].copy_(v.reshape(-1))
-            cur += v.numel()
-        if cur != frag.numel:
-            raise ValueError(f"fragment {frag.fragment_id} logical_param_id {spec.logical_param_id} "
-                             f"packed {cur}, expected {frag.numel}")
-        return out
-
-    def _scatter(self, tensor, spec, frag, payload):
-        cur = 0
-        for v in self._views(tensor, spec):
-            v.copy_(payload[cur:cur + v.numel()].view(v.shape))
-            cur += v.numel()
-        if cur != frag.numel:
-            raise ValueError(f"fragment {frag.fragment_id} unpacked {cur}, expected {frag.numel}")
-
-    def _my_fragments(self):
-        for frag in self.plan.canonical_fragments:
-            spec = self._specs.get(frag.fragment_id)
-            if spec is not None:
-                yield frag, spec, self._bindings[spec.logical_param_id], self._groups[frag.process_group_id]
-
-    # -- broadcasts: broadcast(payload, source_rank, process_group_id, group_ranks, tag, current_rank)
     def synchronize_parameters(self, broadcast):
-        for frag, spec, rt, group in self._my_fragments():
-            payload = self._gather(rt.parameter.data, spec, frag)
-            broadcast(payload, min(group.ranks), frag.process_group_id, group.ranks, frag.fragment_id, self.global_rank)
-            self._scatter(rt.parameter.data, spec, frag, payload)
+        self._replicate(lambda binding, bf: [("", binding.parameter.data, "parameter")], broadcast)
 
     def synchronize_shared_root_gradients(self, broadcast):
         """Tied weights are holders of common fragments here, so their gradients are already equal
         after the fragment all-reduce. Kept so callers written against the reference flow work."""
         return None
 
+    def synchronize_optimizer_state(self, state_for_parameter, broadcast):
+        def moments(binding, bf):
+            state = state_for_parameter(binding.parameter)
+            return [(":" + name, t, kind) for name, t, kind in _parameter_shaped_state(state, binding.parameter, bf.logical_id)]
+        self._replicate(moments, broadcast)
+
     def optimizer_state_manifest_for_group(self, process_group_id, state_for_parameter):
+        """What the members of a group compare before optimizer state is replicated."""
         rows = []
-        for frag, spec, rt, _ in self._my_fragments():
-            if frag.process_group_id != process_group_id:
+        for bf in self._bound:
+            if bf.fragment.process_group_id != process_group_id:
                 continue
-            state = state_for_parameter(rt.parameter)
-            entry = []
-            for name in sorted(state):
-                t = state[name]
-                if not isinstance(t, torch.Tensor):
-                    continue
-                if tuple(t.shape) == tuple(rt.parameter.shape):
-                    kind = "parameter"
-                elif t.numel() == 1:
-                    kind = "scalar"
-                else:
-                    raise ValueError(f"optimizer state shape mismatch for {spec.logical_param_id}.{name}: {tuple(t.shape)}")
-                entry.append((name, kind, str(t.dtype)))
-            rows.append((frag.fragment_id, tuple(entry)))
+            parameter = self._bindings[bf.logical_id].parameter
+            entries = tuple((name, kind, str(t.dtype)) for name, t, kind in
+                            _parameter_shaped_state(state_for_parameter(parameter), parameter, bf.logical_id))
+            rows.append((bf.fragment.fragment_id, entries))
         return tuple(rows)
 
-    def synchronize_optimizer_state(self, state_for_parameter, broadcast):
-        for frag, spec, rt, group in self._my_fragments():
-            state = state_for_parameter(rt.parameter)
-            src = min(group.ranks)
-            for name in sorted(state):
-                t = state[name]
-                if not isinstance(t, torch.Tensor):
-                    continue
-                if tuple(t.shape) == tuple(rt.parameter.shape):
-                    payload = self._gather(t, spec, frag)
-                    broadcast(payload, src, frag.process_group_id, group.ranks, f"{frag.fragment_id}:{name}", self.global_rank)
-                    self._scatter(t, spec, frag, payload)
-                elif t.numel() == 1:
-                    payload = t.reshape(-1).clone()
-                    broadcast(payload, src, frag.process_group_id, group.ranks, f"{frag.fragment_id}:{name}", self.global_rank)
-                    t.copy_(payload.view(t.shape))
-                else:
-                    raise ValueError(f"optimizer state shape mismatch for {spec.logical_param_id}.{name}: {tuple(t.shape)}")
-
-    # -- norm ownership
+    # ------------------------------------------------------------------ count once
     def owned_gradient_views(self):
+        """Views of the gradient elements whose norm contribution this rank is responsible for."""
+        have = {bf.fragment.fragment_id for bf in self._bound}
         for frag in self.plan.canonical_fragments:
-            if not frag.include_in_optimizer_norm or frag.norm_owner_rank != self.global_rank:
-                continue
-            spec = self._specs.get(frag.fragment_id)
-            if spec is None:
+            if frag.include_in_optimizer_norm and frag.norm_owner_rank == self.global_rank and frag.fragment_id not in have:
                 raise ValueError(f"norm owner rank {self.global_rank} is missing binding for fragment {frag.fragment_id}")
-            yield from self._views(self._gradient(spec.logical_param_id), spec)
+        for bf in self._bound:
+            if bf.fragment.include_in_optimizer_norm and bf.fragment.norm_owner_rank == self.global_rank:
+                yield from bf.views(self._gradient(bf.logical_id))
 
     def all_local_gradients(self):
         seen = set()
@@ -164,41 +186,41 @@ class CanonicalOptimizerSemantics:
                 seen.add(id(g))
                 yield g
 
+    def _zero_scalar(self):
+        return torch.zeros((), dtype=torch.float32, device=self.control_device)
+
     def owned_norm_sq(self, inv_scale=1.0):
         """Device scalar: sum of squares of the gradient elements this rank owns."""
-        total = None
+        total = self._zero_scalar()
         for v in self.owned_gradient_views():
-            s = (v.detach().float() * inv_scale).pow(2).sum()
-            total = s if total is None else total + s
-        if total is None:
-            total = torch.zeros((), dtype=torch.float32, device=self.control_device)
+            total = total + (v.detach().float() * inv_scale).pow(2).sum().to(total.device)
         return total
 
     def clip_grad_norm(self, max_norm, norm_type, all_reduce_sum, all_reduce_max):
-        max_norm, norm_type = float(max_norm), float(norm_type)
-        stat = torch.zeros((), dtype=torch.float32, device=self.control_device)
-        if norm_type == float("inf"):
+        """Global norm with every logical element counted once; scales all local gradients."""
+        norm_type = float(norm_type)
+        acc = self._zero_scalar()
+        if norm_type == math.inf:
             for v in self.owned_gradient_views():
                 if v.numel():
-                    stat.copy_(torch.maximum(stat, v.detach().abs().max().float().to(stat.device)))
-            all_reduce_max(stat, "inf_norm")
-            total = float(stat.item())
+                    acc = torch.maximum(acc, v.detach().abs().max().float().to(acc.device))
+            all_reduce_max(acc, "inf_norm")
+            norm = float(acc.item())
         elif norm_type == 2.0:
-            for v in self.owned_gradient_views():
-                stat.add_(v.detach().float().pow(2).sum().to(stat.device))
-            all_reduce_sum(stat, "l2_norm_sq")
-            total = math.sqrt(float(stat.item()))
+            acc = self.owned_norm_sq()
+            all_reduce_sum(acc, "l2_norm_sq")
+            norm = math.sqrt(float(acc.item()))
         else:
             raise ValueError(f"unsupported canonical norm type {norm_type}")
-        coef = max_norm / (total + 1.0e-6)
-        if coef < 1.0:
+        factor = float(max_norm) / (norm + 1.0e-6)
+        if factor < 1.0:
             for g in self.all_local_gradients():
-                g.mul_(coef)
-        return total
+                g.mul_(factor)
+        return norm
 
     def count_zeros(self, all_reduce_sum):
-        total = torch.zeros((), dtype=torch.float32, device=self.control_device)
+        zeros = self._zero_scalar()
         for v in self.owned_gradient_views():
-            total.add_((v.numel() - torch.count_nonzero(v)).to(total.device))
-        all_reduce_sum(total, "zero_count")
-        return float(total.item())
+            zeros = zeros + (v.numel() - torch.count_nonzero(v)).to(zeros.device)
+        all_reduce_sum(zeros, "zero_count")
+        return float(zeros.item())

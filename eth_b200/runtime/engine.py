@@ -29,7 +29,7 @@ from ..optim.grad_scaler import ConstantGradScaler, DynamicGradScaler
 from ..optim.lr import AnnealingLR
 from ..optim.optimizer import FlatMixedPrecisionAdam, coalesce_ranges
 from ..parallel.grad_sync.gpt_adapter import collect_gpt_gradient_metadata
-from ..parallel.grad_sync.loss import TrainingClock, local_sample_slots, synthetic_gpt_batch
+from ..parallel.grad_sync.loss import SampleSchedule, TrainingClock, synthetic_gpt_batch
 from ..parallel.grad_sync.manager import dump_gradient_sync_plan, initialize_gradient_sync
 from ..parallel.p2p import PipelineComm
 from ..parallel.state import ParallelState
@@ -119,6 +119,7 @@ class TrainEngine:
         raw_ops.enable_async_wgrad(self.device, on=getattr(args, "async_wgrad", True) and not evidence)
         self.loss_acc = torch.zeros(2, dtype=torch.float32, device=self.device)
         self._gs_pairs = []
+        self._sample_schedule = None
         self.last_stats: Dict[str, object] = {}
 
     # ------------------------------------------------------------------ set-up
@@ -267,8 +268,10 @@ class TrainEngine:
     # ------------------------------------------------------------------ data
     def _sample_ids(self, mb_index: int):
         a, ps = self.args, self.pstate
-        return local_sample_slots(ps.pipeline_id, mb_index, ps.dp_size, ps.dp_rank, a.mbs_seq,
-                                  a.pipeline_sample_offsets, self.clock.global_data_cursor)
+        if self._sample_schedule is None:
+            self._sample_schedule = SampleSchedule(a.mbs_seq, a.pipeline_sample_offsets)
+        return self._sample_schedule.slots(ps.pipeline_id, mb_index, ps.dp_size, ps.dp_rank,
+                                           self.clock.global_data_cursor)
 
     def get_batch(self, mb_index: int):
         ids = self._sample_ids(mb_index)
