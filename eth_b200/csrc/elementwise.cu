@@ -735,10 +735,19 @@ __global__ void ce_bwd_kernel(T* __restrict__ logits, const int64_t* __restrict_
 // =============================================================================================
 template <typename G>
 __global__ void grad_norm_kernel(const G* __restrict__ g, int64_t n, float inv_scale,
-                                 float* __restrict__ acc) {
+                                 float* __restrict__ acc, int head) {
   __shared__ float red[32];
   float s = 0.f;
   bool bad = false;
+  // `head` leading elements (fewer than 8) bring the pointer to a 16-byte boundary: a range of a
+  // flat buffer may start anywhere, the vector loop below needs aligned addresses
+  if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < head) {
+    const float u = HalfTraits<G>::to_f(g[threadIdx.x]) * inv_scale;
+    bad |= !isfinite(u);
+    s += u * u;
+  }
+  g += head;
+  n -= head;
   const int64_t nvec = n >> 3;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -1111,9 +1120,14 @@ cudaError_t ce_bwd(void* logits, const int64_t* targets, const float* gmax, cons
 cudaError_t grad_norm_sq(const void* grad, int64_t n, int grad_dtype, float inv_scale, float* acc,
                          cudaStream_t st) {
   if (n <= 0) return cudaSuccess;
+  const int esize = grad_dtype == kF32 ? 4 : 2;
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(grad);
+  if (addr % esize != 0) return cudaErrorMisalignedAddress;
+  int64_t head = static_cast<int64_t>(((16 - (addr & 15)) & 15) / esize);
+  if (head > n) head = n;
   ETHB_DISPATCH(grad_dtype, G,
                 (grad_norm_kernel<G><<<grid_for(n / 8 + 1, 256, 4), 256, 0, st>>>((const G*)grad, n,
-                                                                                  inv_scale, acc)));
+                                                                                  inv_scale, acc, static_cast<int>(head))));
   count_launch();
   return cudaGetLastError();
 }
@@ -1200,6 +1214,8 @@ extern "C" int ethb_colsum_noalloc(const void* x, void* out, int64_t rows, int32
   using namespace ethb;
   if (x == nullptr || out == nullptr || rows <= 0 || cols <= 0 || cols % 8 != 0) return ETHB_NOALLOC_BAD_ARGUMENT;
   if (dtype < 0 || dtype > 2 || out_dtype < 0 || out_dtype > 2) return ETHB_NOALLOC_BAD_ARGUMENT;
+  // the kernel reads x with 16-byte vector loads (rows stay aligned because cols % 8 == 0)
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return ETHB_NOALLOC_BAD_ARGUMENT;
   if (cols > ETHB_COLSUM_NOALLOC_MAX_COLS) return ETHB_NOALLOC_TOO_LARGE;
   const int parts = colsum_parts(rows);
   if (parts > ETHB_COLSUM_NOALLOC_MAX_PARTS) return ETHB_NOALLOC_TOO_LARGE;
@@ -1213,7 +1229,8 @@ extern "C" int ethb_colsum_noalloc(const void* x, void* out, int64_t rows, int32
 extern "C" const char* ethb_noalloc_strerror(int code) {
   if (code == 0) return "success";
   if (code == ETHB_NOALLOC_BAD_ARGUMENT)
-    return "bad argument: null pointer, non-positive size, cols not a multiple of 8, or unknown dtype code";
+    return "bad argument: null pointer, x not 16-byte aligned, non-positive size, cols not a multiple of 8, or "
+           "unknown dtype code";
   if (code == ETHB_NOALLOC_TOO_LARGE)
     return "problem exceeds the built-in scratch array (cols <= 16384 and at most 64 row partitions)";
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -26,6 +26,8 @@
  *     order them on one stream or with events.
  *   - No cudaMalloc / cudaFree / allocating library routine is called, on any path.
  *
+ *   - `x` must start on a 16-byte boundary (the kernel uses 16-byte loads); `out` has no alignment
+ *     requirement beyond its element type. A misaligned `x` is rejected with ETHB_NOALLOC_BAD_ARGUMENT.
  * dtype codes: 0 = float32, 1 = float16, 2 = bfloat16 (x uses `dtype`, out uses `out_dtype`).
  * Returns 0 on success, a negative ETHB_NOALLOC_* code for rejected arguments, or a positive
  * cudaError_t value if the runtime reported an error. `ethb_noalloc_strerror` describes any of

@@ -133,9 +133,12 @@ class TrainEngine:
             try:
                 from ..parallel.fused_tp import FusedTPBackend
                 backend = FusedTPBackend.create(ps, self.coll, self.device, self.args)
-            except Exception:
+            except Exception as err:
                 if mode == "fused":
                     raise
+                # said once per rank: a broken peer-memory set-up must not pass as a slower number
+                print(f"[rank {self.args.rank}] fused tensor-parallel kernels unavailable, using GEMM + NCCL "
+                      f"all-reduce instead: {type(err).__name__}: {err}", flush=True)
                 backend = None
         return TPComm(ps.tp_size, ps.tp_rank, ps.tp_group, backend)
 

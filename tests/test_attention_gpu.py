@@ -13,8 +13,12 @@ pytestmark = pytest.mark.gpu
 
 
 def _rel_err(a, b):
+    """max(Frobenius-norm relative error, largest element error relative to the largest reference
+    magnitude): the second term catches a single bad row or element that the norm would hide."""
     a, b = a.float(), b.float()
-    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+    fro = ((a - b).norm() / (b.norm() + 1e-12)).item()
+    worst = ((a - b).abs().max() / (b.abs().max() + 1e-12)).item()
+    return max(fro, worst)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -73,9 +77,9 @@ def test_unfused_attention_matches_flash():
     q, k, v = (torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
     out_f = ops.flash_attention(q, k, v)
     out_u = Fn.unfused_attention(q, k, v)
-    assert ((out_f.float() - out_u.float()).norm() / out_f.float().norm()).item() < 2e-2
+    assert _rel_err(out_u, out_f) < 2e-2
     do = torch.randn_like(out_f)
     gf = torch.autograd.grad(out_f, (q, k, v), do)
     gu = torch.autograd.grad(out_u, (q, k, v), do)
     for a, b in zip(gf, gu):
-        assert ((a.float() - b.float()).norm() / a.float().norm()).item() < 3e-2
+        assert _rel_err(b, a) < 3e-2

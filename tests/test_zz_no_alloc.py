@@ -45,7 +45,8 @@ def test_no_alloc_colsum_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
         assert _rel_err(out, ref) < 1e-5
-        assert _rel_err(out, x.float().sum(0)) < 1e-2
+        assert _rel_err(out, x.float().sum(0)) < 1e-5
+        assert (out - x.float().sum(0)).abs().max().item() <= 1e-5 * x.float().abs().sum(0).max().item()
         # accumulate on top of an existing value
         acc = torch.full((cols,), 3.0, device="cuda")
         rc = lib.ethb_colsum_noalloc(x.data_ptr(), acc.data_ptr(), rows, cols, code[dt], 0, 1, stream)
@@ -60,4 +61,7 @@ def test_no_alloc_colsum_rejects_oversized_and_bad_arguments():
     rc = lib.ethb_colsum_noalloc(x.data_ptr(), out.data_ptr(), 8, 32768, 2, 0, 0, None)
     assert rc == -2 and b"exceeds" in lib.ethb_noalloc_strerror(rc)
     rc = lib.ethb_colsum_noalloc(x.data_ptr(), out.data_ptr(), 8, 12, 2, 0, 0, None)
+    assert rc == -1
+    # an input that does not start on a 16-byte boundary is refused before anything is launched
+    rc = lib.ethb_colsum_noalloc(x.data_ptr() + 2, out.data_ptr(), 8, 64, 2, 0, 0, None)
     assert rc == -1
