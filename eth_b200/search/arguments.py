@@ -1,7 +1,7 @@
 """Flags of `python -m eth_b200.search.search` (reference surface: eth/searching/arguments.py:21-138;
 model table :10-18; node_info expansion :224-249). Every flag that scripts/search_gpt.sh passes is
-accepted; flags that steer the reference's local-search heuristics and have no counterpart in the
-exact boundary solver are accepted and recorded."""
+accepted, and each of them acts: the heuristic flags steer the local search that refines the exact
+boundary solution (refine.py)."""
 from __future__ import annotations
 
 import argparse
@@ -33,17 +33,27 @@ def build_parser():
     g.add_argument("--homo-stage", action="store_true", help="Stages may not mix GPU types.")
     g = p.add_argument_group("budget and heuristics")
     g.add_argument("--time-budget-total", type=float, default=10, help="Search budget in seconds.")
-    g.add_argument("--max-num-hops", type=int, default=7, help="Depth of the reference's multi-hop search (recorded).")
-    g.add_argument("--initial-point", default="balance_v1", help="Initial configuration policy (recorded).")
+    g.add_argument("--max-num-hops", type=int, default=7,
+                   help="Depth of the multi-hop local search that refines the boundary-DP optimum (0 = off).")
+    g.add_argument("--initial-point", default="dp",
+                   help="Extra starting point of the local search: dp (the DP optimum only), balance / balance_v1 "
+                        "(equal layers per stage, TP = stage GPUs), or the path of a legacy single-pipeline JSON.")
+    g.add_argument("--refine-share", type=float, default=0.25,
+                   help="Fraction of the time budget that one device group may spend in the local search.")
     g.add_argument("--support-comm-predict", action="store_true", help="Use measured collective tables.")
     g.add_argument("--comm-revised", action="store_true", help="Charge max(previous output, this input) per boundary.")
-    g.add_argument("--add-action-tp-dp-exchange", action="store_true", help="Allow TP<->DP exchange (always explored).")
-    g.add_argument("--no-add-action-tp-dp", action="store_true", help="Disable GPU moves between stages (recorded).")
+    g.add_argument("--add-action-tp-dp-exchange", action="store_true",
+                   help="Local search may exchange TP against DP inside a stage (the DP enumerates all TP x DP anyway).")
+    g.add_argument("--no-add-action-tp-dp", action="store_true", help="Local search may not move GPUs between stages.")
     g.add_argument("--use-cache", action="store_true", help="Cache the best result per device group.")
     g.add_argument("--optimal-prune", action="store_true", help="Prune pipeline splits by an ideal-throughput bound.")
     g.add_argument("--sort-pipeline", action="store_true", help="Try balanced pipeline splits first.")
     g.add_argument("--dp-find-pipeline", action="store_true", help="Choose splits of >= 4 pipelines by dynamic programming.")
-    g.add_argument("--elastic-time", action="store_true", help="Spend unused budget of easy groups on hard ones.")
+    g.add_argument("--elastic-time", action="store_true",
+                   help="Local-search time a device group did not use is added to the next group's allowance.")
+    g.add_argument("--no-permute-nodes", dest="permute_nodes", action="store_false",
+                   help="Keep the given node order (by default distinct orderings of node kinds are tried).")
+    g.add_argument("--max-node-orders", type=int, default=24, help="Cap on node orderings tried.")
     g.add_argument("--no-grad-sync-term", action="store_true", help="Ignore the gradient all-reduce in the cost model.")
     g.add_argument("--add-tp-comm-term", action="store_true",
                    help="Add tensor-parallel reductions from the collective tables (profiles taken without them).")

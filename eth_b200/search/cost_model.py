@@ -35,6 +35,10 @@ class StageChoice:
     tp: int
     dp: int
     gpu_type: str = "default"
+    gpu_types: Tuple[str, ...] = ()      # all distinct types of a mixed stage; () = just `gpu_type`
+
+    def types(self) -> Tuple[str, ...]:
+        return self.gpu_types or (self.gpu_type,)
 
 
 @dataclass
@@ -45,6 +49,22 @@ class StageEval:
     memory_mb: float
     recompute_layers: int
     weights_mb: float
+
+
+@dataclass
+class OpStageEval:
+    time_us: float
+    fwd_us: float
+    bwd_us: float
+    memory_mb: float
+    recompute: Tuple[int, ...]
+    weights_mb: float
+    memory_limit_mb: float
+    boundary_mb: float
+
+    @property
+    def compute_us(self) -> float:
+        return self.fwd_us + self.bwd_us
 
 
 @dataclass
@@ -71,17 +91,44 @@ class CostModel:
         self._layer_cache: Dict[tuple, dict] = {}
 
     # ------------------------------------------------------------------ per-group aggregates
-    def _groups(self, gpu_type: str, mbs: int, tp: int, algo: int = 0) -> Optional[dict]:
-        """Sums over the three op groups of the one-layer profile: pre (embedding), layer, post."""
+    def op_rows(self, gpu_types, mbs: int, tp: int, algo: int = 0):
+        """The one-layer op table for a stage whose GPUs are of `gpu_types`: per op the slowest
+        type's times (the stage advances at the pace of its slowest device, reference
+        cost_model.py:192-217); sizes do not depend on the type. None if some type lacks the profile."""
+        types = (gpu_types,) if isinstance(gpu_types, str) else tuple(gpu_types)
+        key = ("rows", types, mbs, tp, algo)
+        if key in self._layer_cache:
+            return self._layer_cache[key]
+        tables = []
+        for t in types:
+            db = self.profiles[t]
+            if not db.has(mbs, tp, algo):
+                self._layer_cache[key] = None
+                return None
+            tables.append(db.records(mbs, tp, algo))
+        rows = tables[0]
+        if len(tables) > 1:
+            from dataclasses import replace as _replace
+            rows = [_replace(r, fwd_us=max(t[i].fwd_us for t in tables), bwd_us=max(t[i].bwd_us for t in tables))
+                    for i, r in enumerate(rows)]
+        self._layer_cache[key] = rows
+        return rows
+
+    def memory_limit_mb(self, gpu_types) -> float:
+        types = (gpu_types,) if isinstance(gpu_types, str) else tuple(gpu_types)
+        return min(self.device_memory_mb[t] for t in types) * (1.0 - self.opt.memory_reserve_fraction)
+
+    def _groups(self, gpu_type, mbs: int, tp: int, algo: int = 0) -> Optional[dict]:
+        """Sums over the three op groups of the one-layer profile: pre (embedding), layer, post.
+        `gpu_type` may be one type or a tuple of types (mixed stage)."""
         key = (gpu_type, mbs, tp, algo)
         hit = self._layer_cache.get(key)
         if hit is not None or key in self._layer_cache:
             return hit
-        db = self.profiles[gpu_type]
-        if not db.has(mbs, tp, algo):
+        rows = self.op_rows(gpu_type, mbs, tp, algo)
+        if rows is None:
             self._layer_cache[key] = None
             return None
-        rows = db.records(mbs, tp, algo)
         if len(rows) != PRE_OPS + OPS_PER_LAYER + POST_OPS:
             raise ValueError(f"profile for mbs{mbs} tp{tp} has {len(rows)} ops, expected "
                              f"{PRE_OPS + OPS_PER_LAYER + POST_OPS}")
@@ -106,7 +153,7 @@ class CostModel:
         if mbs % choice.dp:
             return None
         local = mbs // choice.dp
-        g = self._groups(choice.gpu_type, local, choice.tp)
+        g = self._groups(choice.types() if len(choice.types()) > 1 else choice.gpu_type, local, choice.tp)
         if g is None:
             return None
         fwd = num_layers * g["layer"]["fwd"] + (g["pre"]["fwd"] if has_pre else 0) + (g["post"]["fwd"] if has_post else 0)
@@ -119,7 +166,7 @@ class CostModel:
         act_layer = g["layer"]["act"]
         act_fixed = (g["pre"]["act"] if has_pre else 0) + (g["post"]["act"] if has_post else 0)
         peak = max(g["layer"]["peak"], g["post"]["peak"] if has_post else 0, g["pre"]["peak"] if has_pre else 0)
-        limit = self.device_memory_mb[choice.gpu_type] * (1.0 - o.memory_reserve_fraction)
+        limit = self.memory_limit_mb(choice.types())
         layer_in = g["layer"]["in"]
 
         def mem(recomputed: int) -> float:
@@ -157,6 +204,82 @@ class CostModel:
             # forward activation + backward gradient
             time += 2 * db.p2p_ms(send_mb, inter_node) * 1e3
         return StageEval(time, fwd, bwd, mem(recompute), recompute, weights)
+
+    # ------------------------------------------------------------------ op-granular stage
+    def stage_eval_ops(self, stage, mbs: int, stages_behind: int, next_stage=None, inter_node: bool = False,
+                       plan_recompute: bool = True) -> Optional["OpStageEval"]:
+        """Cost of a `StagePlan` (any op range). Recomputation is planned per op when the stage does
+        not fit: ops are marked in order of decreasing stored activation until the stage fits
+        (embedding, the first LayerNorm of a layer and the tail ops are never recomputed), then
+        un-marked again, cheapest recompute per MB first, while it still fits (reference:
+        check_recompute, cost_model.py:1037-1109, 1224-1251). None = infeasible."""
+        from .model_ops import NEVER_RECOMPUTE_OPS
+        from .state import OPS_PER_LAYER as OPL, op_position
+        if mbs % stage.dp:
+            return None
+        rows = self.op_rows(stage.gpu_types, mbs // stage.dp, stage.tp)
+        if rows is None:
+            return None
+        row_of = {"pre": lambda k: rows[0], "layer": lambda k: rows[1 + k], "post": lambda k: rows[1 + OPL + k]}
+        ops = []
+        for i in range(stage.op_begin, stage.op_end):
+            kind, k = op_position(i, self.num_layers)
+            ops.append(row_of[kind](k))
+        o = self.opt
+        weights = sum(r.weights_mb for r in ops)
+        state_mb = weights / o.bytes_per_param * (o.bytes_per_param + o.grad_bytes_per_param + o.optimizer_bytes_per_param)
+        peak = max(max(r.fwd_reserved_mb, r.bwd_reserved_mb) for r in ops)
+        inflight = stages_behind + 1
+        limit = self.memory_limit_mb(stage.gpu_types)
+        mask = list(stage.mask())
+
+        def memory(m):
+            kept = sum(r.activations_mb for r, bit in zip(ops, m) if not bit)
+            # a recomputed run keeps its first input and needs room to rebuild its largest member
+            kept += sum(ops[j].input_mb for j, bit in enumerate(m) if bit and (j == 0 or not m[j - 1]))
+            transient = max((r.activations_mb for r, bit in zip(ops, m) if bit), default=0.0)
+            return state_mb + kept * inflight + transient + peak
+
+        if plan_recompute and memory(mask) > limit:
+            free = [j for j, r in enumerate(ops) if r.name not in NEVER_RECOMPUTE_OPS and not mask[j]]
+            for j in sorted(free, key=lambda j: -ops[j].activations_mb):
+                mask[j] = 1
+                if memory(mask) <= limit:
+                    break
+            if memory(mask) > limit:
+                return None
+            marked = [j for j in free if mask[j]]
+            for j in sorted(marked, key=lambda j: -(ops[j].fwd_us / max(ops[j].activations_mb, 1e-9))):
+                mask[j] = 0
+                if memory(mask) > limit:
+                    mask[j] = 1
+        elif memory(mask) > limit:
+            return None
+        fwd, bwd = sum(r.fwd_us for r in ops), sum(r.bwd_us for r in ops)
+        time = fwd + bwd + sum(r.fwd_us for r, bit in zip(ops, mask) if bit)
+        db = self.profiles[stage.gpu_types[0]]
+        if not o.tp_comm_in_op_time and stage.tp > 1:
+            reductions = sum(1 for r in ops if r.name in ("enc-attention-dense", "enc-MLP-GEMM-2", "enc-attention-qkv",
+                                                          "enc-MLP-GEMM-1"))
+            time += reductions * db.collective_ms("all_reduce", stage.tp, rows[1].input_mb) * 1e3
+        send_mb = 0.0
+        if next_stage is not None:
+            send_mb = self.boundary_mb(stage.op_end, rows)
+            if o.comm_revised and mbs % next_stage.dp == 0:
+                nxt = self.op_rows(next_stage.gpu_types, mbs // next_stage.dp, next_stage.tp)
+                if nxt is not None:
+                    send_mb = max(send_mb, self.boundary_mb(stage.op_end, nxt))
+            time += 2 * db.p2p_ms(send_mb, inter_node) * 1e3      # forward activation + backward gradient
+        return OpStageEval(time, fwd, bwd, memory(mask), tuple(mask), weights, limit, send_mb)
+
+    def boundary_mb(self, cut: int, rows) -> float:
+        """Size of what crosses a stage boundary placed before global op `cut`: the output of the op
+        before it, plus the residual that is still alive when the cut falls inside a sub-block."""
+        from .state import OPS_PER_LAYER as OPL, op_position
+        kind, k = op_position(cut - 1, self.num_layers)
+        last = rows[0] if kind == "pre" else rows[1 + k] if kind == "layer" else rows[1 + OPL + k]
+        residual_alive = kind == "layer" and k not in (4, 9)      # not right after a dropout-add op
+        return last.output_mb + (rows[1].input_mb if residual_alive else 0.0)
 
     # ------------------------------------------------------------------ pipeline / plan
     @staticmethod

@@ -11,7 +11,7 @@ TP x DP factorisation and layer range, the micro-batch size, and op recomputatio
 batch is then balanced over the pipelines.
 
 Method. The reference walks this space with a multi-hop local search over migration actions.
-Here the inner problem is solved exactly: for fixed stage shapes, TP/DP and micro-batch size the
+Here the layer-granular inner problem is solved exactly first: for fixed stage shapes, TP/DP and micro-batch size the
 optimal layer boundaries come from a dynamic programme over layer prefixes (stage cost is additive
 in layers), which is then evaluated with the 1F1B formula. The outer enumeration (stage-size
 compositions, TP x DP choices, micro-batch sizes) is pruned by an ideal-throughput upper bound
@@ -20,6 +20,14 @@ splits are ordered by a TFLOPS-imbalance score (`--sort-pipeline`), pruned by th
 (`--optimal-prune`), and for >= 4 pipelines chosen by a dynamic programme over contiguous node
 splits (`--dp-find-pipeline`). Micro-batches are assigned greedily to the pipeline that would
 finish first (reference: workload_balance_pipeline_v1, search.py:569-633).
+
+On top of that: `--op-grain op|block` (or an explicit `--initial-point`) starts the multi-hop local
+search of `refine.py` from the DP optimum, which may move stage cuts inside a layer, exchange TP
+against DP, move GPUs between stages and change the micro-batch size (`actions.py`, `policy.py`);
+device placement is searched by permuting the node order before the contiguous splits
+(`--permute-nodes`, `device_groups.node_orders`); unsolved device groups are bounded by solved
+groups that dominate them (`device_groups.ThroughputBounds`); the best `--num-of-saved-configs`
+plans are ranked and written with trend CSVs (`reporting.Ranking`).
 """
 from __future__ import annotations
 
@@ -34,9 +42,13 @@ from typing import Dict, List, Optional, Sequence, Tuple
 from ..contract.config import LAYER_OPS, make_config, normalize_flexpipe_config
 from .arguments import parse_args
 from .cost_model import CostModel, CostOptions, StageChoice
+from .device_groups import (ThroughputBounds, compositions_pow2, contiguous_splits, imbalance_loss,  # noqa: F401
+                            node_orders)
 from .profile_db import ProfileDB
-from .reporting import SearchLog
-from .serialization import dump_hybrid_config, dump_pipeline_legacy, pipeline_to_pipe_dict
+from .refine import Refiner
+from .reporting import Ranking, SearchLog, Timers
+from .serialization import dump_hybrid_config, dump_pipeline_legacy, load_initial_plan, pipeline_to_pipe_dict
+from .state import PipelinePlan, StagePlan, plan_from_layers
 
 OPS_PER_LAYER = len(LAYER_OPS)
 
@@ -52,6 +64,9 @@ class PipelineResult:
     stage_weights_mb: List[float]
     stage_memory_mb: List[float]
     mbs: int
+    op_counts: Optional[List[int]] = None            # ops per stage when a cut falls inside a layer
+    recompute_masks: Optional[List[Tuple[int, ...]]] = None   # per-op recompute flags from the op-granular planner
+    found_by: str = "boundary-dp"
 
     @property
     def bottleneck_us(self) -> float:
@@ -65,26 +80,6 @@ class PipelineResult:
         return sum(s.gpus for s in self.stages)
 
 
-def compositions_pow2(total: int, parts: int, max_part: int) -> List[Tuple[int, ...]]:
-    """Ordered ways to write `total` as a sum of `parts` powers of two (each <= max_part)."""
-    sizes = [s for s in (1, 2, 4, 8, 16, 32, 64) if s <= max_part]
-    out: List[Tuple[int, ...]] = []
-
-    def rec(left: int, k: int, acc: Tuple[int, ...]):
-        if k == 0:
-            if left == 0:
-                out.append(acc)
-            return
-        if left < k or left > k * max(sizes):
-            return
-        for s in sizes:
-            if s <= left:
-                rec(left - s, k - 1, acc + (s,))
-
-    rec(total, parts, ())
-    return out
-
-
 def tp_dp_options(gpus: int, max_tp: int) -> List[Tuple[int, int]]:
     return [(tp, gpus // tp) for tp in (1, 2, 4, 8) if tp <= max_tp and gpus % tp == 0 and tp <= gpus]
 
@@ -93,11 +88,16 @@ class PipelineSearcher:
     """Best single-pipeline configuration for a list of GPUs (one type per GPU)."""
 
     def __init__(self, cost: CostModel, num_layers: int, max_tp: int, mbs_list: Sequence[int], heads: int,
-                 hidden: int, deadline: float, homo_stage: bool = True):
+                 hidden: int, deadline: float, homo_stage: bool = True, refiner: Optional[Refiner] = None,
+                 refine_seconds: float = 0.0, elastic: bool = False, initial_point: str = "dp"):
         self.cost, self.L, self.max_tp, self.mbs_list = cost, num_layers, max_tp, list(mbs_list)
         self.heads, self.hidden, self.deadline, self.homo_stage = heads, hidden, deadline, homo_stage
         self.cache: Dict[tuple, Dict[int, PipelineResult]] = {}
         self.evaluated = 0
+        # local search on top of the exact layer-boundary solution (op / block grain cuts, shape moves)
+        self.refiner, self.refine_seconds, self.elastic, self.initial_point = refiner, refine_seconds, elastic, initial_point
+        self.budget_pool = 0.0      # refinement time that easy groups did not use (`--elastic-time`)
+        self.refined = 0
 
     def best(self, gpu_types: Tuple[str, ...], stage_range: Tuple[int, int], gpus_per_node: int) -> Dict[int, PipelineResult]:
         """{mbs: best result} over all stage counts in `stage_range` (cached per device group)."""
@@ -120,7 +120,7 @@ class PipelineSearcher:
                     if len(ts) != 1 and self.homo_stage:
                         aligned = False
                         break
-                    types.append(sorted(ts)[0])
+                    types.append(tuple(sorted(ts)))     # a mixed stage is costed per op at its slowest type
                     # a stage may not straddle a node boundary unless it covers whole nodes
                     if b - a > gpus_per_node and (b - a) % gpus_per_node:
                         aligned = False
@@ -130,8 +130,75 @@ class PipelineSearcher:
                     res = self._best_for_shape(comp, types, mbs)
                     if res is not None and (mbs not in results or self._score(res) < self._score(results[mbs])):
                         results[mbs] = res
+        if self.refiner is not None and results:
+            for res in self._refined(results):
+                if res.mbs not in results or self._score(res) < self._score(results[res.mbs]):
+                    results[res.mbs] = res
         self.cache[key] = results
         return results
+
+    # ------------------------------------------------------------------ local search on top of the DP
+    def _to_plan(self, r: PipelineResult) -> PipelinePlan:
+        shapes = [(c.gpus, c.tp, c.dp, c.types()) for c in r.stages]
+        if r.op_counts:
+            stages, cursor = [], 0
+            for n, (g, tp, dp, types) in zip(r.op_counts, shapes):
+                stages.append(StagePlan(cursor, cursor + n, g, tp, dp, tuple(types)))
+                cursor += n
+            return PipelinePlan(tuple(stages), r.mbs)
+        return plan_from_layers(r.layers, shapes, r.mbs, self.L)
+
+    def _from_scored(self, scored, how: str) -> PipelineResult:
+        plan = scored.plan
+        choices = [StageChoice(st.gpus, st.tp, st.dp, st.gpu_types[0], gpu_types=st.gpu_types) for st in plan.stages]
+        counts = [st.num_ops for st in plan.stages]
+        layers = [max(0, round((n - (1 if i == 0 else 0) - (2 if i == len(counts) - 1 else 0)) / OPS_PER_LAYER))
+                  for i, n in enumerate(counts)]
+        masks = [ev.recompute for ev in scored.evals]
+        return PipelineResult(tuple(c.gpu_type for c in choices), choices, layers, [0] * len(counts),
+                              [e.time_us for e in scored.evals], [e.weights_mb for e in scored.evals],
+                              [e.memory_mb for e in scored.evals], plan.mbs, op_counts=counts, recompute_masks=masks,
+                              found_by=how)
+
+    def _start_plans(self, results: Dict[int, PipelineResult]) -> List[PipelinePlan]:
+        starts = [self._to_plan(r) for r in results.values()]
+        sample = next(iter(results.values()))
+        if self.initial_point in ("balance", "balance_v1"):
+            # equal layers per stage, TP = the stage's GPUs, DP = 1 (reference: config.py:425-489)
+            n = len(sample.stages)
+            base, extra = divmod(self.L, n)
+            layers = [base + (1 if i >= n - extra else 0) for i in range(n)]
+            for mbs in self.mbs_list:
+                shapes = []
+                for c in sample.stages:
+                    tp = min(c.gpus, self.max_tp)
+                    shapes.append((c.gpus, tp, c.gpus // tp, c.types()))
+                if all(mbs % dp == 0 for _, _, dp, _ in shapes) and all(x > 0 for x in layers):
+                    starts.append(plan_from_layers(layers, shapes, mbs, self.L))
+        elif self.initial_point not in ("dp", ""):
+            plan = load_initial_plan(self.initial_point, self.L, sample.gpu_types)
+            if plan is not None and plan.num_gpus == sample.num_gpus:
+                starts.append(plan)
+        return starts
+
+    def _refined(self, results: Dict[int, PipelineResult]) -> List[PipelineResult]:
+        out = []
+        starts = self._start_plans(results)
+        for plan in starts:
+            allowance = self.refine_seconds / max(1, len(starts)) + (self.budget_pool if self.elastic else 0.0)
+            t0 = time.time()
+            until = min(self.deadline, t0 + allowance)
+            if until <= t0:
+                break
+            before = len(self.refiner.trace)
+            scored = self.refiner.refine(plan, until)
+            used = time.time() - t0
+            if self.elastic:
+                self.budget_pool = max(0.0, allowance - used)
+            self.refined += 1
+            if scored.feasible:
+                out.append(self._from_scored(scored, "multi-hop" if len(self.refiner.trace) > before else "start"))
+        return out
 
     @staticmethod
     def _score(r: PipelineResult) -> float:
@@ -154,7 +221,7 @@ class PipelineSearcher:
         for idx, combo in enumerate(combos):
             if idx >= limit or (time.time() > self.deadline and best is not None):
                 break
-            choices = [StageChoice(g, tp, dp, t) for g, (tp, dp), t in zip(comp, combo, types)]
+            choices = [StageChoice(g, tp, dp, t[0], gpu_types=t) for g, (tp, dp), t in zip(comp, combo, types)]
             res = self._solve_boundaries(choices, mbs)
             self.evaluated += 1
             if res is not None and (best is None or self._score(res) < self._score(best)):
@@ -219,6 +286,8 @@ class HybridPlan:
     pipelines: List[PipelineResult]
     batch_sizes: List[int]
     iteration_us: float
+    node_order: Tuple[int, ...] = ()                  # device placement: order of the nodes ...
+    groups: Tuple[Tuple[int, int], ...] = ()          # ... and which slice of that order each pipeline takes
 
     @property
     def throughput(self) -> float:
@@ -245,115 +314,126 @@ def balance_batches(pipes: Sequence[PipelineResult], global_batch: int) -> Optio
     return [c * p.mbs for c, p in zip(counts, pipes)]
 
 
-def contiguous_splits(n: int, k: int):
-    for cuts in itertools.combinations(range(1, n), k - 1):
-        yield [(a, b) for a, b in zip((0,) + cuts, cuts + (n,))]
-
-
-def imbalance_loss(groups, tflops_of_node) -> float:
-    """Variance of the per-pipeline TFLOPS share (reference ordering key, device_groups.py:292-339)."""
-    sums = [sum(tflops_of_node[i] for i in range(a, b)) for a, b in groups]
-    mean = sum(sums) / len(sums)
-    return sum((s - mean) ** 2 for s in sums) / len(sums)
+def plan_signature(plan: "HybridPlan") -> tuple:
+    return tuple((p.mbs, tuple((c.gpus, c.tp, c.dp) for c in p.stages), tuple(p.op_counts or p.layers), b)
+                 for p, b in zip(plan.pipelines, plan.batch_sizes)) + (plan.node_order,)
 
 
 def run_search(args) -> Tuple[Optional[HybridPlan], dict]:
     t0 = time.time()
     deadline = t0 + float(args.time_budget_total)
     log = SearchLog(args.log_path, quiet=args.reduce_output)
-    nodes = args.nodes                       # list of {"GPU": type, "GPU_NUM": n}
-    gpu_types = sorted({n["GPU"] for n in nodes})
+    timers = Timers()
+    gpu_types = sorted({n["GPU"] for n in args.nodes})
     profiles = {}
-    for t in gpu_types:
-        base = os.path.join(args.profiled_time_path, t)
-        pdir = os.path.join(base, f"{args.model_name}_{args.model_size}")
-        if not os.path.isdir(pdir):
-            pdir = args.profiled_time_path
-            base = args.profiled_time_path
-        profiles[t] = ProfileDB.load(pdir, t, args.model_size, args.micro_batch_size, args.max_tp, p2p_dir=base,
-                                     inter_node_file=os.path.join(args.profiled_time_path, "p2p_inter_node.csv"))
+    with timers.phase("load-profiles"):
+        for t in gpu_types:
+            base = os.path.join(args.profiled_time_path, t)
+            pdir = os.path.join(base, f"{args.model_name}_{args.model_size}")
+            if not os.path.isdir(pdir):
+                pdir = args.profiled_time_path
+                base = args.profiled_time_path
+            profiles[t] = ProfileDB.load(pdir, t, args.model_size, args.micro_batch_size, args.max_tp, p2p_dir=base,
+                                         inter_node_file=os.path.join(args.profiled_time_path, "p2p_inter_node.csv"))
     memory = {t: float(args.device_info[t]["memory"]) for t in gpu_types}
     tflops = {t: float(args.device_info[t].get("TFLOPS", 1.0)) for t in gpu_types}
     cost = CostModel(profiles, args.num_layers, memory,
                      CostOptions(include_grad_sync=not args.no_grad_sync_term, comm_revised=args.comm_revised,
                                  tp_comm_in_op_time=not args.add_tp_comm_term))
+    # Local search on top of the boundary DP: needed for cuts inside a layer (`--op-grain op|block`);
+    # at layer grain it still explores shape moves from the requested initial point.
+    refiner = None
+    if args.max_num_hops > 0 and (args.op_grain != "layer" or args.initial_point not in ("dp", "")):
+        refiner = Refiner(cost, args.num_layers, args.op_grain, args.micro_batch_size, args.max_tp,
+                          args.num_attention_heads, args.hidden_size, max_hops=args.max_num_hops,
+                          allow_gpu_moves=not args.no_add_action_tp_dp, allow_exchange=args.add_action_tp_dp_exchange)
     searcher = PipelineSearcher(cost, args.num_layers, args.max_tp, args.micro_batch_size, args.num_attention_heads,
-                                args.hidden_size, deadline, homo_stage=args.homo_stage)
-    node_tflops = [tflops[n["GPU"]] * n["GPU_NUM"] for n in nodes]
-    gpn = max(n["GPU_NUM"] for n in nodes)
+                                args.hidden_size, deadline, homo_stage=args.homo_stage, refiner=refiner,
+                                refine_seconds=float(args.time_budget_total) * args.refine_share,
+                                elastic=args.elastic_time, initial_point=args.initial_point)
+    bounds = ThroughputBounds(tflops, memory)
+    ranking = Ranking(args.num_of_saved_configs, plan_signature)
     stage_range = (args.start_num_stages, args.end_num_stages)
+    stats = {"splits_evaluated": 0, "splits_pruned": 0, "node_orders": 0}
 
-    def group_types(a, b):
-        return tuple(t for n in nodes[a:b] for t in [n["GPU"]] * n["GPU_NUM"])
-
-    def evaluate(groups) -> Optional[HybridPlan]:
-        per_group = []
-        for a, b in groups:
-            res = searcher.best(group_types(a, b), stage_range, gpn)
-            if not res:
-                return None
-            per_group.append(res)
-        best_plan = None
-        # micro-batch size per pipeline: all combinations (<= 4^k, k small); prune by steady-state rate
-        for combo in itertools.product(*[sorted(r) for r in per_group]):
-            pipes = [per_group[i][m] for i, m in enumerate(combo)]
-            sizes = balance_batches(pipes, args.global_batch_size)
-            if sizes is None:
-                continue
-            it = max(p.time_us(s // p.mbs) for p, s in zip(pipes, sizes))
-            replicas = sum(max(st.dp for st in p.stages) for p in pipes)
-            sync = max(cost.grad_sync_us(max(p.stage_weights_mb), replicas, p.stages[0].gpu_type) for p in pipes)
-            plan = HybridPlan(pipes, sizes, it + sync)
-            if best_plan is None or plan.iteration_us < best_plan.iteration_us:
-                best_plan = plan
-            if len(per_group) > 3 and time.time() > deadline:
-                break
-        return best_plan
-
-    n_nodes = len(nodes)
-    best: Optional[HybridPlan] = None
-    stats = {"splits_evaluated": 0, "splits_pruned": 0}
-    max_pipes = min(args.max_num_pipeline, n_nodes if n_nodes > 1 else max(1, sum(n["GPU_NUM"] for n in nodes) // 2))
+    base_nodes = list(args.nodes)                # list of {"GPU": type, "GPU_NUM": n}
+    gpn = max(n["GPU_NUM"] for n in base_nodes)
     # a single node may still be split into several pipelines of whole GPUs
-    if n_nodes == 1 and nodes[0]["GPU_NUM"] > 1 and args.max_num_pipeline > 1:
-        g = nodes[0]["GPU_NUM"]
-        nodes = [{"GPU": nodes[0]["GPU"], "GPU_NUM": 1} for _ in range(g)]
-        node_tflops = [tflops[n["GPU"]] for n in nodes]
-        n_nodes = g
-        max_pipes = min(args.max_num_pipeline, g)
-    for k in range(args.min_num_pipeline, max_pipes + 1):
-        splits = list(contiguous_splits(n_nodes, k))
-        if args.sort_pipeline:
-            splits.sort(key=lambda gs: imbalance_loss(gs, node_tflops))
-        if k >= 4 and args.dp_find_pipeline:
-            splits = _dp_best_splits(splits, searcher, group_types, stage_range, gpn, keep=8)
-        for groups in splits:
-            if time.time() > deadline and best is not None:
-                break
-            if args.optimal_prune and best is not None:
-                # ideal bound: the split cannot beat a perfectly balanced use of its own steady-state rates
-                rates = []
-                ok = True
-                for a, b in groups:
-                    res = searcher.cache.get((group_types(a, b), stage_range))
-                    if res is None:
-                        ok = False
+    if len(base_nodes) == 1 and base_nodes[0]["GPU_NUM"] > 1 and args.max_num_pipeline > 1:
+        base_nodes = [{"GPU": base_nodes[0]["GPU"], "GPU_NUM": 1} for _ in range(base_nodes[0]["GPU_NUM"])]
+    n_nodes = len(base_nodes)
+    max_pipes = min(args.max_num_pipeline, n_nodes)
+
+    def rate_of(results) -> float:
+        return max(r.mbs / r.bottleneck_us for r in results.values())
+
+    for order in (node_orders(base_nodes, args.max_node_orders) if args.permute_nodes else [tuple(range(n_nodes))]):
+        if time.time() > deadline and ranking.best is not None:
+            break
+        stats["node_orders"] += 1
+        nodes = [base_nodes[i] for i in order]
+        node_tflops = [tflops[n["GPU"]] * n["GPU_NUM"] for n in nodes]
+
+        def group_types(a, b, nodes=nodes):
+            return tuple(t for n in nodes[a:b] for t in [n["GPU"]] * n["GPU_NUM"])
+
+        def solve(a, b):
+            with timers.phase("pipeline-search"):
+                res = searcher.best(group_types(a, b), stage_range, gpn)
+            if res:
+                bounds.record(group_types(a, b), rate_of(res))
+            return res
+
+        def evaluate(groups) -> Optional[HybridPlan]:
+            per_group = []
+            for a, b in groups:
+                res = solve(a, b)
+                if not res:
+                    return None
+                per_group.append(res)
+            best_plan = None
+            # micro-batch size per pipeline: all combinations (<= 4^k, k small)
+            with timers.phase("batch-balancing"):
+                for combo in itertools.product(*[sorted(r) for r in per_group]):
+                    pipes = [per_group[i][m] for i, m in enumerate(combo)]
+                    sizes = balance_batches(pipes, args.global_batch_size)
+                    if sizes is None:
+                        continue
+                    it = max(p.time_us(s // p.mbs) for p, s in zip(pipes, sizes))
+                    replicas = sum(max(st.dp for st in p.stages) for p in pipes)
+                    sync = max(cost.grad_sync_us(max(p.stage_weights_mb), replicas, p.stages[0].gpu_type) for p in pipes)
+                    plan = HybridPlan(pipes, sizes, it + sync, node_order=tuple(order), groups=tuple(groups))
+                    if best_plan is None or plan.iteration_us < best_plan.iteration_us:
+                        best_plan = plan
+                    if len(per_group) > 3 and time.time() > deadline:
                         break
-                    if not res:
-                        rates = None
-                        break
-                    rates.append(max(r.mbs / r.bottleneck_us for r in res.values()))
-                if ok and rates is not None and args.global_batch_size / sum(rates) >= best.iteration_us:
-                    stats["splits_pruned"] += 1
-                    continue
-            plan = evaluate(groups)
-            stats["splits_evaluated"] += 1
-            if plan is not None and (best is None or plan.iteration_us < best.iteration_us):
-                best = plan
-                log.write(f"[{time.time() - t0:7.2f}s] pipelines={k} groups={groups} iteration={plan.iteration_us / 1e3:.2f} ms "
-                          f"throughput={plan.throughput:.2f} samples/s")
-    stats.update(seconds=time.time() - t0, pipelines_evaluated=searcher.evaluated)
-    return best, stats
+            return best_plan
+
+        for k in range(args.min_num_pipeline, max_pipes + 1):
+            splits = list(contiguous_splits(n_nodes, k))
+            if args.sort_pipeline:
+                splits.sort(key=lambda gs: imbalance_loss(gs, node_tflops))
+            if k >= 4 and args.dp_find_pipeline:
+                splits = _dp_best_splits(splits, searcher, group_types, stage_range, gpn, keep=8)
+            for groups in splits:
+                if time.time() > deadline and ranking.best is not None:
+                    break
+                if args.optimal_prune and ranking.best is not None:
+                    # The split cannot beat a perfectly balanced use of its groups' best steady-state
+                    # rates; a group not solved yet is bounded by a solved group that dominates it.
+                    total = sum(bounds.upper_bound(group_types(a, b)) for a, b in groups)
+                    if total != float("inf") and total > 0 and args.global_batch_size / total >= ranking.best.iteration_us:
+                        stats["splits_pruned"] += 1
+                        continue
+                plan = evaluate(groups)
+                stats["splits_evaluated"] += 1
+                if plan is not None and ranking.offer(plan):
+                    log.write(f"[{time.time() - t0:7.2f}s] node order={list(order)} pipelines={k} groups={groups} "
+                              f"iteration={plan.iteration_us / 1e3:.2f} ms throughput={plan.throughput:.2f} samples/s")
+    stats.update(seconds=time.time() - t0, pipelines_evaluated=searcher.evaluated, groups_refined=searcher.refined,
+                 refine_evaluations=refiner.evaluated if refiner else 0, timers=timers.report())
+    stats["ranking"] = ranking
+    return ranking.best, stats
 
 
 def _dp_best_splits(splits, searcher, group_types, stage_range, gpn, keep=8):
@@ -387,18 +467,25 @@ def main(argv=None):
     plan, stats = run_search(args)
     if plan is None:
         raise SystemExit("search found no feasible configuration (memory limit or profile coverage)")
+    ranking: Ranking = stats.pop("ranking")
     os.makedirs(os.path.join(args.config_save_path, "top_configs"), exist_ok=True)
     os.makedirs(os.path.join(args.config_save_path, "csv"), exist_ok=True)
-    cfg = plan_to_config(plan, args)
-    normalized = normalize_flexpipe_config(cfg)
     stem = f"{args.save_prefix}_{args.config_suffix}" if args.config_suffix else args.save_prefix
     for i, (p, b) in enumerate(zip(plan.pipelines, plan.batch_sizes)):
         dump_pipeline_legacy(p, b, os.path.join(args.config_save_path, f"{stem}_pipe{i}_{len(p.stages)}stages.json"), args)
-    top = os.path.join(args.config_save_path, "top_configs", f"{stem}_hybrid.json")
-    dump_hybrid_config(cfg, top)
+    normalized = None
+    for rank, (_, ranked) in enumerate(ranking.entries, 1):
+        cfg = plan_to_config(ranked, args)
+        norm = normalize_flexpipe_config(cfg)
+        name = f"{stem}_hybrid.json" if rank == 1 else f"{stem}_hybrid_rank{rank}.json"
+        dump_hybrid_config(cfg, os.path.join(args.config_save_path, "top_configs", name))
+        normalized = normalized or norm
+    ranking.write_csvs(os.path.join(args.config_save_path, "csv"), stem)
     summary = {"iteration_ms": plan.iteration_us / 1e3, "throughput_samples_per_s": plan.throughput,
                "tokens_per_s": plan.throughput * args.seq_length, "config_hash": normalized["config_hash"],
-               "pipelines": len(plan.pipelines), **stats}
+               "pipelines": len(plan.pipelines), "node_order": list(plan.node_order),
+               "pipeline_node_slices": [list(g) for g in plan.groups],
+               "found_by": [p.found_by for p in plan.pipelines], "op_grain": args.op_grain, **stats}
     with open(os.path.join(args.config_save_path, "csv", f"{stem}_summary.json"), "w") as f:
         json.dump(summary, f, indent=2)
     print(json.dumps(summary))

@@ -35,8 +35,13 @@ def recompute_bitmap(stage_index, num_stages, layers, recompute_layers):
 
 def pipeline_to_pipe_dict(p, global_batch, num_layers):
     S = len(p.stages)
-    ops = stage_op_counts(p.layers)
-    rec = [recompute_bitmap(i, S, p.layers[i], p.recompute_layers[i]) for i in range(S)]
+    if getattr(p, "op_counts", None):
+        # op-granular result of the local search: cuts may fall inside a layer, recompute is per op
+        ops = list(p.op_counts)
+        rec = [list(m) if m else [0] * n for m, n in zip(p.recompute_masks or [()] * S, ops)]
+    else:
+        ops = stage_op_counts(p.layers)
+        rec = [recompute_bitmap(i, S, p.layers[i], p.recompute_layers[i]) for i in range(S)]
     return {
         "global_batch_size": int(global_batch), "micro_batch_size": int(p.mbs), "num_stages": S,
         "num_gpus": [s.gpus for s in p.stages],
@@ -63,3 +68,26 @@ def dump_pipeline_legacy(p, global_batch, path, args):
 def dump_hybrid_config(config, path):
     with open(path, "w") as f:
         json.dump(config, f, indent=4)
+
+
+def load_initial_plan(path, num_layers, gpu_types):
+    """A legacy single-pipeline JSON (this module's `dump_pipeline_legacy`, or the reference's) as a
+    starting point of the local search; None if it does not describe this model."""
+    from .state import PipelinePlan, StagePlan, total_ops
+    try:
+        with open(path) as f:
+            d = json.load(f)
+    except (OSError, ValueError):
+        return None
+    counts = d.get("num_ops_in_each_stage")
+    if not counts or sum(counts) != total_ops(num_layers):
+        return None
+    stages, cursor, gpu_cursor = [], 0, 0
+    for i, n in enumerate(counts):
+        gpus = d["num_gpus"][i]
+        types = tuple(sorted(set(gpu_types[gpu_cursor:gpu_cursor + gpus]))) or (gpu_types[0],)
+        stages.append(StagePlan(cursor, cursor + n, gpus, d["model_parallel_size_of_each_op"][i][0],
+                                d["data_parallel_size_of_each_op"][i][0], types))
+        cursor += n
+        gpu_cursor += gpus
+    return PipelinePlan(tuple(stages), int(d["micro_batch_size"]))

@@ -26,12 +26,12 @@ def _shares():
 
 
 def generate(output, model_size="1_3B", hardware="example-gpu", tp_sizes=(1, 2, 4), mbs_list=(1, 2, 4, 8), seed=0,
-             alpha_us=10.0, beta_gbs=20.0, vocab=51200, status="complete"):
+             alpha_us=10.0, beta_gbs=20.0, vocab=51200, status="complete", slowdown=1.0):
     m = GPT_SIZES[model_size]
     h, s = m["hidden_size"], m["seq_length"]
     rng = random.Random(seed)
-    layer_fwd_ms = rng.uniform(1.0, 3.0)     # one layer, mbs 1, TP 1
-    layer_bwd_ms = rng.uniform(1.0, 3.0) * 2
+    layer_fwd_ms = rng.uniform(1.0, 3.0) * slowdown     # one layer, mbs 1, TP 1 (`slowdown` > 1: a slower GPU type)
+    layer_bwd_ms = rng.uniform(1.0, 3.0) * 2 * slowdown
     os.makedirs(output, exist_ok=True)
     mb = 1.0 / (1024 * 1024)
     sizes = set()
