@@ -35,9 +35,20 @@ LAYER_OPS = (
     "enc-MLP-GEMM-2",
     "enc-post-MLP-dropout",
 )
+# The older 13-op layer: attention is four ops (scores, softmax, dropout, context) instead of one
+# fused flash-attention op (reference: eth/searching/model_ops.py:10-43,
+# eth/runtime/megatron/model/flex_ops.py:1144-1519).
+LEGACY_LAYER_OPS = (
+    "enc-1st-layernorm", "enc-attention-qkv", "enc-attention-score", "enc-attention-softmax",
+    "enc-attention-dropout", "enc-attention-context", "enc-attention-dense", "enc-post-attention-dropout",
+    "enc-2nd-layernorm", "enc-MLP-GEMM-1", "enc-MLP-gelu", "enc-MLP-GEMM-2", "enc-post-MLP-dropout",
+)
 FIRST_OP = "encoder-embedding"
 TAIL_OPS = ("final-layernorm", "gpt-post-process")
-MODEL_IMPLS = {"gpt": {"id": "gpt", "ops_per_layer": len(LAYER_OPS), "layer_schema": LAYER_OPS}}
+MODEL_IMPLS = {
+    "gpt": {"id": "gpt", "ops_per_layer": len(LAYER_OPS), "layer_schema": LAYER_OPS},
+    "gpt-legacy13": {"id": "gpt-legacy13", "ops_per_layer": len(LEGACY_LAYER_OPS), "layer_schema": LEGACY_LAYER_OPS},
+}
 
 SUPPORTED_TP = (1, 2, 4, 6, 8)
 

@@ -73,6 +73,45 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& d, con
   check(ethb::gemm_tcgen05(g, cur_stream()), "gemm_tcgen05");
 }
 
+// Batched GEMM over two leading batch dimensions: d[i, j] = alpha * a[i, j] x b[i, j]^T (+ d[i, j]).
+// a, b, d are 4-D views [B1, B2, rows, cols] with unit inner stride and arbitrary other strides, so
+// the per-head q / k / v slices of a packed QKV activation are used in place. One launch of the
+// tcgen05 GEMM per (i, j): the score (Q K^T) and context (P V) products of the unfused attention ops.
+void gemm_batched(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& d, double alpha,
+                  bool accumulate, const OptTensor& status) {
+  need_cuda(a, "a"); need_cuda(b, "b"); need_cuda(d, "d");
+  TORCH_CHECK(a.dim() == 4 && b.dim() == 4 && d.dim() == 4, "gemm_batched expects 4-D views");
+  TORCH_CHECK(a.stride(3) == 1 && b.stride(3) == 1 && d.stride(3) == 1, "inner stride must be 1");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a/b dtype mismatch");
+  TORCH_CHECK(a.size(0) == b.size(0) && a.size(0) == d.size(0) && a.size(1) == b.size(1) && a.size(1) == d.size(1),
+              "batch dimensions differ");
+  c10::cuda::CUDAGuard guard(a.device());
+  ethb::GemmArgs g{};
+  g.M = static_cast<int>(a_mn ? a.size(3) : a.size(2));
+  g.K = static_cast<int>(a_mn ? a.size(2) : a.size(3));
+  g.N = static_cast<int>(b_mn ? b.size(3) : b.size(2));
+  TORCH_CHECK((b_mn ? b.size(2) : b.size(3)) == g.K, "reduction dims differ");
+  TORCH_CHECK(d.size(2) == g.M && d.size(3) == g.N, "bad output shape");
+  g.lda = a.stride(2); g.a_mn = a_mn;
+  g.ldb = b.stride(2); g.b_mn = b_mn;
+  g.ldd = d.stride(2);
+  g.ab_dtype = dtype_code(a);
+  TORCH_CHECK(g.ab_dtype != 0, "gemm operands must be fp16/bf16");
+  g.d_dtype = dtype_code(d);
+  g.accumulate = accumulate;
+  g.alpha = static_cast<float>(alpha);
+  g.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  const int64_t ea = a.element_size(), ed = d.element_size();
+  auto stream = cur_stream();
+  for (int64_t i = 0; i < a.size(0); ++i)
+    for (int64_t j = 0; j < a.size(1); ++j) {
+      g.A = static_cast<const char*>(a.data_ptr()) + (i * a.stride(0) + j * a.stride(1)) * ea;
+      g.B = static_cast<const char*>(b.data_ptr()) + (i * b.stride(0) + j * b.stride(1)) * ea;
+      g.D = static_cast<char*>(d.data_ptr()) + (i * d.stride(0) + j * d.stride(1)) * ed;
+      check(ethb::gemm_tcgen05(g, stream), "gemm_batched");
+    }
+}
+
 // GEMM fused with the tensor-parallel all-reduce. The result lands in every rank's `out` buffer
 // (`out_ptrs[rank]` is this rank's, M x N with row stride ldd).
 void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, const OptTensor& bias,
@@ -520,6 +559,7 @@ void peer_flags(const std::vector<int64_t>& flags, int64_t rank, int64_t epoch, 
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_batched", &gemm_batched);
   m.def("gemm_allreduce", &gemm_allreduce);
   m.def("gemm_allgather", &gemm_allgather);
   m.def("layernorm_fwd", &layernorm_fwd);

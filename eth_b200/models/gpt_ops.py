@@ -24,7 +24,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..contract.config import FIRST_OP, LAYER_OPS, TAIL_OPS
+from ..contract.config import FIRST_OP, MODEL_IMPLS, TAIL_OPS
 from ..ops import raw
 
 
@@ -47,6 +47,8 @@ class GPTModelConfig:
     seed: int = 1234
     canonical_init: bool = False     # U(-0.02, 0.02) seeded by sha256(logical id), CPU generator
     zero_labels: bool = False        # the reference's synthetic labels are all zero
+    model_impl: str = "gpt"          # "gpt": 10 ops per layer; "gpt-legacy13": unfused attention, 13 ops
+    attention_dropout: float = 0.0   # used by the unfused attention ops only
 
     @property
     def ffn_hidden_size(self) -> int:
@@ -352,6 +354,84 @@ class FlashAttentionOp(Op):
                                         self.cfg.head_dim)
 
 
+class AttentionScoreOp(Op):
+    """Unfused attention, op 1 of 4: raw scores Q K^T per head as batched tcgen05 GEMMs. `qkv` stays
+    alive for the context op (reference: ParallelAttentionScoreOp, model/flex_ops.py:1144-1244)."""
+    reads = ("qkv",)
+    writes = ("attention_scores", "qkv")
+
+    def fwd(self, env, ctx, mb):
+        qkv = env["qkv"]
+        heads = self.cfg.num_attention_heads // self.tp.size
+        ctx["qkv"], ctx["shape"] = qkv, (mb.batch, mb.seq, heads, self.cfg.head_dim)
+        env["attention_scores"] = raw.attn_scores_fwd(qkv, *ctx["shape"])
+
+    def bwd(self, genv, ctx, mb):
+        d_scores = _take(genv, "attention_scores")
+        dqkv = genv.get("qkv")      # created by the context op's backward (v slot already filled)
+        if dqkv is None:
+            raise RuntimeError("missing gradient for qkv: the context op must run its backward first")
+        raw.attn_scores_bwd(d_scores, ctx["qkv"], dqkv, *ctx["shape"])
+
+
+class AttentionSoftmaxOp(Op):
+    """Unfused attention, op 2 of 4: softmax(scores / sqrt(d)) with the implicit causal mask
+    (reference: ParallelSoftmaxFusionOp, model/flex_ops.py:1246-1330)."""
+    reads = ("attention_scores",)
+    writes = ("attention_probs",)
+    consumes = ("attention_scores",)
+
+    def fwd(self, env, ctx, mb):
+        scale = 1.0 / math.sqrt(self.cfg.head_dim)
+        probs = raw.softmax_fwd(env.pop("attention_scores"), scale, causal=True)
+        ctx["probs"], ctx["scale"] = probs, scale
+        env["attention_probs"] = probs
+
+    def bwd(self, genv, ctx, mb):
+        d = _take(genv, "attention_probs")
+        genv["attention_scores"] = raw.softmax_bwd(d, ctx["probs"], ctx["scale"], causal=True)
+
+
+class AttentionDropoutOp(Op):
+    """Unfused attention, op 3 of 4: dropout on the attention probabilities
+    (reference: ParallelSoftmaxDropoutOp, model/flex_ops.py:1332-1374)."""
+    reads = ("attention_probs",)
+    writes = ("attention_probs",)
+
+    def fwd(self, env, ctx, mb):
+        p = self.cfg.attention_dropout
+        if p > 0:
+            ctx["drop"] = (p, self.cfg.seed + self.op_index, self.dropout_offset(mb) + self.tp.rank)
+            probs = env["attention_probs"]
+            env["attention_probs"] = raw.bias_dropout_add_fwd(probs.view(-1, probs.shape[-1]), None, None,
+                                                              *ctx["drop"]).view(probs.shape)
+
+    def bwd(self, genv, ctx, mb):
+        if "drop" in ctx:
+            d = _take(genv, "attention_probs")
+            genv["attention_probs"] = raw.dropout_bwd(d.view(-1, d.shape[-1]), *ctx["drop"]).view(d.shape)
+
+
+class AttentionContextOp(Op):
+    """Unfused attention, op 4 of 4: context = P V per head (batched tcgen05 GEMMs), token-major
+    (reference: ParallelContextOp, model/flex_ops.py:1431-1519)."""
+    reads = ("attention_probs", "qkv")
+    writes = ("hidden_states",)
+    consumes = ("attention_probs", "qkv")
+
+    def fwd(self, env, ctx, mb):
+        probs, qkv = env.pop("attention_probs"), env.pop("qkv")
+        heads = self.cfg.num_attention_heads // self.tp.size
+        ctx["probs"], ctx["qkv"], ctx["shape"] = probs, qkv, (mb.batch, mb.seq, heads, self.cfg.head_dim)
+        env["hidden_states"] = raw.attn_context_fwd(probs, qkv, *ctx["shape"])
+
+    def bwd(self, genv, ctx, mb):
+        d = _take(genv, "hidden_states")
+        d_probs, dqkv = raw.attn_context_bwd(d.contiguous(), ctx["probs"], ctx["qkv"], *ctx["shape"])
+        genv["attention_probs"] = d_probs
+        genv["qkv"] = dqkv
+
+
 class BiasDropoutAddOp(Op):
     """hidden = residual + dropout(hidden + output_bias) (reference: model/flex_ops.py:104-134)."""
 
@@ -429,11 +509,12 @@ class PostProcessOp(Op):
 # ------------------------------------------------------------------------------------------
 # manifest -> ops
 # ------------------------------------------------------------------------------------------
-def build_op_descriptors(num_layers: int) -> List[dict]:
+def build_op_descriptors(num_layers: int, model_impl: str = "gpt") -> List[dict]:
     """Runtime op list in manifest order: [{op_index, name, layer_index, prev_name}]."""
+    layer_ops = MODEL_IMPLS[model_impl]["layer_schema"]
     names: List[Tuple[str, Optional[int]]] = [(FIRST_OP, None)]
     for layer in range(num_layers):
-        names += [(n, layer) for n in LAYER_OPS]
+        names += [(n, layer) for n in layer_ops]
     names += [(n, None) for n in TAIL_OPS]
     out = []
     for i, (n, layer) in enumerate(names):
@@ -453,6 +534,14 @@ def make_op(desc: dict, cfg: GPTModelConfig, tp: TPComm) -> Op:
         return ColumnLinearOp(*a, in_features=h, out_features=3 * h, suffix="attention.query_key_value", out_name="qkv")
     if n == "enc-flash-attention":
         return FlashAttentionOp(*a)
+    if n == "enc-attention-score":
+        return AttentionScoreOp(*a)
+    if n == "enc-attention-softmax":
+        return AttentionSoftmaxOp(*a)
+    if n == "enc-attention-dropout":
+        return AttentionDropoutOp(*a)
+    if n == "enc-attention-context":
+        return AttentionContextOp(*a)
     if n == "enc-attention-dense":
         return RowLinearOp(*a, in_features=h, out_features=h, suffix="attention.dense")
     if n == "enc-post-attention-dropout":
@@ -487,6 +576,12 @@ LIVE_AFTER = {
     "enc-1st-layernorm": (_H, _R1),
     "enc-attention-qkv": (("qkv", 3, True, True), _R1),
     "enc-flash-attention": (("hidden_states", 1, True, True), _R1),
+    # the per-head [seq x seq] tensors of the unfused attention block are not token-major: a stage
+    # boundary may not fall inside that block
+    "enc-attention-score": None,
+    "enc-attention-softmax": None,
+    "enc-attention-dropout": None,
+    "enc-attention-context": (("hidden_states", 1, True, True), _R1),
     "enc-attention-dense": (_H, _B, _R1),
     "enc-post-attention-dropout": (_H,),
     "enc-2nd-layernorm": (_H, _R2),

@@ -50,7 +50,7 @@ class GPTStage:
         self.cfg = cfg
         self.tp = tp or TPComm()
         self.device = torch.device(device)
-        self.descriptors = build_op_descriptors(cfg.num_layers)
+        self.descriptors = build_op_descriptors(cfg.num_layers, getattr(cfg, "model_impl", "gpt"))
         self.op_begin, self.op_end = op_begin, op_end
         self.ops: List[Op] = [make_op(d, cfg, self.tp) for d in self.descriptors[op_begin:op_end]]
         self.is_first = op_begin == 0
@@ -70,6 +70,9 @@ class GPTStage:
         prev = self.descriptors[op_begin - 1]["name"] if op_begin > 0 else None
         self.input_spec = LIVE_AFTER[prev] if prev else ()
         self.output_spec = LIVE_AFTER[self.descriptors[op_end - 1]["name"]]
+        if self.input_spec is None or self.output_spec is None:
+            raise ValueError("a stage boundary may not fall inside the unfused attention block "
+                             "(enc-attention-score .. enc-attention-context)")
 
     # ------------------------------------------------------------------ parameters
     def _build_params(self):
@@ -236,4 +239,5 @@ class GPTStage:
 
 def build_full_model(cfg: GPTModelConfig, device="cpu", tp: Optional[TPComm] = None, **kw) -> GPTStage:
     """The whole op list as a single stage (PP = 1)."""
-    return GPTStage(cfg, 0, 3 + 10 * cfg.num_layers, tp=tp, device=device, **kw)
+    per_layer = 13 if getattr(cfg, "model_impl", "gpt") == "gpt-legacy13" else 10
+    return GPTStage(cfg, 0, 3 + per_layer * cfg.num_layers, tp=tp, device=device, **kw)

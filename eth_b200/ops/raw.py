@@ -321,3 +321,90 @@ def attention_bwd(d_out, qkv, out, lse, batch, seq, heads, head_dim, scale=None,
         ref = attention_ref(qd, kd, vd, scale, causal)
         gq, gk, gv = torch.autograd.grad(ref, (qd, kd, vd), d_out.view(batch, seq, heads, head_dim).float())
     return torch.stack([gq, gk, gv], 3).to(qkv.dtype).reshape(qkv.shape)
+
+
+# ---------------------------------------------------------------------------------- unfused attention (13-op manifest)
+def bmm_heads(a, b, out, *, a_mn=False, b_mn=False, alpha=1.0, accumulate=False):
+    """out[i, j] = alpha * a[i, j] x b[i, j]^T (+ out[i, j]) over two leading batch dims
+    ([batch, heads, rows, cols] views, unit inner stride, any other strides). CUDA: one tcgen05 GEMM
+    launch per (batch, head) from a single native call (the reference: torch.baddbmm / torch.bmm on
+    cuBLAS, eth/runtime/megatron/model/flex_ops.py:1229-1233, 1502)."""
+    if native.use_native(a):
+        native.lib().gemm_batched(a, a_mn, b, b_mn, out, float(alpha), bool(accumulate), native.status(a.device))
+        return out
+    af = (a.transpose(-1, -2) if a_mn else a).float()
+    bf = (b if b_mn else b.transpose(-1, -2)).float()
+    v = alpha * torch.matmul(af, bf)
+    out.copy_((v + out.float() if accumulate else v).to(out.dtype))
+    return out
+
+
+def _qkv_heads(qkv, batch, seq, heads, head_dim):
+    """q, k, v as [batch, heads, seq, head_dim] views of the packed [tokens, heads * 3 * head_dim] activation."""
+    v5 = qkv.view(batch, seq, heads, 3, head_dim)
+    return tuple(v5[:, :, :, j].permute(0, 2, 1, 3) for j in range(3))
+
+
+def attn_scores_fwd(qkv, batch, seq, heads, head_dim):
+    """Raw scores Q K^T per head: [batch, heads, seq, seq] (the scale is applied by the softmax op)."""
+    q, k, _ = _qkv_heads(qkv, batch, seq, heads, head_dim)
+    scores = torch.empty((batch, heads, seq, seq), dtype=qkv.dtype, device=qkv.device)
+    return bmm_heads(q, k, scores)
+
+
+def attn_scores_bwd(d_scores, qkv, dqkv, batch, seq, heads, head_dim):
+    """dQ = dS K and dK = dS^T Q written into the q / k slots of the packed gradient `dqkv`."""
+    q, k, _ = _qkv_heads(qkv, batch, seq, heads, head_dim)
+    dq, dk, _ = _qkv_heads(dqkv, batch, seq, heads, head_dim)
+    bmm_heads(d_scores, k, dq, b_mn=True)
+    bmm_heads(d_scores, q, dk, a_mn=True, b_mn=True)
+
+
+def attn_context_fwd(probs, qkv, batch, seq, heads, head_dim):
+    """P V per head, written token-major: [tokens, heads * head_dim]."""
+    _, _, v = _qkv_heads(qkv, batch, seq, heads, head_dim)
+    out = torch.empty((batch * seq, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    o4 = out.view(batch, seq, heads, head_dim).permute(0, 2, 1, 3)
+    bmm_heads(probs, v, o4, b_mn=True)
+    return out
+
+
+def attn_context_bwd(d_out, probs, qkv, batch, seq, heads, head_dim):
+    """(dP, dqkv): dP = dO V^T; dV = P^T dO goes into the v slot of a fresh packed gradient whose
+    q / k slots the score op's backward fills."""
+    _, _, v = _qkv_heads(qkv, batch, seq, heads, head_dim)
+    do4 = d_out.view(batch, seq, heads, head_dim).permute(0, 2, 1, 3)
+    d_probs = torch.empty_like(probs)
+    bmm_heads(do4, v, d_probs)
+    dqkv = torch.empty_like(qkv)
+    _, _, dv = _qkv_heads(dqkv, batch, seq, heads, head_dim)
+    bmm_heads(probs, do4, dv, a_mn=True, b_mn=True)
+    return d_probs, dqkv
+
+
+def softmax_fwd(x, scale, causal=True):
+    """softmax(scale * x) over the last dim with the implicit causal mask (x: [..., sq, sk])."""
+    from .functional import SOFTMAX_CAUSAL, SOFTMAX_PLAIN
+    mode = SOFTMAX_CAUSAL if causal else SOFTMAX_PLAIN
+    if native.use_native(x):
+        y = torch.empty_like(x)
+        native.lib().softmax_fwd(x.view(-1, x.shape[-2], x.shape[-1]), None, y.view(-1, x.shape[-2], x.shape[-1]),
+                                 float(scale), mode)
+        return y
+    v = x.float() * scale
+    if causal:
+        sq, sk = x.shape[-2], x.shape[-1]
+        v = v.masked_fill(torch.triu(torch.ones(sq, sk, dtype=torch.bool, device=x.device), 1), float("-inf"))
+    return torch.softmax(v, -1).to(x.dtype)
+
+
+def softmax_bwd(dy, y, scale, causal=True):
+    from .functional import SOFTMAX_CAUSAL, SOFTMAX_PLAIN
+    if native.use_native(y):
+        dx = torch.empty_like(y)
+        shape = (-1, y.shape[-2], y.shape[-1])
+        native.lib().softmax_bwd(dy.contiguous().view(shape), y.view(shape), dx.view(shape), float(scale),
+                                 SOFTMAX_CAUSAL if causal else SOFTMAX_PLAIN)
+        return dx
+    yf, dyf = y.float(), dy.float()
+    return ((dyf - (dyf * yf).sum(-1, keepdim=True)) * yf * scale).to(y.dtype)

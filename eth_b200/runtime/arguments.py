@@ -179,8 +179,6 @@ def finalize_args(args, config=None):
     if args.bf16:
         args.accumulate_allreduce_grads_in_fp32 = True   # reference: arguments.py:268-277
     args.grad_dtype = torch.float32 if (args.accumulate_allreduce_grads_in_fp32 or not args.fp16) else torch.float16
-    if args.attention_dropout not in (0, 0.0):
-        raise ValueError("the flash-attention path supports --attention-dropout 0 only")
     if args.interleave_factor != 1:
         raise NotImplementedError("interleaved 1F1B (--interleave-factor > 1) is not available; use 1")
 
@@ -193,6 +191,9 @@ def finalize_args(args, config=None):
     normalized = normalize_flexpipe_config(config, args.world_size)
     apply_normalized_config_to_args(args, normalized)
     args.normalized_config = normalized
+    if args.attention_dropout not in (0, 0.0) and normalized["model_impl"] == "gpt":
+        raise ValueError("the flash-attention path supports --attention-dropout 0 only "
+                         "(the unfused 13-op manifest, model_impl gpt-legacy13, has an attention-dropout op)")
     args.canonical_topology = build_canonical_topology(normalized)
     max_tp = max(s.tp_degree for s in args.canonical_topology.stages)
     multiple = args.make_vocab_size_divisible_by * max_tp

@@ -102,7 +102,8 @@ class TrainEngine:
             layernorm_epsilon=args.layernorm_epsilon, init_method_std=args.init_method_std,
             params_dtype=args.params_dtype, grad_dtype=args.grad_dtype, seed=args.seed,
             canonical_init=getattr(args, "grad_sync_evidence_canonical_init", False),
-            zero_labels=getattr(args, "reference_zero_labels", False))
+            zero_labels=getattr(args, "reference_zero_labels", False),
+            model_impl=cfg.get("model_impl", "gpt"), attention_dropout=getattr(args, "attention_dropout", 0.0) or 0.0)
         self.tp = self._make_tp_comm()
         begin, end = ps.op_range
         self.stage = GPTStage(self.model_cfg, begin, end, tp=self.tp, device=self.device,

@@ -11,14 +11,9 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional
 
-from ..contract.config import FIRST_OP, LAYER_OPS, TAIL_OPS
+from ..contract.config import FIRST_OP, LAYER_OPS, LEGACY_LAYER_OPS, TAIL_OPS
 
 PUBLIC_LAYER_OPS = LAYER_OPS
-LEGACY_LAYER_OPS = (
-    "enc-1st-layernorm", "enc-attention-qkv", "enc-attention-score", "enc-attention-softmax",
-    "enc-attention-dropout", "enc-attention-context", "enc-attention-dense", "enc-post-attention-dropout",
-    "enc-2nd-layernorm", "enc-MLP-GEMM-1", "enc-MLP-gelu", "enc-MLP-GEMM-2", "enc-post-MLP-dropout",
-)
 TP_TUNABLE_OPS = ("enc-attention-qkv", "enc-attention-dense", "enc-MLP-GEMM-1", "enc-MLP-GEMM-2")
 NEVER_RECOMPUTE_OPS = (FIRST_OP, "enc-1st-layernorm") + TAIL_OPS
 

@@ -138,3 +138,33 @@ def test_bounded_device_wait_runs_out_and_reports():
     native.lib().peer_flags([mine.data_ptr(), other.data_ptr()], 0, 1, -1, 0, native.status(dev))
     torch.cuda.synchronize()
     native.check_status(dev)
+
+
+def test_unfused_attention_ops_on_gpu_match_flash_attention():
+    """The four ops of the 13-op manifest (batched tcgen05 GEMMs for Q K^T and P V, the causal
+    softmax kernel) against the fused flash-attention kernel: same output, same packed gradient."""
+    from eth_b200.ops import native, raw
+    dev = torch.device("cuda", 0)
+    b, s, heads, d = 2, 256, 4, 64
+    torch.manual_seed(0)
+    qkv = (torch.randn(b * s, heads * 3 * d, device=dev) * 0.5).to(torch.bfloat16)
+    d_out = (torch.randn(b * s, heads * d, device=dev) * 0.5).to(torch.bfloat16)
+    out_f, lse = raw.attention_fwd(qkv, b, s, heads, d)
+    dqkv_f = raw.attention_bwd(d_out, qkv, out_f, lse, b, s, heads, d)
+    scores = raw.attn_scores_fwd(qkv, b, s, heads, d)
+    probs = raw.softmax_fwd(scores, d ** -0.5, causal=True)
+    out_u = raw.attn_context_fwd(probs, qkv, b, s, heads, d)
+    d_probs, dqkv_u = raw.attn_context_bwd(d_out, probs, qkv, b, s, heads, d)
+    d_scores = raw.softmax_bwd(d_probs, probs, d ** -0.5, causal=True)
+    raw.attn_scores_bwd(d_scores, qkv, dqkv_u, b, s, heads, d)
+    torch.cuda.synchronize()
+    native.check_status()
+    # fp32 reference of the scores, to check the batched GEMM on its own
+    v5 = qkv.view(b, s, heads, 3, d).float()
+    ref_scores = torch.einsum("bqhd,bkhd->bhqk", v5[:, :, :, 0], v5[:, :, :, 1])
+    def err(a, ref):
+        a, ref = a.float(), ref.float()
+        return max(((a - ref).norm() / ref.norm()).item(), ((a - ref).abs().max() / ref.abs().max()).item())
+    assert err(scores, ref_scores) < 1e-2
+    assert err(out_u, out_f) < 2e-2
+    assert err(dqkv_u, dqkv_f) < 4e-2
