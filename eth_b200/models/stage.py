@@ -45,34 +45,50 @@ def _align(n: int, a: int = 128) -> int:
 
 
 class GPTStage:
+    """`chunks`: for interleaved pipelining a rank owns several op ranges (model chunks) that are
+    not adjacent in the model; they share the flat buffers and are executed one chunk at a time
+    (`forward(..., chunk=c)`). Without it the stage is the single range [op_begin, op_end)."""
+
     def __init__(self, cfg: GPTModelConfig, op_begin: int, op_end: int, tp: Optional[TPComm] = None,
-                 device="cpu", recompute_ops: Optional[Sequence[int]] = None, fuse: bool = True):
+                 device="cpu", recompute_ops: Optional[Sequence[int]] = None, fuse: bool = True,
+                 chunks: Optional[Sequence[Tuple[int, int]]] = None):
         self.cfg = cfg
         self.tp = tp or TPComm()
         self.device = torch.device(device)
         self.descriptors = build_op_descriptors(cfg.num_layers, getattr(cfg, "model_impl", "gpt"))
-        self.op_begin, self.op_end = op_begin, op_end
-        self.ops: List[Op] = [make_op(d, cfg, self.tp) for d in self.descriptors[op_begin:op_end]]
-        self.is_first = op_begin == 0
-        self.is_last = op_end == len(self.descriptors)
+        self.chunk_ranges: List[Tuple[int, int]] = [tuple(c) for c in chunks] if chunks else [(op_begin, op_end)]
+        self.op_begin, self.op_end = self.chunk_ranges[0][0], self.chunk_ranges[-1][1]
+        self.ops: List[Op] = []
+        self._chunk_slices: List[Tuple[int, int]] = []      # index range of every chunk inside self.ops
+        for b, e in self.chunk_ranges:
+            start = len(self.ops)
+            self.ops += [make_op(d, cfg, self.tp) for d in self.descriptors[b:e]]
+            self._chunk_slices.append((start, len(self.ops)))
+        self.is_first = self.chunk_ranges[0][0] == 0
+        self.is_last = self.chunk_ranges[-1][1] == len(self.descriptors)
         self.recompute = list(recompute_ops) if recompute_ops is not None else [0] * len(self.ops)
         if len(self.recompute) != len(self.ops):
             raise ValueError("recompute_ops length must equal the stage's op count")
         self._build_params()
         if fuse:
             self._mark_fusions()
-        self._segments = self._plan_segments()
-        self._contexts: Dict[int, dict] = {}
+        self._segments_by_chunk = [self._plan_segments(a, z) for a, z in self._chunk_slices]
+        self._segments = self._segments_by_chunk[0]
+        self._contexts: Dict[object, dict] = {}
         # called with the global op index after every op's backward (the engine sets it for the last
         # micro-batch of an iteration to start gradient reductions while backward is still running)
         self.after_op_backward = None
         self.op_events = None   # set to a list to record (op name, phase, start event, end event)
-        prev = self.descriptors[op_begin - 1]["name"] if op_begin > 0 else None
-        self.input_spec = LIVE_AFTER[prev] if prev else ()
-        self.output_spec = LIVE_AFTER[self.descriptors[op_end - 1]["name"]]
-        if self.input_spec is None or self.output_spec is None:
-            raise ValueError("a stage boundary may not fall inside the unfused attention block "
-                             "(enc-attention-score .. enc-attention-context)")
+        self.chunk_specs = []         # per chunk: (tensors entering it, tensors leaving it)
+        for b, e in self.chunk_ranges:
+            prev = self.descriptors[b - 1]["name"] if b > 0 else None
+            spec_in = LIVE_AFTER[prev] if prev else ()
+            spec_out = LIVE_AFTER[self.descriptors[e - 1]["name"]]
+            if spec_in is None or spec_out is None:
+                raise ValueError("a stage boundary may not fall inside the unfused attention block "
+                                 "(enc-attention-score .. enc-attention-context)")
+            self.chunk_specs.append((spec_in, spec_out))
+        self.input_spec, self.output_spec = self.chunk_specs[0][0], self.chunk_specs[-1][1]
 
     # ------------------------------------------------------------------ parameters
     def _build_params(self):
@@ -144,16 +160,19 @@ class GPTStage:
         self.grad_buf.zero_()
 
     def _mark_fusions(self):
-        for a, b in zip(self.ops, self.ops[1:]):
-            if a.name == "enc-MLP-GEMM-1" and b.name == "enc-MLP-gelu":
-                a.fuse_next = True
-            if a.name == "enc-MLP-gelu" and b.name == "enc-MLP-GEMM-2":
-                b.fuse_prev = True
+        for start, end in self._chunk_slices:       # never across a chunk boundary
+            ops = self.ops[start:end]
+            for a, b in zip(ops, ops[1:]):
+                if a.name == "enc-MLP-GEMM-1" and b.name == "enc-MLP-gelu":
+                    a.fuse_next = True
+                if a.name == "enc-MLP-gelu" and b.name == "enc-MLP-GEMM-2":
+                    b.fuse_prev = True
 
     # ------------------------------------------------------------------ recompute segments
-    def _plan_segments(self) -> List[Tuple[int, int, bool]]:
-        """Maximal runs [i, j) of equal recompute flag; recompute runs break at enc-1st-layernorm."""
-        segs, i, n = [], 0, len(self.ops)
+    def _plan_segments(self, start: int = 0, end: Optional[int] = None) -> List[Tuple[int, int, bool]]:
+        """Maximal runs [i, j) of equal recompute flag inside ops[start:end]; recompute runs break at
+        enc-1st-layernorm."""
+        segs, i, n = [], start, len(self.ops) if end is None else end
         while i < n:
             flag = bool(self.recompute[i])
             j = i + 1
@@ -183,12 +202,15 @@ class GPTStage:
             out[(name, phase)] = out.get((name, phase), 0.0) + s.elapsed_time(e)
         return out
 
-    def forward(self, mb: MicroBatch, inputs: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    def _key(self, mb_index: int, chunk: int):
+        return mb_index if len(self.chunk_ranges) == 1 else (mb_index, chunk)
+
+    def forward(self, mb: MicroBatch, inputs: Dict[str, torch.Tensor], chunk: int = 0) -> Dict[str, torch.Tensor]:
         env = dict(inputs)
         ctxs: Dict[int, dict] = {}
         mb.ctxs = ctxs
         saved_envs: Dict[int, dict] = {}
-        for (i, j, recompute) in self._segments:
+        for (i, j, recompute) in self._segments_by_chunk[chunk]:
             if recompute:
                 # tensors that live in a short-lived ring slot must be copied to survive until backward
                 saved_envs[i] = {k: (v.clone() if getattr(v, "_ethb_ring", False) else v) for k, v in env.items()}
@@ -202,16 +224,20 @@ class GPTStage:
                 for op in self.ops[i:j]:
                     ctxs[op.op_index] = {}
                     self._run(op, "fwd", op.fwd, env, ctxs[op.op_index], mb)
-        self._contexts[mb.index] = {"ctxs": ctxs, "envs": saved_envs, "mb": mb}
-        keep = {name for name, *_ in self.output_spec} | ({"output"} if self.is_last else set())
+        self._contexts[self._key(mb.index, chunk)] = {"ctxs": ctxs, "envs": saved_envs, "mb": mb}
+        last_chunk = chunk == len(self.chunk_ranges) - 1
+        keep = {name for name, *_ in self.chunk_specs[chunk][1]} | ({"output"} if (self.is_last and last_chunk) else set())
         return {k: v for k, v in env.items() if k in keep}
 
-    def backward(self, mb_index: int, grad_outputs: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        rec = self._contexts.pop(mb_index)
+    def context_of(self, mb_index: int, chunk: int = 0) -> dict:
+        return self._contexts[self._key(mb_index, chunk)]
+
+    def backward(self, mb_index: int, grad_outputs: Dict[str, torch.Tensor], chunk: int = 0) -> Dict[str, torch.Tensor]:
+        rec = self._contexts.pop(self._key(mb_index, chunk))
         ctxs, saved_envs, mb = rec["ctxs"], rec["envs"], rec["mb"]
         mb.ctxs = ctxs
         genv = dict(grad_outputs)
-        for (i, j, recompute) in reversed(self._segments):
+        for (i, j, recompute) in reversed(self._segments_by_chunk[chunk]):
             if recompute:
                 env = saved_envs.pop(i)
                 for op in self.ops[i:j]:
@@ -221,11 +247,11 @@ class GPTStage:
                 self._run(op, "bwd", op.bwd, genv, ctxs.pop(op.op_index), mb)
                 if self.after_op_backward is not None:
                     self.after_op_backward(op.op_index)
-        keep = {name for name, *_ in self.input_spec}
+        keep = {name for name, *_ in self.chunk_specs[chunk][0]}
         return {k: v for k, v in genv.items() if k in keep and isinstance(v, torch.Tensor)}
 
-    def drop_context(self, mb_index: int) -> None:
-        self._contexts.pop(mb_index, None)
+    def drop_context(self, mb_index: int, chunk: int = 0) -> None:
+        self._contexts.pop(self._key(mb_index, chunk), None)
 
     # ------------------------------------------------------------------ boundary shapes
     def boundary_shapes(self, spec, tokens: int) -> Dict[str, Tuple[int, ...]]:

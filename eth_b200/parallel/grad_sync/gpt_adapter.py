@@ -25,8 +25,10 @@ def collect_gpt_gradient_metadata(stage, pstate, normalized_config) -> Tuple[Lis
     """Descriptors (serialisable) and bindings (local tensors) of all parameters of `stage`."""
     manifest = normalized_config["manifest"]
     begin, end = pstate.op_range
-    if (stage.op_begin, stage.op_end) != (begin, end):
-        raise ValueError(f"stage owns ops [{stage.op_begin}, {stage.op_end}) but the topology says [{begin}, {end})")
+    want_ranges = [tuple(r) for r in getattr(pstate, "chunk_ranges", [(begin, end)])]
+    have_ranges = [tuple(r) for r in getattr(stage, "chunk_ranges", [(stage.op_begin, stage.op_end)])]
+    if have_ranges != want_ranges:
+        raise ValueError(f"stage owns ops {have_ranges} but the topology says {want_ranges}")
     for op in stage.ops:
         want = manifest["ordered_ops"][op.op_index]["name"]
         if op.name != want:

@@ -144,10 +144,14 @@ def run_batch(op_lists) -> None:
 class PipelineComm:
     """The four channels of a rank: activations in/out and gradients in/out."""
 
-    def __init__(self, pstate, hidden: int, seq_len: int, in_spec, out_spec, dtype, device, group=None):
+    def __init__(self, pstate, hidden: int, seq_len: int, in_spec, out_spec, dtype, device, group=None,
+                 neighbours=None):
+        """`neighbours`: (previous stage, next stage) topologies when they are not the adjacent
+        physical stages (interleaved pipelining wraps from the last stage to the first)."""
         self.pstate, self.dtype, self.device, self.seq_len, self.hidden = pstate, dtype, device, seq_len, hidden
         mbs = pstate.micro_batch_size
-        prev, nxt, me = pstate.neighbour(-1), pstate.neighbour(+1), pstate.stage
+        prev, nxt = neighbours if neighbours is not None else (pstate.neighbour(-1), pstate.neighbour(+1))
+        me = pstate.stage
         self.in_spec, self.out_spec = tuple(in_spec), tuple(out_spec)
         r = pstate.rank
         self.fwd_in = BoundaryChannel(r, plan_transfers(prev, me, in_spec, mbs, hidden), seq_len, group) if prev else None
@@ -211,3 +215,29 @@ class PipelineComm:
             if name not in out:
                 out[name] = need[name].zero_()
         return out
+
+
+def exchange(send_next=None, send_prev=None, recv_prev=None, recv_next=None):
+    """One batched call with up to four transfers of possibly different model chunks:
+        send_next = (comm, activations)   output of a chunk to the stage that runs the next virtual stage
+        send_prev = (comm, gradients)     input gradients of a chunk to the stage before it
+        recv_prev = comm                  inputs of that comm's chunk
+        recv_next = comm                  output gradients of that comm's chunk
+    always posted in this order. Every rank uses the same order, so two ranks that are each other's
+    previous AND next stage (a two-stage interleaved pipeline wraps around) pair their messages
+    correctly. Returns (received activations or None, received gradients or None)."""
+    batches, got_fwd, got_bwd = [], None, None
+    if send_next is not None and send_next[0].fwd_out is not None:
+        comm, tensors = send_next
+        batches.append(comm.fwd_out.make_ops(tensors, None))
+    if send_prev is not None and send_prev[0].bwd_out is not None:
+        comm, grads = send_prev
+        batches.append(comm.bwd_out.make_ops(comm._complete(grads, comm.in_spec), None))
+    if recv_prev is not None and recv_prev.fwd_in is not None:
+        got_fwd = recv_prev._buffers(recv_prev.in_spec)
+        batches.append(recv_prev.fwd_in.make_ops(None, got_fwd))
+    if recv_next is not None and recv_next.bwd_in is not None:
+        got_bwd = recv_next._buffers(recv_next.out_spec, grad=True)
+        batches.append(recv_next.bwd_in.make_ops(None, got_bwd))
+    run_batch(batches)
+    return got_fwd, got_bwd

@@ -179,8 +179,8 @@ def finalize_args(args, config=None):
     if args.bf16:
         args.accumulate_allreduce_grads_in_fp32 = True   # reference: arguments.py:268-277
     args.grad_dtype = torch.float32 if (args.accumulate_allreduce_grads_in_fp32 or not args.fp16) else torch.float16
-    if args.interleave_factor != 1:
-        raise NotImplementedError("interleaved 1F1B (--interleave-factor > 1) is not available; use 1")
+    if args.interleave_factor < 1:
+        raise ValueError("--interleave-factor must be >= 1")
 
     if args.prof_tp_size is not None:
         config = profiler_config(args)
@@ -195,6 +195,13 @@ def finalize_args(args, config=None):
         raise ValueError("the flash-attention path supports --attention-dropout 0 only "
                          "(the unfused 13-op manifest, model_impl gpt-legacy13, has an attention-dropout op)")
     args.canonical_topology = build_canonical_topology(normalized)
+    if args.interleave_factor > 1:
+        for i, p in enumerate(normalized["pipe"]):
+            n_mb = p["global_batch_size"] // p["micro_batch_size"]
+            if p["num_stages"] < 2 or n_mb % p["num_stages"]:
+                raise ValueError(f"--interleave-factor > 1 needs at least two stages and a number of micro-batches "
+                                 f"divisible by the number of stages (pipeline {i}: {p['num_stages']} stages, "
+                                 f"{n_mb} micro-batches)")
     max_tp = max(s.tp_degree for s in args.canonical_topology.stages)
     multiple = args.make_vocab_size_divisible_by * max_tp
     args.padded_vocab_size = (args.vocab_size + multiple - 1) // multiple * multiple

@@ -92,7 +92,8 @@ class TrainEngine:
         self.coll = collectives or Collectives(args.world_size)
         self.timers = Timers()
         cfg = args.normalized_config
-        self.pstate = ParallelState(cfg, args.rank, self.coll.create_group, topology=args.canonical_topology)
+        self.pstate = ParallelState(cfg, args.rank, self.coll.create_group, topology=args.canonical_topology,
+                                    interleave=getattr(args, "interleave_factor", 1))
         ps = self.pstate
         self.model_cfg = GPTModelConfig(
             num_layers=cfg["num_layers"], hidden_size=cfg["hidden_size"],
@@ -106,11 +107,20 @@ class TrainEngine:
             model_impl=cfg.get("model_impl", "gpt"), attention_dropout=getattr(args, "attention_dropout", 0.0) or 0.0)
         self.tp = self._make_tp_comm()
         begin, end = ps.op_range
+        chunks = ps.chunk_ranges if ps.interleave > 1 else None
         self.stage = GPTStage(self.model_cfg, begin, end, tp=self.tp, device=self.device,
-                              recompute_ops=ps.recompute_ops)
+                              recompute_ops=ps.recompute_ops, chunks=chunks)
         self.seq_len = cfg["seq_length"]
         self.comm = PipelineComm(ps, cfg["hidden_size"], self.seq_len, self.stage.input_spec, self.stage.output_spec,
                                  args.params_dtype, self.device) if ps.num_stages > 1 else None
+        # interleaved pipelining: one set of channels per model chunk, wired to the stage that holds
+        # the previous / next virtual stage
+        self.chunk_comms = None
+        if ps.interleave > 1:
+            self.chunk_comms = [
+                PipelineComm(ps, cfg["hidden_size"], self.seq_len, spec_in, spec_out, args.params_dtype, self.device,
+                             neighbours=(ps.chunk_neighbour(c, -1), ps.chunk_neighbour(c, +1)))
+                for c, (spec_in, spec_out) in enumerate(self.stage.chunk_specs)]
         self.data_provider = data_provider
         self.clock = TrainingClock(total_gbs=args.total_gbs)
         self.iteration = 0
@@ -289,38 +299,40 @@ class TrainEngine:
         return tokens, labels, mask
 
     # ------------------------------------------------------------------ steps used by the schedules
-    def forward_step(self, mb_index: int, inputs: Optional[Dict[str, torch.Tensor]]):
+    def forward_step(self, mb_index: int, inputs: Optional[Dict[str, torch.Tensor]], chunk: int = 0):
         ps = self.pstate
         seq = self.args.mbs_seq[ps.pipeline_id][mb_index][1]
         mb = MicroBatch(index=mb_index, batch=ps.local_micro_batch, seq=seq, global_step=self.iteration,
                         dp_rank=ps.dp_rank)
         env = dict(inputs) if inputs else {}
-        if ps.is_first_stage or ps.is_last_stage:
+        first, last = ps.is_first_virtual(chunk), ps.is_last_virtual(chunk)
+        if first or last:
             tokens, labels, mask = self.get_batch(mb_index)
-            if ps.is_first_stage:
+            if first:
                 env["enc_input_ids"] = tokens
-            if ps.is_last_stage:
+            if last:
                 env["labels"] = labels
                 mb.loss_mask = mask.reshape(-1)
-        out = self.stage.forward(mb, env)
-        if ps.is_last_stage:
+        out = self.stage.forward(mb, env, chunk)
+        if last:
             losses = out.pop("output")
             if ps.tp_rank == 0:   # TP peers hold identical losses; count them once
                 self.loss_acc[0] += torch.dot(losses, mb.loss_mask)
                 self.loss_acc[1] += mb.loss_mask.sum()
         return out
 
-    def backward_step(self, mb_index: int, grad_outputs: Optional[Dict[str, torch.Tensor]]):
+    def backward_step(self, mb_index: int, grad_outputs: Optional[Dict[str, torch.Tensor]], chunk: int = 0):
         ps = self.pstate
-        if ps.is_last_stage:
-            rec = self.stage._contexts[mb_index]["mb"]
+        if ps.is_last_virtual(chunk):
+            rec = self.stage.context_of(mb_index, chunk)["mb"]
             scale = self.scaler.value() if self.scaler is not None else 1.0
             grad_outputs = {"output": rec.loss_mask * (scale / self.args.nominal_global_loss_scale)}
-        last = self._sync_stream is not None and mb_index == self.pstate.num_microbatches - 1
+        # start reductions during the very last backward of the iteration (chunk 0 runs last when interleaved)
+        last = self._sync_stream is not None and mb_index == self.pstate.num_microbatches - 1 and ps.interleave == 1
         if last:
             self.stage.after_op_backward = self._reduce_ready_buckets
         try:
-            return self.stage.backward(mb_index, grad_outputs or {})
+            return self.stage.backward(mb_index, grad_outputs or {}, chunk)
         finally:
             if last:
                 self.stage.after_op_backward = None
@@ -338,6 +350,8 @@ class TrainEngine:
         n_mb = self.pstate.num_microbatches
         if self.pstate.num_stages == 1:
             schedules.forward_backward_no_pipelining(self, n_mb)
+        elif self.pstate.interleave > 1:
+            schedules.forward_backward_interleaved(self, n_mb)
         else:
             schedules.forward_backward_1f1b(self, n_mb)
         raw_ops.join_async_wgrad(self.device)

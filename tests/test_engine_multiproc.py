@@ -100,3 +100,49 @@ def test_block_mode_issues_fewer_collectives_than_tensor_mode():
     assert block[0]["collectives"] < tensor[0]["collectives"]
     for (a, b) in zip(block[0]["shards"], tensor[0]["shards"]):
         assert torch.allclose(a[-1], b[-1], atol=1e-6)
+
+
+# ------------------------------------------------------------------ interleaved 1F1B
+def _train_interleaved(rank, world, config, steps, factor):
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+    argv = ["--hidden-dropout", "0.0", "--device", "cpu", "--vocab-size", str(VOCAB),
+            "--make-vocab-size-divisible-by", "8", "--lr", "1e-2", "--lr-warmup-fraction", "0.0",
+            "--lr-decay-style", "constant", "--grad-sync-mode", "block", "--grad-sync-bucket-size-mb", "1",
+            "--distributed-backend", "gloo", "--interleave-factor", str(factor)]
+    args = parse_args(argv, config=config, rank=rank, world_size=world)
+    eng = TrainEngine(args, device="cpu")
+    losses, norms = [], []
+    for _ in range(steps):
+        st = eng.train_step()
+        losses.append(eng.reduced_loss())
+        norms.append(st["grad_norm"])
+    params = {lid: p.detach().clone() for lid, p in eng.stage.named_parameters()}
+    return {"losses": losses, "norms": norms, "params": params, "chunks": eng.stage.chunk_ranges}
+
+
+@pytest.mark.parametrize("name,world,stage_ops,factor,gbs,mbs", [
+    ("pp2-v2", 2, [11, N_OPS - 11], 2, 8, 2),           # 4 micro-batches, chunks cut inside the layers
+    ("pp2-v2-all-warmup", 2, [11, N_OPS - 11], 2, 4, 2),  # micro-batches == stages: no steady phase
+    ("pp3-v2", 3, [7, 7, N_OPS - 14], 2, 12, 2),        # 6 micro-batches, uneven op-granular chunks
+])
+def test_interleaved_schedule_matches_single_rank(name, world, stage_ops, factor, gbs, mbs):
+    single = run_ranks(1, _train_interleaved, _config([make_pipe([N_OPS], [1], [1], gbs=gbs, mbs=mbs)]), 2, 1)[0]
+    pipe = make_pipe(stage_ops, [1] * world, [1] * world, gbs=gbs, mbs=mbs)
+    results = run_ranks(world, _train_interleaved, _config([pipe]), 2, factor)
+    # every rank holds `factor` chunks and together they cover the model exactly once, in virtual-stage order
+    ranges = sorted(r for res in results for r in res["chunks"])
+    assert all(len(res["chunks"]) == factor for res in results)
+    assert ranges[0][0] == 0 and ranges[-1][1] == N_OPS and all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+    virtual = [results[s]["chunks"][c] for c in range(factor) for s in range(world)]
+    assert virtual == ranges
+    merged = {}
+    for res in results:
+        merged.update(res["params"])
+    for lid, ref in single["params"].items():
+        err = (merged[lid] - ref).norm() / (ref.norm() + 1e-12)
+        assert err < 2e-4, (name, lid, float(err))
+    for a, b in zip(results[-1]["losses"], single["losses"]):
+        assert abs(a - b) < 1e-4
+    for a, b in zip(results[0]["norms"], single["norms"]):
+        assert abs(a - b) / b < 1e-3
