@@ -219,7 +219,7 @@ int64_t ln_bwd_parts(int64_t rows, int64_t hidden, bool fp32) {
 }
 void layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const Tensor& mean,
                    const Tensor& rstd, Tensor& dx, Tensor& dgamma, Tensor& dbeta, Tensor& ws,
-                   bool accumulate, const c10::optional<Tensor>& dres) {
+                   bool accumulate, const c10::optional<Tensor>& dres, int64_t ws_mode) {
   c10::cuda::CUDAGuard guard(x.device());
   const int hidden = static_cast<int>(x.size(-1));
   const int rows = static_cast<int>(x.numel() / hidden);
@@ -233,7 +233,7 @@ void layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const
   check(ethb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr<float>(),
                             rstd.data_ptr<float>(), res, dx.data_ptr(), dgamma.data_ptr(),
                             dbeta.data_ptr(), ws.data_ptr<float>(), rows, hidden, dtype_code(x),
-                            dtype_code(dgamma), accumulate, cur_stream()),
+                            dtype_code(dgamma), accumulate, cur_stream(), static_cast<int>(ws_mode)),
         "layernorm_bwd");
 }
 
@@ -270,7 +270,7 @@ int64_t dropout_bwd_colsum_parts(int64_t rows, int64_t cols, bool fp32) {
   return ethb::dropout_bwd_colsum_parts(rows, static_cast<int>(cols), fp32 ? 0 : 2);
 }
 void dropout_bwd_colsum(const Tensor& dy, Tensor& dx, Tensor& bias_grad, Tensor& ws, double p, int64_t seed,
-                        int64_t offset, bool accumulate) {
+                        int64_t offset, bool accumulate, int64_t ws_mode) {
   c10::cuda::CUDAGuard guard(dy.device());
   const int cols = static_cast<int>(dy.size(-1));
   const int64_t rows = dy.numel() / cols;
@@ -281,7 +281,7 @@ void dropout_bwd_colsum(const Tensor& dy, Tensor& dx, Tensor& bias_grad, Tensor&
   check(ethb::dropout_bwd_colsum(dy.data_ptr(), dx.data_ptr(), bias_grad.data_ptr(), ws.data_ptr<float>(), rows,
                                  cols, static_cast<float>(p), static_cast<uint64_t>(seed),
                                  static_cast<uint64_t>(offset), dtype_code(dy), dtype_code(bias_grad),
-                                 accumulate, cur_stream()),
+                                 accumulate, cur_stream(), static_cast<int>(ws_mode)),
         "dropout_bwd_colsum");
 }
 int64_t colsum_parts(int64_t rows) { return ethb::colsum_parts(rows); }
@@ -564,16 +564,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_allgather", &gemm_allgather);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("ln_bwd_parts", &ln_bwd_parts);
+  m.def("ln_bwd_fused_ok", [](int64_t hidden, bool fp32) {
+    return ethb::ln_bwd_fused_ok(static_cast<int>(hidden), fp32 ? 0 : 2);
+  });
   m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"),
         py::arg("rstd"), py::arg("dx"), py::arg("dgamma"), py::arg("dbeta"), py::arg("ws"), py::arg("accumulate"),
-        py::arg("dres") = py::none());
+        py::arg("dres") = py::none(), py::arg("ws_mode") = 0);
   m.def("bias_gelu_fwd", &bias_gelu_fwd);
   m.def("bias_gelu_bwd", &bias_gelu_bwd);
   m.def("bias_dropout_add_fwd", &bias_dropout_add_fwd);
   m.def("dropout_bwd", &dropout_bwd);
   m.def("colsum_parts", &colsum_parts);
   m.def("dropout_bwd_colsum_parts", &dropout_bwd_colsum_parts);
-  m.def("dropout_bwd_colsum", &dropout_bwd_colsum);
+  m.def("dropout_bwd_colsum", &dropout_bwd_colsum, py::arg("dy"), py::arg("dx"), py::arg("bias_grad"), py::arg("ws"),
+        py::arg("p"), py::arg("seed"), py::arg("offset"), py::arg("accumulate"), py::arg("ws_mode") = 0);
   m.def("colsum", &colsum);
   m.def("softmax_fwd", &softmax_fwd);
   m.def("softmax_bwd", &softmax_bwd);

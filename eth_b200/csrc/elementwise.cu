@@ -54,6 +54,30 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
+// Eight elements as they sit in memory: 4 registers for 16-bit types, 8 for fp32.
+template <typename T, int N>
+__device__ __forceinline__ void load_raw8(const T* p, float (&raw)[N]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    raw[0] = __uint_as_float(u.x); raw[1] = __uint_as_float(u.y);
+    raw[2] = __uint_as_float(u.z); raw[3] = __uint_as_float(u.w);
+  } else {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    raw[0] = a.x; raw[1] = a.y; raw[2] = a.z; raw[3] = a.w;
+    raw[4] = b.x; raw[5] = b.y; raw[6] = b.z; raw[7] = b.w;
+  }
+}
+template <typename T, int N>
+__device__ __forceinline__ void unpack_raw8(const float (&raw)[N], float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    unpack8<T>(make_uint4(__float_as_uint(raw[0]), __float_as_uint(raw[1]), __float_as_uint(raw[2]),
+                          __float_as_uint(raw[3])), f);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) f[q] = raw[q];
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -143,6 +167,59 @@ __global__ void ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gam
   }
 }
 
+// Warp-per-row forward for 16-bit rows of 256 * VPL elements (VPL <= 16). A lane keeps VPL 16-byte
+// pieces of the row packed in registers (lane l owns pieces l, l + 32, ...: a warp reads 512
+// contiguous bytes per instruction), so mean and variance need only warp shuffles: no block barrier
+// sits between a row's load and its store, and with 8 independent warps per CTA the loads of some
+// rows always overlap the arithmetic of others. gamma / beta (a few KB) are re-read per row: they stay
+// in L1, and keeping them out of the register file lets two CTAs (16 warps) share an SM.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(256, VPL > 8 ? 1 : 2)
+ln_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                   T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows,
+                   float eps) {
+  constexpr int kHidden = VPL * 256;
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  for (int row = warp; row < rows; row += nwarps) {
+    const T* xr = x + static_cast<int64_t>(row) * kHidden;
+    uint4 raw[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) raw[i] = *reinterpret_cast<const uint4*>(xr + (lane + 32 * i) * 8);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float v[8];
+      unpack8<T>(raw[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[j];
+    }
+    const float mu = warp_sum(s) * (1.0f / kHidden);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float v[8];
+      unpack8<T>(raw[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float d = v[j] - mu; q += d * d; }
+    }
+    const float rs = rsqrtf(warp_sum(q) * (1.0f / kHidden) + eps);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+    T* yr = y + static_cast<int64_t>(row) * kHidden;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float v[8], gv[8], bv[8], o[8];
+      unpack8<T>(raw[i], v);
+      load8(gamma + (lane + 32 * i) * 8, gv);
+      load8(beta + (lane + 32 * i) * 8, bv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[j] - mu) * rs * gv[j] + bv[j];
+      store8(yr + (lane + 32 * i) * 8, o);
+    }
+  }
+}
+
 // Backward. One pass over dy and x: thread t of a CTA owns columns [8t, 8t + 8) of every row the CTA
 // visits (blockDim.x = hidden / 8), so the dgamma / dbeta column sums stay in registers for the
 // whole kernel and dx needs only two block-wide reductions per batch of R rows (sum(dy*gamma) and
@@ -150,11 +227,11 @@ __global__ void ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gam
 // reduction and the dx pass. Each CTA writes one slab of partial column sums; reduce_parts_kernel
 // adds the slabs. Rows wider than 8192 elements use the two-kernel fallback below.
 template <typename T, int R>
-__global__ void __launch_bounds__(R == 4 ? 512 : 1024, R == 4 ? 2 : 1)
+__global__ void __launch_bounds__(R == 5 ? 256 : (R == 4 ? 512 : 1024), R == 5 ? 2 : 1)
 ln_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                     const float* __restrict__ mean, const float* __restrict__ rstd,
                     const T* __restrict__ dres, T* __restrict__ dx, float* __restrict__ ws, int rows,
-                    int hidden) {
+                    int hidden, int add_to_ws) {
   __shared__ float red[2][R][32];
   __shared__ float tot[2][R];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
@@ -163,21 +240,21 @@ ln_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* 
   load8(gamma + c0, g);
   float dg[8] = {0, 0, 0, 0, 0, 0, 0, 0}, db[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   for (int r0 = blockIdx.x * R; r0 < rows; r0 += gridDim.x * R) {
-    uint4 xr[R], dyr[R];
-    float mu[R], rs[R];
+    // everything a batch needs from memory is requested up front (the residual gradient too): one
+    // memory latency per batch, R * 3 independent 16-byte loads per thread in flight
+    uint4 xr[R], dyr[R], rr[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const int r = r0 + i;
       if (r < rows) {
         xr[i] = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(r) * hidden + c0);
         dyr[i] = *reinterpret_cast<const uint4*>(dy + static_cast<int64_t>(r) * hidden + c0);
-        mu[i] = mean[r];
-        rs[i] = rstd[r];
+        rr[i] = dres != nullptr ? *reinterpret_cast<const uint4*>(dres + static_cast<int64_t>(r) * hidden + c0)
+                                : make_uint4(0, 0, 0, 0);
       } else {
         xr[i] = make_uint4(0, 0, 0, 0);
         dyr[i] = make_uint4(0, 0, 0, 0);
-        mu[i] = 0.f;
-        rs[i] = 0.f;
+        rr[i] = make_uint4(0, 0, 0, 0);
       }
     }
 #pragma unroll
@@ -185,12 +262,14 @@ ln_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* 
       float xv[8], dv[8];
       unpack8<T>(xr[i], xv);
       unpack8<T>(dyr[i], dv);
+      // per-row statistics are re-read where they are used (broadcast loads, L1 hits)
+      const float mu_i = r0 + i < rows ? mean[r0 + i] : 0.f, rs_i = r0 + i < rows ? rstd[r0 + i] : 0.f;
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float w = dv[j] * g[j];
         s1 += w;
-        s2 += w * (xv[j] - mu[i]) * rs[i];
+        s2 += w * (xv[j] - mu_i) * rs_i;
       }
       s1 = warp_sum(s1);
       s2 = warp_sum(s2);
@@ -211,20 +290,26 @@ ln_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* 
     for (int i = 0; i < R; ++i) {
       const int r = r0 + i;
       if (r >= rows) break;
+      // The rows are unpacked again here on purpose: carrying R * 16 floats across the barrier
+      // instead of R * 8 packed registers would spill. The empty asm hides the packed values'
+      // provenance from the optimiser so that it cannot reuse the first unpacking.
+      asm volatile("" : "+r"(xr[i].x), "+r"(xr[i].y), "+r"(xr[i].z), "+r"(xr[i].w));
+      asm volatile("" : "+r"(dyr[i].x), "+r"(dyr[i].y), "+r"(dyr[i].z), "+r"(dyr[i].w));
       float xv[8], dv[8], o[8];
       unpack8<T>(xr[i], xv);
       unpack8<T>(dyr[i], dv);
       const float m1 = tot[0][i], m2 = tot[1][i];
+      const float mu_i = mean[r], rs_i = rstd[r];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float xh = (xv[j] - mu[i]) * rs[i];
-        o[j] = (dv[j] * g[j] - m1 - xh * m2) * rs[i];
+        const float xh = (xv[j] - mu_i) * rs_i;
+        o[j] = (dv[j] * g[j] - m1 - xh * m2) * rs_i;
         dg[j] += dv[j] * xh;
         db[j] += dv[j];
       }
       if (dres != nullptr) {   // gradient arriving through the residual branch
         float rv[8];
-        load8(dres + static_cast<int64_t>(r) * hidden + c0, rv);
+        unpack8<T>(rr[i], rv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] += rv[j];
       }
@@ -233,6 +318,14 @@ ln_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* 
   }
   float* wg = ws + static_cast<int64_t>(blockIdx.x) * hidden + c0;
   float* wb = ws + static_cast<int64_t>(gridDim.x + blockIdx.x) * hidden + c0;
+  if (add_to_ws) {   // the slabs persist over micro-batches and are reduced once per step
+    const float4 a0 = reinterpret_cast<const float4*>(wg)[0], a1 = reinterpret_cast<const float4*>(wg)[1];
+    const float4 b0 = reinterpret_cast<const float4*>(wb)[0], b1 = reinterpret_cast<const float4*>(wb)[1];
+    dg[0] += a0.x; dg[1] += a0.y; dg[2] += a0.z; dg[3] += a0.w;
+    dg[4] += a1.x; dg[5] += a1.y; dg[6] += a1.z; dg[7] += a1.w;
+    db[0] += b0.x; db[1] += b0.y; db[2] += b0.z; db[3] += b0.w;
+    db[4] += b1.x; db[5] += b1.y; db[6] += b1.z; db[7] += b1.w;
+  }
   *reinterpret_cast<float4*>(wg) = make_float4(dg[0], dg[1], dg[2], dg[3]);
   *reinterpret_cast<float4*>(wg + 4) = make_float4(dg[4], dg[5], dg[6], dg[7]);
   *reinterpret_cast<float4*>(wb) = make_float4(db[0], db[1], db[2], db[3]);
@@ -335,8 +428,8 @@ __global__ void ln_bwd_param_kernel(const T* __restrict__ dy, const T* __restric
 // out[c] (+)= sum_p ws[p, c]   for two stacked workspaces (dgamma | dbeta) or one (colsum).
 // CTA = 32 columns x 8 part-lanes: each thread adds every 8th slab, shared memory adds the lanes.
 template <typename G>
-__global__ void reduce_parts_kernel(const float* __restrict__ ws, G* __restrict__ out0,
-                                    G* __restrict__ out1, int parts, int cols, int accumulate) {
+__global__ void reduce_parts_kernel(float* __restrict__ ws, G* __restrict__ out0,
+                                    G* __restrict__ out1, int parts, int cols, int accumulate, int clear = 0) {
   __shared__ float sa[8][33], sb[8][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
@@ -344,6 +437,10 @@ __global__ void reduce_parts_kernel(const float* __restrict__ ws, G* __restrict_
     for (int p = threadIdx.y; p < parts; p += 8) {
       a += ws[static_cast<int64_t>(p) * cols + c];
       if (out1) b += ws[static_cast<int64_t>(parts + p) * cols + c];
+      if (clear) {   // persistent slabs start the next step from zero
+        ws[static_cast<int64_t>(p) * cols + c] = 0.f;
+        if (out1) ws[static_cast<int64_t>(parts + p) * cols + c] = 0.f;
+      }
     }
   }
   sa[threadIdx.y][threadIdx.x] = a;
@@ -429,21 +526,45 @@ __global__ void bias_dropout_add_kernel(const T* __restrict__ x, const T* __rest
                                         int64_t nvec, int cvec, float p, uint64_t seed,
                                         uint64_t offset) {
   const float inv_keep = p > 0.f ? 1.0f / (1.0f - p) : 1.0f;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float a[8], b[8], r[8], o[8];
-    load8(x + i * 8, a);
-    if (bias) load8(bias + (i % cvec) * 8, b);
-    if (residual) load8(residual + i * 8, r);
-    bool keep[8];
-    if (p > 0.f) keep8(seed, offset, i, p, keep);
+  constexpr int kVecRegs = sizeof(T) == 2 ? 4 : 8;
+  // U vectors per thread and step: all loads of a step are issued before any arithmetic, so a
+  // thread has 2 * U independent 16-byte requests in flight instead of two
+  constexpr int U = 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // column of vector i0 and its advance per vector, kept incrementally: a 64-bit `i % cvec` per
+  // vector would cost more instructions than the rest of the loop body
+  const int col_step = static_cast<int>(stride % cvec);
+  int col0 = static_cast<int>((blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) % cvec);
+  for (int64_t i0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    float a[U][kVecRegs], r[U][kVecRegs];      // kept as loaded (packed for 16-bit types)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float v = a[j] + (bias ? b[j] : 0.f);
-      if (p > 0.f) v = keep[j] ? v * inv_keep : 0.f;
-      o[j] = v + (residual ? r[j] : 0.f);
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < nvec) {
+        load_raw8(x + i * 8, a[u]);
+        if (residual) load_raw8(residual + i * 8, r[u]);
+      }
     }
-    store8(out + i * 8, o);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i >= nvec) break;
+      float av[8], rv[8], b[8], o[8];
+      unpack_raw8<T>(a[u], av);
+      if (residual) unpack_raw8<T>(r[u], rv);
+      if (bias) load8(bias + col0 * 8, b);
+      col0 += col_step;
+      if (col0 >= cvec) col0 -= cvec;
+      bool keep[8];
+      if (p > 0.f) keep8(seed, offset, i, p, keep);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v = av[j] + (bias ? b[j] : 0.f);
+        if (p > 0.f) v = keep[j] ? v * inv_keep : 0.f;
+        o[j] = v + (residual ? rv[j] : 0.f);
+      }
+      store8(out + i * 8, o);
+    }
   }
 }
 template <typename T>
@@ -468,12 +589,12 @@ __global__ void dropout_bwd_kernel(const T* __restrict__ dy, T* __restrict__ dx,
 template <typename T>
 __global__ void dropout_bwd_colsum_kernel(const T* __restrict__ dy, T* __restrict__ dx,
                                           float* __restrict__ ws, int64_t rows, int cols, float p,
-                                          uint64_t seed, uint64_t offset) {
+                                          uint64_t seed, uint64_t offset, int add_to_ws) {
   const float inv_keep = 1.0f / (1.0f - p);
   const int cvec = cols >> 3;
   const int t = threadIdx.x;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  constexpr int U = 4;
+  constexpr int U = 8;
   for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * U; r0 < rows; r0 += static_cast<int64_t>(gridDim.x) * U) {
     uint4 raw[U];
 #pragma unroll
@@ -496,6 +617,11 @@ __global__ void dropout_bwd_colsum_kernel(const T* __restrict__ dy, T* __restric
     }
   }
   float* w = ws + static_cast<int64_t>(blockIdx.x) * cols + t * 8;
+  if (add_to_ws) {
+    const float4 a0 = reinterpret_cast<const float4*>(w)[0], a1 = reinterpret_cast<const float4*>(w)[1];
+    acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
+    acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
+  }
   *reinterpret_cast<float4*>(w) = make_float4(acc[0], acc[1], acc[2], acc[3]);
   *reinterpret_cast<float4*>(w + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
@@ -877,6 +1003,28 @@ cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, vo
                           float* mean, float* rstd, int rows, int hidden, float eps, int dtype,
                           cudaStream_t st) {
   if (hidden % 8 != 0 || hidden / 8 > 4 * 1024) return cudaErrorInvalidValue;
+  if (dtype != kF32 && hidden % 256 == 0 && hidden / 256 <= 16 && hidden / 256 >= 1) {
+    // warp per row, 8 warps per CTA; one row per warp, so the block scheduler balances the SMs
+    const int grid = (rows + 7) / 8;
+#define ETHB_LN_WARP(V)                                                                          \
+  case V:                                                                                         \
+    if (dtype == kBF16)                                                                           \
+      ln_fwd_warp_kernel<__nv_bfloat16, V><<<grid, 256, 0, st>>>(                                 \
+          (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta,       \
+          (__nv_bfloat16*)y, mean, rstd, rows, eps);                                              \
+    else                                                                                          \
+      ln_fwd_warp_kernel<__half, V><<<grid, 256, 0, st>>>((const __half*)x, (const __half*)gamma, \
+                                                          (const __half*)beta, (__half*)y, mean,  \
+                                                          rstd, rows, eps);                       \
+    count_launch();                                                                               \
+    return cudaGetLastError();
+    switch (hidden / 256) {
+      ETHB_LN_WARP(1) ETHB_LN_WARP(2) ETHB_LN_WARP(3) ETHB_LN_WARP(4) ETHB_LN_WARP(5) ETHB_LN_WARP(6)
+      ETHB_LN_WARP(8) ETHB_LN_WARP(10) ETHB_LN_WARP(12) ETHB_LN_WARP(16)
+      default: break;   // other widths: the CTA-per-row kernel below
+    }
+#undef ETHB_LN_WARP
+  }
   int iters, threads;
   ln_shape(hidden, iters, threads);
   const int grid = rows < kSMs * 16 ? rows : kSMs * 16;
@@ -892,9 +1040,9 @@ cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, vo
 // a CTA of hidden / 8 threads.
 static int ln_bwd_rows_per_batch(int hidden) {
   const int threads = hidden / 8;
-  return threads <= 512 ? 4 : 2;
+  return threads <= 256 ? 5 : (threads <= 512 ? 4 : 2);
 }
-static bool ln_bwd_fused_ok(int hidden, int dtype) {
+bool ln_bwd_fused_ok(int hidden, int dtype) {
   return dtype != kF32 && hidden % 256 == 0 && hidden <= 8192;
 }
 
@@ -902,7 +1050,7 @@ int ln_bwd_parts(int rows, int hidden, int dtype) {
   if (ln_bwd_fused_ok(hidden, dtype)) {
     const int r = ln_bwd_rows_per_batch(hidden);
     const int threads = hidden / 8;
-    const int per_sm = threads <= 256 ? 4 : (threads <= 512 ? 2 : 1);
+    const int per_sm = threads <= 256 ? 2 : 1;
     int p = (rows + r - 1) / r;
     if (p > kSMs * per_sm) p = kSMs * per_sm;
     return p < 1 ? 1 : p;
@@ -916,8 +1064,9 @@ int ln_bwd_parts(int rows, int hidden, int dtype) {
 cudaError_t layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
                           float* ws, int rows, int hidden, int dtype, int grad_dtype, int accumulate,
-                          cudaStream_t st) {
+                          cudaStream_t st, int ws_mode) {
   if (hidden % 8 != 0 || hidden / 8 > 4 * 1024) return cudaErrorInvalidValue;
+  if (ws_mode != kWsImmediate && !ln_bwd_fused_ok(hidden, dtype)) return cudaErrorInvalidValue;
   const int parts = ln_bwd_parts(rows, hidden, dtype);
   dim3 rgrid((hidden + 31) / 32), rblock(32, 8);
   if (ln_bwd_fused_ok(hidden, dtype)) {
@@ -927,12 +1076,16 @@ cudaError_t layernorm_bwd(const void* dy, const void* x, const void* gamma, cons
   ETHB_DISPATCH(dtype, T,                                                                           \
                 (ln_bwd_fused_kernel<T, R><<<parts, threads, 0, st>>>(                              \
                     (const T*)dy, (const T*)x, (const T*)gamma, mean, rstd, (const T*)dres, (T*)dx, ws, rows, \
-                    hidden)))
-    if (r == 4) { ETHB_LN_BWD(4); } else { ETHB_LN_BWD(2); }
+                    hidden, ws_mode != kWsImmediate)))
+    if (r == 5) { ETHB_LN_BWD(5); } else if (r == 4) { ETHB_LN_BWD(4); } else { ETHB_LN_BWD(2); }
 #undef ETHB_LN_BWD
+    if (ws_mode == kWsAccumulate) {   // the column sums stay in the slabs until a later call flushes them
+      count_launch();
+      return cudaGetLastError();
+    }
     ETHB_DISPATCH(grad_dtype, G,
                   (reduce_parts_kernel<G><<<rgrid, rblock, 0, st>>>(ws, (G*)dgamma, (G*)dbeta, parts, hidden,
-                                                                    accumulate)));
+                                                                    accumulate, ws_mode == kWsFlush)));
     count_launch(2);
     return cudaGetLastError();
   }
@@ -1000,22 +1153,26 @@ cudaError_t dropout_bwd(const void* dy, void* dx, int64_t rows, int cols, float 
 
 int dropout_bwd_colsum_parts(int64_t rows, int cols, int dtype) {
   if (dtype == kF32 || cols % 256 != 0 || cols > 8192) return 0;   // not fusable: use the separate kernels
-  int64_t p = (rows + 3) / 4;
+  int64_t p = (rows + 7) / 8;
   const int cap = kSMs * (cols / 8 <= 256 ? 4 : (cols / 8 <= 512 ? 2 : 1));
   if (p > cap) p = cap;
   return static_cast<int>(p < 1 ? 1 : p);
 }
 cudaError_t dropout_bwd_colsum(const void* dy, void* dx, void* bias_grad, float* ws, int64_t rows,
                                int cols, float p, uint64_t seed, uint64_t offset, int dtype,
-                               int grad_dtype, int accumulate, cudaStream_t st) {
+                               int grad_dtype, int accumulate, cudaStream_t st, int ws_mode) {
   const int parts = dropout_bwd_colsum_parts(rows, cols, dtype);
   if (parts <= 0) return cudaErrorInvalidValue;
   ETHB_DISPATCH(dtype, T,
                 (dropout_bwd_colsum_kernel<T><<<parts, cols / 8, 0, st>>>((const T*)dy, (T*)dx, ws, rows, cols,
-                                                                         p, seed, offset)));
+                                                                         p, seed, offset, ws_mode != kWsImmediate)));
+  if (ws_mode == kWsAccumulate) {
+    count_launch();
+    return cudaGetLastError();
+  }
   ETHB_DISPATCH(grad_dtype, G,
                 (reduce_parts_kernel<G><<<dim3((cols + 31) / 32), dim3(32, 8), 0, st>>>(
-                    ws, (G*)bias_grad, (G*)nullptr, parts, cols, accumulate)));
+                    ws, (G*)bias_grad, (G*)nullptr, parts, cols, accumulate, ws_mode == kWsFlush)));
   count_launch(2);
   return cudaGetLastError();
 }

@@ -11,15 +11,26 @@ namespace ethb {
 cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
                           float* mean, float* rstd, int rows, int hidden, float eps, int dtype,
                           cudaStream_t st);
+// What happens to the per-CTA partial column sums ("slabs") that a kernel leaves in its workspace:
+//   kWsImmediate   slabs are overwritten and summed into the output by a second launch right away;
+//   kWsAccumulate  the kernel ADDS its partials to the slabs and nothing else happens: the caller
+//                  keeps one zero-initialised workspace per op across the micro-batches of a step,
+//                  which takes the second launch off the critical path of every backward;
+//   kWsFlush       as kWsAccumulate, then the slabs are summed into the output and cleared
+//                  (the last micro-batch of a step).
+enum WorkspaceMode : int { kWsImmediate = 0, kWsAccumulate = 1, kWsFlush = 2 };
+
 // Workspace: `ws` holds 2 * ln_bwd_parts(rows, hidden, dtype) * hidden floats (partial dgamma |
 // partial dbeta).
 int ln_bwd_parts(int rows, int hidden, int dtype);
+// Whether the one-kernel backward (and with it kWsAccumulate / kWsFlush) handles this width and type.
+bool ln_bwd_fused_ok(int hidden, int dtype);
 // `dres` (may be null): a gradient of the same shape that is added to dx, i.e. the gradient that
 // reaches the LayerNorm input through the residual branch.
 cudaError_t layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
                           float* ws, int rows, int hidden, int dtype, int grad_dtype, int accumulate,
-                          cudaStream_t st);
+                          cudaStream_t st, int ws_mode = kWsImmediate);
 
 // ---- bias + GeLU(tanh) ----------------------------------------------------------------------
 cudaError_t bias_gelu_fwd(const void* x, const void* bias, void* y, int64_t rows, int cols,
@@ -40,7 +51,7 @@ cudaError_t dropout_bwd(const void* dy, void* dx, int64_t rows, int cols, float 
 int dropout_bwd_colsum_parts(int64_t rows, int cols, int dtype);
 cudaError_t dropout_bwd_colsum(const void* dy, void* dx, void* bias_grad, float* ws, int64_t rows,
                                int cols, float p, uint64_t seed, uint64_t offset, int dtype,
-                               int grad_dtype, int accumulate, cudaStream_t st);
+                               int grad_dtype, int accumulate, cudaStream_t st, int ws_mode = kWsImmediate);
 
 // ---- column sums: out[c] (+)= sum_r x[r, c]  (bias gradients) -----------------------------
 // Workspace: colsum_parts(rows) * cols floats.

@@ -159,6 +159,7 @@ class Op:
         self.params: Dict[str, torch.Tensor] = {}
         self.fuse_next = False   # set by the stage builder when the following op is fused into this one
         self.fuse_prev = False
+        self.slabs = raw.ColumnSumSlabs()   # used by ops whose backward leaves partial column sums
 
     def specs(self) -> List[ParamSpec]:
         return []
@@ -264,7 +265,8 @@ class LayerNormOp(Op):
         dy = _take(genv, "hidden_states")
         res = genv.pop(self.residual_name, None) if self.residual_name else None
         genv["hidden_states"] = raw.ln_bwd(dy, ctx["x"], self.p("weight"), self.p("bias"), ctx["mean"],
-                                           ctx["rstd"], residual_grad=res)
+                                           ctx["rstd"], residual_grad=res, slabs=self.slabs,
+                                           ws_mode=getattr(mb, "colsum_mode", raw.WS_IMMEDIATE))
 
 
 class ColumnLinearOp(Op):
@@ -445,13 +447,23 @@ class BiasDropoutAddOp(Op):
         x, bias, res = env["hidden_states"], env.pop("output_bias"), env.pop(self.residual_name)
         p = self.cfg.hidden_dropout
         ctx["drop"] = (p, self.cfg.seed + self.op_index, self.dropout_offset(mb))
+        ctx["bias"] = bias
         env["hidden_states"] = raw.bias_dropout_add_fwd(x, bias, res, *ctx["drop"])
 
     def bwd(self, genv, ctx, mb):
         dout = _take(genv, "hidden_states")
+        genv[self.residual_name] = dout
+        mode = getattr(mb, "colsum_mode", raw.WS_IMMEDIATE)
+        bias = ctx.get("bias")
+        if mode != raw.WS_IMMEDIATE and bias is not None and getattr(bias, "main_grad", None) is not None:
+            # the bias is a parameter of this rank: its gradient goes straight to main_grad, through
+            # this op's own slabs, once per step
+            dx = raw.dropout_bwd_colsum_into(dout, *ctx["drop"], bias.main_grad, self.slabs, mode)
+            if dx is not None:
+                genv["hidden_states"] = dx
+                return
         dx, dbias = raw.dropout_bwd_colsum(dout, *ctx["drop"])
         genv["hidden_states"] = dx
-        genv[self.residual_name] = dout
         genv["output_bias"] = dbias
 
 

@@ -41,19 +41,49 @@ def ln_fwd(x, gamma, beta, eps):
     return y, mean, rstd
 
 
-def ln_bwd(dy, x, gamma, beta, mean, rstd, residual_grad=None):
+WS_IMMEDIATE, WS_ACCUMULATE, WS_FLUSH = 0, 1, 2   # what a kernel does with its partial column sums
+
+
+class ColumnSumSlabs:
+    """Partial column sums of one op that live across the micro-batches of a step.
+
+    A backward kernel that also produces a parameter gradient as column sums (LayerNorm's dgamma /
+    dbeta, the bias gradient behind a dropout) leaves one partial row per CTA; turning those into
+    the gradient takes a second, tiny launch that sits on the critical path of every backward.
+    With a slab of its own per op the kernel adds to the partials instead (`WS_ACCUMULATE`) and the
+    second launch runs once per step, with the last micro-batch (`WS_FLUSH`), which also clears the
+    slab for the next step. The slab is sized for one (rows, cols, dtype) and refuses another."""
+
+    def __init__(self):
+        self.buf, self.key = None, None
+
+    def get(self, device, floats: int, key):
+        if self.buf is None:
+            self.buf, self.key = torch.zeros(floats, dtype=torch.float32, device=device), key
+        elif self.key != key:
+            raise RuntimeError(f"column-sum slabs were sized for {self.key}, got {key}: deferred column sums "
+                               "need equal micro-batch shapes")
+        return self.buf
+
+
+def ln_bwd(dy, x, gamma, beta, mean, rstd, residual_grad=None, slabs=None, ws_mode=WS_IMMEDIATE):
     """Returns dx (+ `residual_grad`, the gradient reaching the input through the residual branch);
-    accumulates dgamma / dbeta into the parameters' main_grad."""
+    accumulates dgamma / dbeta into the parameters' main_grad: at once, or -- with `slabs` (a
+    `ColumnSumSlabs` of the calling op) and `ws_mode` WS_ACCUMULATE / WS_FLUSH -- once per step."""
     hidden = x.shape[-1]
     rows = x.numel() // hidden
     dg, db = _grad_of(gamma).view(-1), _grad_of(beta).view(-1)
     if native.use_native(x):
         dx = torch.empty_like(x)
-        parts = native.lib().ln_bwd_parts(rows, hidden, x.dtype == torch.float32)
+        fp32 = x.dtype == torch.float32
+        parts = native.lib().ln_bwd_parts(rows, hidden, fp32)
         if residual_grad is not None and not residual_grad.is_contiguous():
             residual_grad = residual_grad.contiguous()
-        native.lib().layernorm_bwd(dy, x, gamma, mean, rstd, dx, dg, db,
-                                   _workspace(x.device, 2 * parts * hidden), True, residual_grad)
+        if slabs is not None and ws_mode != WS_IMMEDIATE and native.lib().ln_bwd_fused_ok(hidden, fp32):
+            ws = slabs.get(x.device, 2 * parts * hidden, (rows, hidden, x.dtype))
+        else:
+            ws, ws_mode = _workspace(x.device, 2 * parts * hidden), WS_IMMEDIATE
+        native.lib().layernorm_bwd(dy, x, gamma, mean, rstd, dx, dg, db, ws, True, residual_grad, ws_mode)
         return dx
     xf, dyf = x.float().reshape(rows, hidden), dy.float().reshape(rows, hidden)
     xh = (xf - mean[:, None]) * rstd[:, None]
@@ -188,6 +218,23 @@ def dropout_bwd(dy, p, seed, offset):
         return dx
     keep = _keep_mask_ref(dy.shape, p, seed, offset, dy.device)
     return torch.where(keep, dy.float() / (1.0 - p), torch.zeros_like(dy.float())).to(dy.dtype)
+
+
+def dropout_bwd_colsum_into(dy, p, seed, offset, bias_grad, slabs, ws_mode):
+    """dropout_bwd(dy), with its column sums added to `bias_grad` (a parameter's main_grad) through
+    the op's own `slabs`: once per step instead of once per micro-batch. Returns None when the fused
+    kernel does not take this shape; the caller then uses `dropout_bwd_colsum`."""
+    cols = dy.shape[-1]
+    if not (p > 0 and ws_mode != WS_IMMEDIATE and native.use_native(dy) and dy.is_contiguous()):
+        return None
+    rows = dy.numel() // cols
+    parts = native.lib().dropout_bwd_colsum_parts(rows, cols, dy.dtype == torch.float32)
+    if parts <= 0:
+        return None
+    dx = torch.empty_like(dy)
+    ws = slabs.get(dy.device, parts * cols, (rows, cols, dy.dtype))
+    native.lib().dropout_bwd_colsum(dy, dx, bias_grad.view(-1), ws, float(p), int(seed), int(offset), True, ws_mode)
+    return dx
 
 
 def dropout_bwd_colsum(dy, p, seed, offset):

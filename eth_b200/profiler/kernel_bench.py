@@ -150,6 +150,16 @@ def main(argv=None):
                  ("ln_bwd + residual gradient", lambda: raw.ln_bwd(dy, x, g, b, mean, rstd, residual_grad=res), 4 * nb),
                  ("bias_dropout_add_fwd", lambda: raw.bias_dropout_add_fwd(x, bias, res, 0.1, 1, 2), 3 * nb),
                  ("dropout_bwd + bias-gradient column sums", lambda: raw.dropout_bwd_colsum(dy, 0.1, 1, 2), 2 * nb)]
+        # the same two backward kernels as the training step runs them on all but the last micro-batch:
+        # partial column sums stay in the op's slabs, no second launch
+        bias.main_grad = torch.zeros(h, device="cuda")
+        ln_slabs, drop_slabs = raw.ColumnSumSlabs(), raw.ColumnSumSlabs()
+        cases += [("ln_bwd + residual gradient, column sums deferred",
+                   lambda: raw.ln_bwd(dy, x, g, b, mean, rstd, residual_grad=res, slabs=ln_slabs,
+                                      ws_mode=raw.WS_ACCUMULATE), 4 * nb),
+                  ("dropout_bwd, bias-gradient column sums deferred",
+                   lambda: raw.dropout_bwd_colsum_into(dy, 0.1, 1, 2, bias.main_grad, drop_slabs, raw.WS_ACCUMULATE),
+                   2 * nb)]
         for name, fn, byts in cases:
             med, best = time_fn(fn, args.warmup, args.repeat)
             out.append({"kernel": name, "rows": rows, "hidden": h, "ms_median": med, "gbs": byts / med / 1e6,

@@ -124,6 +124,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="Reduce all gradient buckets after backward. By default a bucket served by the peer-memory "
                         "backend is reduced on a side stream as soon as the last micro-batch's backward has passed "
                         "its first op.")
+    g.add_argument("--no-deferred-colsums", dest="no_deferred_colsums", action="store_true",
+                   help="Sum LayerNorm-weight and bias gradients after every micro-batch (default: partial column "
+                        "sums stay in per-op slabs and are summed once per step, with the last micro-batch).")
     g.add_argument("--grad-sync-backend", default="auto", choices=["auto", "collective", "peer"],
                    help="Reduction backend: torch.distributed all-reduce or the peer-memory kernel.")
     g.add_argument("--grad-sync-dump-plan", type=str, default=None, help="Write the gradient sync plan as JSON.")

@@ -131,6 +131,7 @@ class TrainEngine:
         self.loss_acc = torch.zeros(2, dtype=torch.float32, device=self.device)
         self._gs_pairs = []
         self._sample_schedule = None
+        self._defer_colsums = None   # decided at the first micro-batch (see _colsum_mode)
         self.last_stats: Dict[str, object] = {}
 
     # ------------------------------------------------------------------ set-up
@@ -303,7 +304,7 @@ class TrainEngine:
         ps = self.pstate
         seq = self.args.mbs_seq[ps.pipeline_id][mb_index][1]
         mb = MicroBatch(index=mb_index, batch=ps.local_micro_batch, seq=seq, global_step=self.iteration,
-                        dp_rank=ps.dp_rank)
+                        dp_rank=ps.dp_rank, colsum_mode=self._colsum_mode(mb_index))
         env = dict(inputs) if inputs else {}
         first, last = ps.is_first_virtual(chunk), ps.is_last_virtual(chunk)
         if first or last:
@@ -320,6 +321,18 @@ class TrainEngine:
                 self.loss_acc[0] += torch.dot(losses, mb.loss_mask)
                 self.loss_acc[1] += mb.loss_mask.sum()
         return out
+
+    def _colsum_mode(self, mb_index: int) -> int:
+        """Column-sum gradients (LayerNorm weights, biases behind a dropout) are summed once per step,
+        with the backward of the last micro-batch, when every micro-batch has the same shape: each
+        op sees its micro-batches in index order under all three schedules."""
+        if self._defer_colsums is None:
+            seqs = {int(entry[1]) for entry in self.args.mbs_seq[self.pstate.pipeline_id]}
+            self._defer_colsums = (self.device.type == "cuda" and len(seqs) == 1
+                                   and not getattr(self.args, "no_deferred_colsums", False))
+        if not self._defer_colsums:
+            return raw_ops.WS_IMMEDIATE
+        return raw_ops.WS_FLUSH if mb_index == self.pstate.num_microbatches - 1 else raw_ops.WS_ACCUMULATE
 
     def backward_step(self, mb_index: int, grad_outputs: Optional[Dict[str, torch.Tensor]], chunk: int = 0):
         ps = self.pstate

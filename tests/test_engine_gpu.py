@@ -43,6 +43,19 @@ def test_async_wgrad_matches_single_stream():
     assert all(abs(a - b) <= max(1e-3, 4 * abs(a - c)) for a, b, c in zip(l0, l2, l1)), (l0, l1, l2)
 
 
+def test_deferred_column_sums_train_like_per_micro_batch_sums():
+    """Summing LayerNorm-weight and bias gradients once per step (partial sums kept in per-op slabs
+    over the five micro-batches) trains like summing them after every micro-batch."""
+    p0, l0 = _run(["--no-async-wgrad", "--no-deferred-colsums"])
+    p1, l1 = _run(["--no-async-wgrad", "--no-deferred-colsums"])
+    p2, l2 = _run(["--no-async-wgrad"])
+    assert l0[0] == l2[0]
+    noise = (p0 - p1).abs().max().item()
+    diff = (p0 - p2).abs().max().item()
+    assert diff <= max(4 * noise, 2e-3), (noise, diff, l0, l2)
+    assert all(abs(a - b) <= max(1e-3, 4 * abs(a - c)) for a, b, c in zip(l0, l2, l1)), (l0, l1, l2)
+
+
 @pytest.mark.parametrize("dtype_flag,tol", [("--bf16", 4e-2), ("--fp16", 1.5e-2)])
 def test_native_stage_program_matches_fp32_oracle(dtype_flag, tol):
     """Forward + backward of the sm_100a stage program (tcgen05 GEMMs with fused epilogues, flash

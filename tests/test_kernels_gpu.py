@@ -352,6 +352,50 @@ def test_dropout_bwd_colsum(rows, cols):
     assert abs(zeros - p) < 0.02
 
 
+@pytest.mark.parametrize("rows,hidden", [(4096, 2048), (777, 1024), (300, 4096)])
+def test_deferred_column_sums_equal_per_call_sums(rows, hidden):
+    """Three backward calls that leave their partial column sums in the op's slabs and flush with
+    the third equal three calls that sum at once: LayerNorm's dgamma / dbeta and the bias gradient
+    behind a dropout. A second round shows the flush left the slabs clear."""
+    from eth_b200.ops import raw
+    torch.manual_seed(21)
+    dtype = torch.bfloat16
+    g = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(dtype)
+    b = (0.1 * torch.randn(hidden, device=DEV)).to(dtype)
+    bias = torch.zeros(hidden, device=DEV, dtype=dtype)
+    data = []
+    for _ in range(3):
+        x = torch.randn(rows, hidden, device=DEV, dtype=dtype)
+        y, mean, rstd = raw.ln_fwd(x, g, b, 1e-5)
+        data.append((x, mean, rstd, torch.randn_like(x)))
+
+    def run(deferred, rounds):
+        for t in (g, b, bias):
+            t.main_grad = torch.zeros(hidden, device=DEV, dtype=torch.float32)
+        ln_slabs, drop_slabs = raw.ColumnSumSlabs(), raw.ColumnSumSlabs()
+        outs = []
+        for _ in range(rounds):
+            for i, (x, mean, rstd, dy) in enumerate(data):
+                mode = raw.WS_IMMEDIATE if not deferred else (raw.WS_FLUSH if i == 2 else raw.WS_ACCUMULATE)
+                outs.append(raw.ln_bwd(dy, x, g, b, mean, rstd, slabs=ln_slabs, ws_mode=mode))
+                if deferred:
+                    dx = raw.dropout_bwd_colsum_into(dy, 0.1, 5, i, bias.main_grad, drop_slabs, mode)
+                    assert dx is not None
+                else:
+                    dx, db = raw.dropout_bwd_colsum(dy, 0.1, 5, i)
+                    bias.main_grad += db
+                outs.append(dx)
+        return outs, [t.main_grad.clone() for t in (g, b, bias)]
+
+    for rounds in (1, 2):
+        ref_out, ref_grads = run(False, rounds)
+        out, grads = run(True, rounds)
+        assert all(torch.equal(a, c) for a, c in zip(out, ref_out))
+        for got, ref in zip(grads, ref_grads):
+            assert _rel_err(got, ref) < 1e-5
+    native.check_status()
+
+
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
 @pytest.mark.parametrize("shape", [(8192, 2048, 256), (8192, 3072, 192), (4864, 4096, 128)])
 def test_gemm_tail_split_half_tiles(a_mn, b_mn, shape):
