@@ -100,44 +100,6 @@ def build_config(n_gpus: int):
     return uniform_config(MODEL, pp=pp, tp=tp, dp=dp, gbs=gbs, mbs=MICRO_BATCH * dp), (pp, tp, dp), gbs
 
 
-def host_batch_provider(vocab: int):
-    """Builds each micro-batch on the host (numpy), stages it in pinned memory and copies it to the
-    device. Returns (provider, byte counter)."""
-    import numpy as np
-    import torch
-    counter = {"h2d": 0}
-    ring, events, cursor = {}, {}, {"i": 0}
-    RING = 4
-
-    def provider(sample_ids, seq, device):
-        ids = np.asarray(sample_ids, dtype=np.int64)[:, None]
-        pos = np.arange(seq, dtype=np.int64)[None, :]
-        tokens = (ids * 1103515245 + pos * 12345) % vocab
-        labels = (ids * 1103515245 + (pos + 1) * 12345) % vocab
-        mask = ((ids + pos) % 4 != 0).astype(np.float32)
-        slot = (len(sample_ids), seq, cursor["i"] % RING)
-        cursor["i"] += 1
-        if slot not in ring:
-            shape = slot[:2]
-            ring[slot] = (torch.empty(shape, dtype=torch.long).pin_memory(),
-                          torch.empty(shape, dtype=torch.long).pin_memory(),
-                          torch.empty(shape, dtype=torch.float32).pin_memory())
-        else:
-            events[slot].synchronize()   # the copies that last used this pinned slot have finished
-        pt, pl, pm = ring[slot]
-        pt.copy_(torch.from_numpy(tokens))
-        pl.copy_(torch.from_numpy(labels))
-        pm.copy_(torch.from_numpy(mask))
-        out = (pt.to(device, non_blocking=True), pl.to(device, non_blocking=True), pm.to(device, non_blocking=True))
-        ev = torch.cuda.Event()
-        ev.record()
-        events[slot] = ev
-        counter["h2d"] += pt.numel() * 8 + pl.numel() * 8 + pm.numel() * 4
-        return out
-
-    return provider, counter
-
-
 def run_ours(opts):
     import torch
     import torch.distributed as dist
@@ -211,10 +173,11 @@ def run_ours(opts):
     value = tokens / (ms / 1e3)
 
     # end-to-end arm: host-built batches from pinned memory + loss read-back every step
-    provider, counter = host_batch_provider(VOCAB)
+    from eth_b200.data.provider import SyntheticHostProvider
+    provider = SyntheticHostProvider(VOCAB)   # what --host-data selects in the training entry point
     engine.data_provider = provider
     engine.train_step()
-    counter["h2d"] = 0
+    provider.reset_counter()
     ms_e2e, _, losses = timed(opts.steps, e2e=True)
     e2e_value = tokens / (ms_e2e / 1e3)
     native.check_status()
@@ -231,7 +194,7 @@ def run_ours(opts):
                        "l2": "inputs larger than L2 (each step streams several GB of weights and activations)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / opts.steps,
-                    "h2d_bytes_per_step": counter["h2d"] // opts.steps, "d2h_bytes_per_step": 8,
+                    "h2d_bytes_per_step": provider.h2d_bytes // opts.steps, "d2h_bytes_per_step": 8,
                     "final_loss": losses[-1] if losses else None},
             "gpu_launches": launches,
             "exposed_grad_sync_ms_per_step": exposed_ms,

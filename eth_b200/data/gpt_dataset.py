@@ -45,18 +45,38 @@ def build_shuffle_idx(num_samples: int, total_size: int, rng: np.random.RandomSt
     return np.concatenate((first, last))
 
 
+def last_epoch_is_separate(tokens_per_epoch: int, seq_length: int, num_samples: int, epochs: int):
+    """(separate, samples before the last epoch). When the run needs only a small part (< 80 %) of
+    its last epoch, that epoch's samples must not be mixed into the global shuffle: they would push
+    samples of the full epochs out of the first `num_samples` draws. The last epoch then gets its
+    own document order and its own shuffle range (reference: gpt_dataset.py:222-262, 286-293)."""
+    if epochs == 1:
+        return False, 0
+    before = ((epochs - 1) * tokens_per_epoch - 1) // seq_length
+    in_last = num_samples - before
+    per_epoch = (tokens_per_epoch - 1) // seq_length
+    if not 0 <= in_last <= per_epoch:
+        raise ValueError(f"inconsistent epoch arithmetic: {in_last} samples in the last epoch of {per_epoch}")
+    return in_last < int(0.80 * per_epoch), before
+
+
 class GPTDataset:
+    """Index maps are built in memory on every rank from (documents, num_samples, seq_length, seed):
+    deterministic, so ranks agree without the reference's .npy files beside the data."""
+
     def __init__(self, indexed_dataset, documents, num_samples: int, seq_length: int, seed: int):
         self.data, self.seq_length = indexed_dataset, seq_length
         documents = np.asarray(documents, dtype=np.int32)
         tokens = num_tokens_per_epoch(indexed_dataset.sizes, documents)
         epochs = num_epochs_for(tokens, seq_length, num_samples)
         rng = np.random.RandomState(seed)
-        self.doc_idx = build_doc_idx(documents, epochs, rng)
+        separate, before_last = last_epoch_is_separate(tokens, seq_length, num_samples, epochs)
+        self.separate_last_epoch = separate
+        self.doc_idx = build_doc_idx(documents, epochs, rng, separate)
         self.sample_idx = build_sample_idx(np.asarray(indexed_dataset.sizes, dtype=np.int32), self.doc_idx, seq_length,
                                            epochs, tokens)
         n = self.sample_idx.shape[0] - 1
-        self.shuffle_idx = build_shuffle_idx(n, n, rng)
+        self.shuffle_idx = build_shuffle_idx(before_last if separate else n, n, rng)
 
     def __len__(self) -> int:
         return self.sample_idx.shape[0] - 1

@@ -55,9 +55,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--eval-interval", type=int, default=1000, help="Iterations between evaluations.")
     g.add_argument("--async-optimizer", action="store_true",
                    help="Do not read the overflow flag / norm back each step (bf16 runs); the kernels skip on overflow.")
-    g.add_argument("--cuda-graphs", action="store_true", help="Capture per-micro-batch stage programs in CUDA graphs.")
     g.add_argument("--host-data", action="store_true",
-                   help="Build every batch on the host and copy it from pinned memory (end-to-end timing path).")
+                   help="Build every synthetic batch on the host and copy it from pinned memory (the input path "
+                        "a dataset takes; ignored with --data-path).")
 
     g = p.add_argument_group("initialization")
     g.add_argument("--seed", type=int, default=1234, help="Random seed.")
@@ -104,10 +104,19 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--device", default=None, help="Device override (cpu for validation runs).")
 
     g = p.add_argument_group("data")
-    g.add_argument("--data-path", nargs="*", default=None, help="Weights and prefixes of indexed datasets (optional).")
-    g.add_argument("--split", type=str, default="949,50,1", help="Train/valid/test split.")
-    g.add_argument("--vocab-file", type=str, default=None, help="GPT-2 vocabulary json.")
+    g.add_argument("--data-path", nargs="*", default=None,
+                   help="One prefix of an indexed token dataset, or weight/prefix pairs to blend. Without it the "
+                        "run trains on synthetic tokens.")
+    g.add_argument("--split", type=str, default="949,50,1",
+                   help="Train/valid/test proportions of the documents of each dataset.")
+    g.add_argument("--vocab-file", type=str, default=None,
+                   help="GPT-2 vocabulary json; with --merge-file it sets the vocabulary size and the "
+                        "end-of-document token.")
     g.add_argument("--merge-file", type=str, default=None, help="GPT-2 BPE merges.")
+    g.add_argument("--eod-mask-loss", action="store_true", help="No loss on end-of-document tokens.")
+    g.add_argument("--reset-position-ids", action="store_true", help="Not supported (positions run over the sequence).")
+    g.add_argument("--reset-attention-mask", action="store_true",
+                   help="Not supported (attention is causal over the whole sequence).")
     g.add_argument("--data-impl", type=str, default="mmap", choices=["lazy", "cached", "mmap", "infer"],
                    help="Indexed dataset implementation.")
     g.add_argument("--reference-zero-labels", action="store_true",
@@ -205,6 +214,18 @@ def finalize_args(args, config=None):
                 raise ValueError(f"--interleave-factor > 1 needs at least two stages and a number of micro-batches "
                                  f"divisible by the number of stages (pipeline {i}: {p['num_stages']} stages, "
                                  f"{n_mb} micro-batches)")
+    if args.reset_position_ids or args.reset_attention_mask:
+        raise ValueError("--reset-position-ids / --reset-attention-mask are not supported: the attention kernels are "
+                         "causal over the whole sequence and positions are not restarted at document boundaries")
+    args.eod_token = None
+    if bool(args.vocab_file) != bool(args.merge_file):
+        raise ValueError("--vocab-file and --merge-file go together")
+    if args.vocab_file:
+        from ..tokenizer.tokenizer import GPT2BPETokenizer
+        tokenizer = GPT2BPETokenizer(args.vocab_file, args.merge_file)
+        args.vocab_size, args.eod_token = tokenizer.vocab_size, tokenizer.eod
+    if args.eod_mask_loss and args.eod_token is None:
+        raise ValueError("--eod-mask-loss needs the tokenizer files (--vocab-file, --merge-file) to know the token")
     max_tp = max(s.tp_degree for s in args.canonical_topology.stages)
     multiple = args.make_vocab_size_divisible_by * max_tp
     args.padded_vocab_size = (args.vocab_size + multiple - 1) // multiple * multiple

@@ -122,6 +122,8 @@ class TrainEngine:
                              neighbours=(ps.chunk_neighbour(c, -1), ps.chunk_neighbour(c, +1)))
                 for c, (spec_in, spec_out) in enumerate(self.stage.chunk_specs)]
         self.data_provider = data_provider
+        self.eval_data_provider = None   # batches of eval_step; None = the training provider
+        self.eval_cursor = 0             # position in the validation data (advanced by the evaluation loop)
         self.clock = TrainingClock(total_gbs=args.total_gbs)
         self.iteration = 0
         self._setup_grad_sync()
@@ -439,14 +441,16 @@ class TrainEngine:
         sum and weight into `loss_acc` (read them with `reduced_loss`). Gradients, optimizer state,
         the data cursor and the iteration counter are left untouched."""
         cfg = self.stage.cfg
-        saved = cfg.hidden_dropout
+        saved, provider = cfg.hidden_dropout, self.data_provider
         cfg.hidden_dropout = 0.0
+        if self.eval_data_provider is not None:
+            self.data_provider = self.eval_data_provider
         try:
             self.loss_acc.zero_()
             schedules.forward_only(self, self.pstate.num_microbatches)
             self.coll.all_reduce_sum(self.loss_acc)
         finally:
-            cfg.hidden_dropout = saved
+            cfg.hidden_dropout, self.data_provider = saved, provider
 
     def _evidence(self, phase, out_dir, **metrics):
         from ..parallel.grad_sync.evidence import snapshot_rank

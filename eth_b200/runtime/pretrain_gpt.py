@@ -21,6 +21,7 @@ import torch.distributed as dist
 from ..parallel.grad_sync.loss import validate_training_clock_states
 from .arguments import parse_args
 from .checkpointing import load_checkpoint, save_checkpoint
+from ..data.provider import providers_from_args
 from .engine import TrainEngine
 
 
@@ -113,12 +114,18 @@ def evaluate(engine, eval_iters: int):
     training cursor without advancing it."""
     total, weight = 0.0, 0.0
     cursor = engine.clock.global_data_cursor
+    # a validation dataset is read from its own position, which moves on from one evaluation to the next
+    own_cursor = engine.eval_data_provider is not None and engine.eval_data_provider is not engine.data_provider
+    if own_cursor:
+        engine.clock.global_data_cursor = engine.eval_cursor
     try:
         for _ in range(eval_iters):
             engine.eval_step()
             s, w = engine.loss_acc.tolist()
             total, weight = total + s, weight + w
             engine.clock.global_data_cursor += engine.clock.total_gbs
+        if own_cursor:
+            engine.eval_cursor = engine.clock.global_data_cursor
     finally:
         engine.clock.global_data_cursor = cursor
     loss = total / weight if weight > 0 else float("nan")
@@ -130,8 +137,14 @@ def pretrain(argv=None):
     device = initialize_distributed(args)
     t_start = time.time()
     engine = TrainEngine(args, device=device)
+    engine.data_provider, engine.eval_data_provider = providers_from_args(args, engine.pstate, args.eod_token)
+    if args.data_path:
+        print_rank_0(f"> training on {args.data_path} (split {args.split}); validation set: "
+                     f"{'yes' if engine.eval_data_provider is not None else 'none'}")
     if args.load:
         load_checkpoint(engine, args.load)
+        if args.eval_interval:   # validation data already read by the evaluations before the checkpoint
+            engine.eval_cursor = (engine.iteration // args.eval_interval) * args.eval_iters * args.total_gbs
     # all ranks must agree on the clock before the first step (reference: training.py:896-898)
     states = [None] * args.world_size
     engine.coll.all_gather_object(states, (engine.clock.global_data_cursor, engine.clock.successful_optimizer_steps))

@@ -146,3 +146,40 @@ def test_interleaved_schedule_matches_single_rank(name, world, stage_ops, factor
         assert abs(a - b) < 1e-4
     for a, b in zip(results[0]["norms"], single["norms"]):
         assert abs(a - b) / b < 1e-3
+
+
+def _tp_feed(rank, world, prefix):
+    """TP2 engine on an indexed dataset: rank 0 of the group reads, rank 1 receives the broadcast."""
+    from types import SimpleNamespace
+    from eth_b200.data.provider import providers_from_args
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+    config = _config([make_pipe([N_OPS], [2], [1], gbs=4, mbs=2)])
+    argv = ["--hidden-dropout", "0.0", "--device", "cpu", "--vocab-size", str(VOCAB), "--make-vocab-size-divisible-by",
+            "8", "--distributed-backend", "gloo", "--data-path", prefix, "--split", "1,0,0", "--train-iters", "2"]
+    args = parse_args(argv, config=config, rank=rank, world_size=world)
+    eng = TrainEngine(args, device="cpu")
+    eng.data_provider, eng.eval_data_provider = providers_from_args(args, eng.pstate, None)
+    tokens, labels, mask = eng.get_batch(1)
+    eng.train_step()
+    reads_data = getattr(eng.data_provider, "inner", None) is not None
+    return {"tokens": tokens.clone(), "labels": labels.clone(), "mask": mask.clone(), "reads": reads_data,
+            "loss": eng.reduced_loss()}
+
+
+def test_dataset_batches_are_broadcast_inside_a_tp_group(tmp_path):
+    import numpy as np
+    from eth_b200.data.indexed_dataset import MMapIndexedDatasetBuilder
+    prefix = str(tmp_path / "toy")
+    rng = np.random.RandomState(0)
+    b = MMapIndexedDatasetBuilder(prefix + ".bin", dtype=np.uint16)
+    for _ in range(60):
+        b.add_item(rng.randint(1, VOCAB, size=rng.randint(5, 30)))
+        b.end_document()
+    b.finalize(prefix + ".idx")
+    r0, r1 = run_ranks(2, _tp_feed, prefix)
+    assert r0["reads"] and not r1["reads"]
+    for key in ("tokens", "labels", "mask"):
+        assert torch.equal(r0[key], r1[key])
+    assert torch.equal(r0["tokens"][:, 1:], r0["labels"][:, :-1])
+    assert r0["loss"] == r1["loss"] and r0["loss"] == r0["loss"]
