@@ -218,7 +218,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bf16", action="store_true", help="bf16 instead of the config's fp16")
+    ap.add_argument("--layout", default=None,
+                    help="pp,tp,dp to use instead of the default layout of --gpus (same model, batch per GPU and "
+                         "metric; for studying a layout, e.g. 2,2,1 on four GPUs)")
     opts = ap.parse_args()
+    if opts.layout:
+        pp, tp, dp = (int(v) for v in opts.layout.split(","))
+        if pp * tp * dp != opts.gpus:
+            raise SystemExit("--layout must multiply to --gpus")
+        LAYOUTS[opts.gpus] = (pp, tp, dp)
     if opts.gpus not in LAYOUTS:
         raise SystemExit(f"--gpus must be one of {sorted(LAYOUTS)}")
     if opts.impl == "reference":

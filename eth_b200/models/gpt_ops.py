@@ -102,6 +102,20 @@ class TPComm:
         y = raw.gemm(x, weight, b_mn=b_mn)
         return self.all_reduce_(y)
 
+    def reshard(self, x: torch.Tensor, step) -> torch.Tensor:
+        """Run one placement change (`parallel.resharding.ReshardStep`) of a token-major tensor over
+        this stage's tensor-parallel group. The placement algebra numbers dims (sequence, batch,
+        hidden); here sequence and batch are folded into the rows, so the hidden dim is the last."""
+        if self.size == 1 or step.primitive == "identity":
+            return x
+        from ..parallel.resharding import ReshardStep, apply_reshard
+        last = x.dim() - 1
+        local = ReshardStep(step.primitive, step.group_size, None if step.src_dim is None else last,
+                            None if step.dst_dim is None else last)
+        if step.group_size != self.size:
+            raise ValueError(f"placement change over {step.group_size} ranks inside a TP group of {self.size}")
+        return apply_reshard(x, local, self.group, self.rank)
+
     def gather_stats(self, stats: torch.Tensor) -> torch.Tensor:
         """[rows, 3] -> [tp, rows, 3] (cross-entropy statistics)."""
         if self.size == 1:
@@ -160,6 +174,23 @@ class Op:
         self.fuse_next = False   # set by the stage builder when the following op is fused into this one
         self.fuse_prev = False
         self.slabs = raw.ColumnSumSlabs()   # used by ops whose backward leaves partial column sums
+        self.algo = 0
+
+    def set_algo(self, algo: int) -> None:
+        """Sharding choice of a tensor-parallel GEMM op: 0 = its usual column- or row-parallel form,
+        1 = the other one (reference: model/flex_ops.py:140-236 `gen_op(..., algo)`). With algo 1 the
+        op keeps its placement contract towards its neighbours (what it reads and writes is sharded
+        as under algo 0) and converts at its own input and output; the conversions are the ones the
+        placement algebra plans between the two algos' specs (`search/model_ops.get_op_spec`,
+        `parallel/resharding.plan_reshard`; reference: mpu/mappings.py:381-467 `tensor_adapter`)."""
+        from ..parallel.resharding import plan_reshard
+        from ..search.model_ops import get_op_spec
+        if algo not in (0, 1):
+            raise ValueError(f"algo {algo} is not implemented (0 or 1)")
+        self.algo = int(algo) if self.tp.size > 1 else 0
+        t = self.tp.size
+        self.in_step = plan_reshard(get_op_spec(self.name, t, 1, 0, True), get_op_spec(self.name, t, 1, self.algo, True))
+        self.out_step = plan_reshard(get_op_spec(self.name, t, 1, self.algo, False), get_op_spec(self.name, t, 1, 0, False))
 
     def specs(self) -> List[ParamSpec]:
         return []
@@ -280,11 +311,29 @@ class ColumnLinearOp(Op):
         self.consumes = ("hidden_states",) if out_name != "hidden_states" else ()
 
     def specs(self):
-        return [ParamSpec("weight", self._lid(self.suffix + ".weight"), (self.out_features, self.in_features), 0),
-                ParamSpec("bias", self._lid(self.suffix + ".bias"), (self.out_features,), 0, init="zeros",
+        # algo 1 runs this GEMM row-parallel: the weight is cut along its input features and the
+        # bias, added after the reduction, is replicated
+        wdim, bdim = (0, 0) if self.algo == 0 else (1, -1)
+        return [ParamSpec("weight", self._lid(self.suffix + ".weight"), (self.out_features, self.in_features), wdim),
+                ParamSpec("bias", self._lid(self.suffix + ".bias"), (self.out_features,), bdim, init="zeros",
                           weight_decay=False)]
 
+    def _fwd_row(self, env, ctx):
+        x = self.tp.reshard(env.pop("hidden_states"), self.in_step)          # replicated -> my input features
+        ctx["x"] = x
+        y = self.tp.linear_all_reduce(x, self.p("weight"))                    # [tokens, out], summed over TP
+        y = raw.bias_dropout_add_fwd(y, self.p("bias"), None, 0.0, 0, 0)
+        env[self.out_name] = self.tp.reshard(y, self.out_step)                # replicated -> my output features
+
+    def _bwd_row(self, genv, ctx):
+        dy = self.tp.reshard(_take(genv, self.out_name), self.out_step.dual())
+        dx = raw.linear_dgrad(dy, self.p("weight"))                           # my input features only
+        raw.linear_wgrad(dy, ctx["x"], self.p("weight"), self.p("bias"))
+        genv["hidden_states"] = self.tp.reshard(dx, self.in_step.dual())
+
     def fwd(self, env, ctx, mb):
+        if self.algo == 1:
+            return self._fwd_row(env, ctx)
         x = env.pop("hidden_states")
         ctx["x"] = x
         if self.fuse_next:   # GeLU in the GEMM epilogue
@@ -295,6 +344,8 @@ class ColumnLinearOp(Op):
             env[self.out_name] = raw.linear_fwd(x, self.p("weight"), self.p("bias"))
 
     def bwd(self, genv, ctx, mb):
+        if self.algo == 1:
+            return self._bwd_row(genv, ctx)
         dy = _take(genv, self.out_name)
         dx = self.tp.linear_all_reduce(dy, self.p("weight"), b_mn=True)
         raw.linear_wgrad(dy, ctx["x"], self.p("weight"), self.p("bias"))
@@ -312,22 +363,36 @@ class RowLinearOp(Op):
         self.in_features, self.out_features, self.suffix = in_features, out_features, suffix
 
     def specs(self):
-        return [ParamSpec("weight", self._lid(self.suffix + ".weight"), (self.out_features, self.in_features), 1,
-                          init="scaled_normal"),
+        # algo 1 runs this GEMM column-parallel (weight cut along its output features); the bias stays
+        # replicated and still travels to the dropout-add op, which adds it to the gathered output
+        return [ParamSpec("weight", self._lid(self.suffix + ".weight"), (self.out_features, self.in_features),
+                          1 if self.algo == 0 else 0, init="scaled_normal"),
                 ParamSpec("bias", self._lid(self.suffix + ".bias"), (self.out_features,), -1, init="zeros",
                           weight_decay=False)]
 
     def fwd(self, env, ctx, mb):
+        env["output_bias"] = self.p("bias")
+        if self.algo == 1:
+            x = self.tp.reshard(env["hidden_states"], self.in_step)           # my input features -> all of them
+            ctx["x"] = x
+            y = raw.linear_fwd(x, self.p("weight"))                            # my output features
+            env["hidden_states"] = self.tp.reshard(y, self.out_step)           # -> replicated
+            return
         x = env["hidden_states"]
         ctx["x"] = x
         env["hidden_states"] = self.tp.linear_all_reduce(x, self.p("weight"))
-        env["output_bias"] = self.p("bias")
 
     def bwd(self, genv, ctx, mb):
         dy = _take(genv, "hidden_states")
         db = genv.pop("output_bias", None)
         if db is not None:
             self.p("bias").main_grad.view(-1).add_(db.to(self.p("bias").main_grad.dtype).view(-1))
+        if self.algo == 1:
+            dy = self.tp.reshard(dy, self.out_step.dual())
+            dx = self.tp.linear_all_reduce(dy, self.p("weight"), b_mn=True)   # all input features, summed over TP
+            genv["hidden_states"] = self.tp.reshard(dx, self.in_step.dual())
+            raw.linear_wgrad(dy, ctx["x"], self.p("weight"))
+            return
         gelu_pre = mb.ctxs[self.op_index - 1]["pre"] if self.fuse_prev else None
         genv["hidden_states"] = raw.linear_dgrad(dy, self.p("weight"), gelu_pre=gelu_pre)
         if gelu_pre is not None:
@@ -534,7 +599,17 @@ def build_op_descriptors(num_layers: int, model_impl: str = "gpt") -> List[dict]
     return out
 
 
-def make_op(desc: dict, cfg: GPTModelConfig, tp: TPComm) -> Op:
+def make_op(desc: dict, cfg: GPTModelConfig, tp: TPComm, algo: int = 0) -> Op:
+    op = _make_op(desc, cfg, tp)
+    if algo:
+        if not isinstance(op, (ColumnLinearOp, RowLinearOp)):
+            algo = 0      # only the four tensor-parallel GEMMs have a second sharding choice
+        else:
+            op.set_algo(algo)
+    return op
+
+
+def _make_op(desc: dict, cfg: GPTModelConfig, tp: TPComm) -> Op:
     n, i, layer = desc["name"], desc["op_index"], desc["layer_index"]
     h, f = cfg.hidden_size, cfg.ffn_hidden_size
     a = (n, i, layer, cfg, tp)

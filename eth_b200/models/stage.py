@@ -51,7 +51,7 @@ class GPTStage:
 
     def __init__(self, cfg: GPTModelConfig, op_begin: int, op_end: int, tp: Optional[TPComm] = None,
                  device="cpu", recompute_ops: Optional[Sequence[int]] = None, fuse: bool = True,
-                 chunks: Optional[Sequence[Tuple[int, int]]] = None):
+                 chunks: Optional[Sequence[Tuple[int, int]]] = None, algo_ops: Optional[Sequence[int]] = None):
         self.cfg = cfg
         self.tp = tp or TPComm()
         self.device = torch.device(device)
@@ -60,9 +60,13 @@ class GPTStage:
         self.op_begin, self.op_end = self.chunk_ranges[0][0], self.chunk_ranges[-1][1]
         self.ops: List[Op] = []
         self._chunk_slices: List[Tuple[int, int]] = []      # index range of every chunk inside self.ops
+        n_ops = sum(e - b for b, e in self.chunk_ranges)
+        algos = list(algo_ops) if algo_ops is not None else [0] * n_ops
+        if len(algos) != n_ops:
+            raise ValueError("algo_ops length must equal the stage's op count")
         for b, e in self.chunk_ranges:
             start = len(self.ops)
-            self.ops += [make_op(d, cfg, self.tp) for d in self.descriptors[b:e]]
+            self.ops += [make_op(d, cfg, self.tp, algos[start + k]) for k, d in enumerate(self.descriptors[b:e])]
             self._chunk_slices.append((start, len(self.ops)))
         self.is_first = self.chunk_ranges[0][0] == 0
         self.is_last = self.chunk_ranges[-1][1] == len(self.descriptors)
@@ -163,9 +167,11 @@ class GPTStage:
         for start, end in self._chunk_slices:       # never across a chunk boundary
             ops = self.ops[start:end]
             for a, b in zip(ops, ops[1:]):
-                if a.name == "enc-MLP-GEMM-1" and b.name == "enc-MLP-gelu":
+                # the GeLU epilogues belong to the usual sharding: with algo 1 the bias is added after a
+                # reduction (GEMM-1) and the data gradient is reduced before it is cut (GEMM-2)
+                if a.name == "enc-MLP-GEMM-1" and b.name == "enc-MLP-gelu" and a.algo == 0:
                     a.fuse_next = True
-                if a.name == "enc-MLP-gelu" and b.name == "enc-MLP-GEMM-2":
+                if a.name == "enc-MLP-gelu" and b.name == "enc-MLP-GEMM-2" and b.algo == 0:
                     b.fuse_prev = True
 
     # ------------------------------------------------------------------ recompute segments

@@ -10,8 +10,14 @@ reference brackets host wall-clock with device synchronisation, eth/profiler/op_
 Output: `gpt_<size>_mbs<m>_tp<t>_algo<a>.csv` with header
 `op_name, forward-compute, backward-compute, input_size, output_size, weights, activations,
 fwd_reserved, bwd_reserved` (times in microseconds, sizes in MB; :424-445) and a pickle cache.
-Both algo files carry the same measurements: the stage program implements the column-then-row
-sharding (algo 0) only. A failed op is recorded with the reference's sentinel 1e7 (:528-530).
+The algo-1 file is measured with the four tensor-parallel GEMM ops in their swapped sharding
+(placement conversions at their inputs and outputs included); every other op has one form, so
+its measurement is shared by both files through the cache key (`op_key`; reference :221-228). A
+failed op is recorded with the reference's sentinel 1e7 (:528-530).
+
+With `--prof-num-nodes N --prof-node-rank r` the micro-batch sizes are dealt out to the nodes by
+estimated cost (tokens per micro-batch), largest first onto the least loaded node, so that N nodes
+of the same GPU type profile disjoint shares (reference :452-487 splits by a previous run's times).
 """
 from __future__ import annotations
 
@@ -110,9 +116,31 @@ def profile_op(stage: GPTStage, mbs: int, seq: int, vocab: int, warmup: int, rep
             max(fwd_res, 0.0), max(bwd_res, 0.0)]
 
 
+ALGO_OPS = ("enc-attention-qkv", "enc-attention-dense", "enc-MLP-GEMM-1", "enc-MLP-GEMM-2")
+
+
+def op_key(model_size: str, mbs: int, tp_size: int, op_name: str, op_index: int, algo: int):
+    """Cache key of one measurement: ops without a second sharding choice share it across algos."""
+    return (model_size, mbs, tp_size, op_index, op_name, algo if op_name in ALGO_OPS and tp_size > 1 else 0)
+
+
+def node_share(mbs_list, num_nodes: int, node_rank: int):
+    """The micro-batch sizes this node profiles: longest first onto the least loaded node."""
+    if num_nodes <= 1:
+        return list(mbs_list)
+    load, mine = [0] * num_nodes, []
+    for mbs in sorted(mbs_list, reverse=True):
+        node = load.index(min(load))
+        load[node] += mbs
+        if node == node_rank:
+            mine.append(mbs)
+    return sorted(mine)
+
+
 def run_profile(args, tp_size: int, tp_rank: int, group, device):
     shape = gpt_profile_shape(args.prof_model_size)
-    mbs_list = args.prof_mbs_list or [1, 2, 4, 8]
+    mbs_list = node_share(args.prof_mbs_list or [1, 2, 4, 8], getattr(args, "prof_num_nodes", 1) or 1,
+                          getattr(args, "prof_node_rank", 0) or 0)
     n_ops = manifest_size(1)
     cache_path = args.prof_cache_file
     cache = {}
@@ -135,15 +163,16 @@ def run_profile(args, tp_size: int, tp_rank: int, group, device):
             print(f"[op_profiler] fused TP backend unavailable: {exc}", file=sys.stderr)
     tp = TPComm(tp_size, tp_rank, group, backend)
     warmup, repeat = args.prof_warmup_times, args.prof_repeat_times[0]
-    for mbs in mbs_list:
+    names = [d["name"] for d in GPTStage(cfg, 0, 1, tp=TPComm(), device="cpu").descriptors]
+    for mbs, algo in ((m, a) for m in mbs_list for a in (0, 1)):
         rows = []
         for i in range(n_ops):
-            key = (args.prof_model_size, mbs, tp_size, i)
+            key = op_key(args.prof_model_size, mbs, tp_size, names[i], i, algo)
             if key in cache:
                 rows.append(cache[key])
                 continue
             try:
-                stage = GPTStage(cfg, i, i + 1, tp=tp, device=device, fuse=False)
+                stage = GPTStage(cfg, i, i + 1, tp=tp, device=device, fuse=False, algo_ops=[algo])
                 row = profile_op(stage, mbs, shape["seq_length"], shape["vocab"], warmup, repeat, device)
                 del stage
             except Exception as exc:
@@ -158,13 +187,12 @@ def run_profile(args, tp_size: int, tp_rank: int, group, device):
             rows.append(row)
             torch.cuda.empty_cache()
         if tp_rank == 0:
-            for algo in (0, 1):
-                path = os.path.join(args.prof_path, f"gpt_{args.prof_model_size}_mbs{mbs}_tp{tp_size}_algo{algo}.csv")
-                with open(path, "w", newline="") as f:
-                    w = csv.writer(f)
-                    w.writerow(OP_HEADER)
-                    for r in rows:
-                        w.writerow([r[0]] + [f"{x:.3f}" for x in r[1:3]] + [f"{x:.4f}" for x in r[3:]])
+            path = os.path.join(args.prof_path, f"gpt_{args.prof_model_size}_mbs{mbs}_tp{tp_size}_algo{algo}.csv")
+            with open(path, "w", newline="") as f:
+                w = csv.writer(f)
+                w.writerow(OP_HEADER)
+                for r in rows:
+                    w.writerow([r[0]] + [f"{x:.3f}" for x in r[1:3]] + [f"{x:.4f}" for x in r[3:]])
     if tp_rank == 0 and cache_path:
         with open(cache_path, "wb") as f:
             pickle.dump(cache, f)

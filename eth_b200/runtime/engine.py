@@ -108,8 +108,13 @@ class TrainEngine:
         self.tp = self._make_tp_comm()
         begin, end = ps.op_range
         chunks = ps.chunk_ranges if ps.interleave > 1 else None
+        algo_ops = list(ps.pipe["algo_of_each_op"][ps.stage_id])
+        if any(algo_ops) and ps.tp_size > 1 and not ps.pipe["resharding_stages"][ps.stage_id]:
+            raise ValueError(f"pipeline {ps.pipeline_id} stage {ps.stage_id} asks for algo 1 (the swapped sharding of the "
+                             "tensor-parallel GEMMs), which converts placements inside the stage: set "
+                             "resharding_stages to true for it")
         self.stage = GPTStage(self.model_cfg, begin, end, tp=self.tp, device=self.device,
-                              recompute_ops=ps.recompute_ops, chunks=chunks)
+                              recompute_ops=ps.recompute_ops, chunks=chunks, algo_ops=algo_ops)
         self.seq_len = cfg["seq_length"]
         self.comm = PipelineComm(ps, cfg["hidden_size"], self.seq_len, self.stage.input_spec, self.stage.output_spec,
                                  args.params_dtype, self.device) if ps.num_stages > 1 else None

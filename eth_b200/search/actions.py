@@ -106,6 +106,16 @@ def move_gpus(plan: PipelinePlan, donor: int, receiver: int, max_tp: int, heads:
             yield PipelinePlan(tuple(stages), plan.mbs)
 
 
+def swap_sharding(plan: PipelinePlan, index: int) -> Iterator[PipelinePlan]:
+    """The stage's four tensor-parallel GEMMs in their other sharding (algo 0 <-> 1): qkv / MLP-GEMM-1
+    row- instead of column-parallel, dense / MLP-GEMM-2 the other way round. Only the profile says
+    which is faster for a given shape (reference: per-op algo fine-tuning, actions.py:1236-1433; one
+    value per stage here, as the config contract demands)."""
+    st = plan.stages[index]
+    if st.tp > 1:
+        yield plan.with_stage(index, replace(st, algo=1 - st.algo, recompute=()))
+
+
 def _shapes(gpus: int, max_tp: int, heads: int, hidden: int, mbs: int) -> List[Tuple[int, int]]:
     return [(tp, gpus // tp) for tp in (1, 2, 4, 8)
             if tp <= max_tp and gpus % tp == 0 and heads % tp == 0 and hidden % tp == 0 and mbs % (gpus // tp) == 0]
@@ -145,4 +155,5 @@ CATALOGUE: Tuple[Move, ...] = (
     Move("take-gpus", _effects(time="-", memory="-", devices="+"), move_gpus),
     Move("smaller-micro-batch", _effects(time="-", memory="-", efficiency="-"), change_micro_batch),
     Move("larger-micro-batch", _effects(time="+", memory="+", efficiency="+"), change_micro_batch),
+    Move("swap-sharding", _effects(time="-", memory="-", comm="-"), swap_sharding),
 )

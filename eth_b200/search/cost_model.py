@@ -36,6 +36,7 @@ class StageChoice:
     dp: int
     gpu_type: str = "default"
     gpu_types: Tuple[str, ...] = ()      # all distinct types of a mixed stage; () = just `gpu_type`
+    algo: int = 0                        # sharding choice of the stage's tensor-parallel GEMMs
 
     def types(self) -> Tuple[str, ...]:
         return self.gpu_types or (self.gpu_type,)
@@ -217,7 +218,7 @@ class CostModel:
         from .state import OPS_PER_LAYER as OPL, op_position
         if mbs % stage.dp:
             return None
-        rows = self.op_rows(stage.gpu_types, mbs // stage.dp, stage.tp)
+        rows = self.op_rows(stage.gpu_types, mbs // stage.dp, stage.tp, getattr(stage, "algo", 0))
         if rows is None:
             return None
         row_of = {"pre": lambda k: rows[0], "layer": lambda k: rows[1 + k], "post": lambda k: rows[1 + OPL + k]}

@@ -14,7 +14,7 @@ import time
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
-from .actions import change_micro_batch, exchange_tp_dp, migrate_ops, move_gpus
+from .actions import change_micro_batch, exchange_tp_dp, migrate_ops, move_gpus, swap_sharding
 from .cost_model import CostModel
 from .policy import Visited, ordered_moves, partner_stages, target_stage, views_of
 from .state import PipelinePlan
@@ -86,6 +86,9 @@ class Refiner:
                 for p in exchange_tp_dp(plan, target, self.max_tp, self.heads, self.hidden):
                     if (p.stages[target].tp > plan.stages[target].tp) == want_tp_up:
                         yield move.name, p
+            elif move.name == "swap-sharding":
+                for p in swap_sharding(plan, target):
+                    yield move.name, p
             elif move.name == "take-gpus":
                 for partner in partners:
                     for p in move_gpus(plan, partner, target, self.max_tp, self.heads, self.hidden):

@@ -142,15 +142,16 @@ class PipelineSearcher:
         shapes = [(c.gpus, c.tp, c.dp, c.types()) for c in r.stages]
         if r.op_counts:
             stages, cursor = [], 0
-            for n, (g, tp, dp, types) in zip(r.op_counts, shapes):
-                stages.append(StagePlan(cursor, cursor + n, g, tp, dp, tuple(types)))
+            for n, (g, tp, dp, types), c in zip(r.op_counts, shapes, r.stages):
+                stages.append(StagePlan(cursor, cursor + n, g, tp, dp, tuple(types), algo=c.algo))
                 cursor += n
             return PipelinePlan(tuple(stages), r.mbs)
         return plan_from_layers(r.layers, shapes, r.mbs, self.L)
 
     def _from_scored(self, scored, how: str) -> PipelineResult:
         plan = scored.plan
-        choices = [StageChoice(st.gpus, st.tp, st.dp, st.gpu_types[0], gpu_types=st.gpu_types) for st in plan.stages]
+        choices = [StageChoice(st.gpus, st.tp, st.dp, st.gpu_types[0], gpu_types=st.gpu_types, algo=st.algo)
+                   for st in plan.stages]
         counts = [st.num_ops for st in plan.stages]
         layers = [max(0, round((n - (1 if i == 0 else 0) - (2 if i == len(counts) - 1 else 0)) / OPS_PER_LAYER))
                   for i, n in enumerate(counts)]

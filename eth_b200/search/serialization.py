@@ -45,11 +45,13 @@ def pipeline_to_pipe_dict(p, global_batch, num_layers):
     return {
         "global_batch_size": int(global_batch), "micro_batch_size": int(p.mbs), "num_stages": S,
         "num_gpus": [s.gpus for s in p.stages],
-        "checkpoint_activations": [max(r) > 0 for r in rec], "resharding_stages": [False] * S,
+        "checkpoint_activations": [max(r) > 0 for r in rec],
+        # a stage in the swapped sharding converts placements at its GEMMs' inputs and outputs
+        "resharding_stages": [bool(getattr(s, "algo", 0)) for s in p.stages],
         "num_ops_in_each_stage": ops,
         "model_parallel_size_of_each_op": [[s.tp] * n for s, n in zip(p.stages, ops)],
         "data_parallel_size_of_each_op": [[s.dp] * n for s, n in zip(p.stages, ops)],
-        "algo_of_each_op": [[0] * n for n in ops],
+        "algo_of_each_op": [[int(getattr(s, "algo", 0))] * n for s, n in zip(p.stages, ops)],
         "recompute_ops": rec,
     }
 
@@ -87,7 +89,8 @@ def load_initial_plan(path, num_layers, gpu_types):
         gpus = d["num_gpus"][i]
         types = tuple(sorted(set(gpu_types[gpu_cursor:gpu_cursor + gpus]))) or (gpu_types[0],)
         stages.append(StagePlan(cursor, cursor + n, gpus, d["model_parallel_size_of_each_op"][i][0],
-                                d["data_parallel_size_of_each_op"][i][0], types))
+                                d["data_parallel_size_of_each_op"][i][0], types,
+                                algo=int((d.get("algo_of_each_op") or [[0]] * len(counts))[i][0])))
         cursor += n
         gpu_cursor += gpus
     return PipelinePlan(tuple(stages), int(d["micro_batch_size"]))

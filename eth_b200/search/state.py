@@ -61,6 +61,7 @@ class StagePlan:
     dp: int
     gpu_types: Tuple[str, ...]           # distinct GPU types among the stage's devices
     recompute: Tuple[int, ...] = ()      # 0/1 per op of the stage; () = none
+    algo: int = 0                        # 0: usual column-then-row sharding of the TP GEMMs, 1: swapped
 
     @property
     def num_ops(self) -> int:
@@ -95,7 +96,7 @@ class PipelinePlan:
         return PipelinePlan(tuple(stages), self.mbs)
 
     def key(self) -> tuple:
-        return (self.mbs,) + tuple((s.op_begin, s.op_end, s.tp, s.dp, s.gpus) for s in self.stages)
+        return (self.mbs,) + tuple((s.op_begin, s.op_end, s.tp, s.dp, s.gpus, s.algo) for s in self.stages)
 
 
 def plan_from_layers(layers: Sequence[int], shapes: Iterable[Tuple[int, int, int, Tuple[str, ...]]], mbs: int,

@@ -64,6 +64,11 @@ LAYOUTS = {
     "pp2-tp2-to-dp2": (4, [make_pipe([11, N_OPS - 11], [2, 1], [1, 2], gbs=8, mbs=4)]),
     "two-pipelines-hetero": (3, [make_pipe([N_OPS], [2], [1], gbs=4, mbs=4), make_pipe([N_OPS], [1], [1], gbs=4, mbs=2)]),
     "pp3-1f1b": (3, [make_pipe([11, 10, N_OPS - 21], [1, 1, 1], [1, 1, 1], gbs=8, mbs=2)]),
+    # algo 1: the four tensor-parallel GEMMs of a stage use the swapped sharding (qkv / GEMM-1 row-parallel,
+    # dense / GEMM-2 column-parallel) and convert placements at their own inputs and outputs
+    "tp2-algo1": (2, [dict(make_pipe([N_OPS], [2], [1], gbs=8, mbs=4, algo=[1]), resharding_stages=[True])]),
+    "pp2-tp2-algo1-then-algo0": (4, [dict(make_pipe([7, N_OPS - 7], [2, 2], [1, 1], gbs=8, mbs=4, algo=[1, 0]),
+                                          resharding_stages=[True, False])]),
 }
 
 
@@ -183,3 +188,13 @@ def test_dataset_batches_are_broadcast_inside_a_tp_group(tmp_path):
         assert torch.equal(r0[key], r1[key])
     assert torch.equal(r0["tokens"][:, 1:], r0["labels"][:, :-1])
     assert r0["loss"] == r1["loss"] and r0["loss"] == r0["loss"]
+
+
+def test_algo1_needs_a_resharding_stage():
+    from eth_b200.runtime.arguments import parse_args
+    from eth_b200.runtime.engine import TrainEngine
+    cfg = _config([make_pipe([N_OPS], [2], [1], gbs=8, mbs=4, algo=[1])])
+    args = parse_args(["--device", "cpu", "--vocab-size", str(VOCAB), "--distributed-backend", "gloo"], config=cfg,
+                      rank=0, world_size=2)
+    with pytest.raises(ValueError, match="resharding_stages"):
+        TrainEngine(args, device="cpu")

@@ -140,3 +140,35 @@ def test_permuted_placement_wins_on_a_two_type_cluster(two_types, tmp_path):
     assert times == sorted(times) and len(times) == len(ranked)
     assert (out / "csv" / "eth_gpt_trend.csv").read_text().count("\n") >= 2
     normalize_flexpipe_config(json.loads((out / "top_configs" / "eth_gpt_hybrid.json").read_text()))
+
+
+def test_swapped_sharding_is_chosen_where_the_profile_says_it_is_faster(tmp_path):
+    """A profile whose algo-1 GEMM rows are much cheaper at TP2: the local search flips the stage to
+    algo 1, and the serialised plan carries algo 1 with resharding enabled for that stage."""
+    import csv
+    d = tmp_path / "fast-gpu" / "gpt_1_3B"
+    generate(str(d), "1_3B", "fast-gpu", (1, 2), seed=0)
+    os.replace(d / "p2p_intra_node.csv", tmp_path / "fast-gpu" / "p2p_intra_node.csv")
+    gemms = ("enc-attention-qkv", "enc-attention-dense", "enc-MLP-GEMM-1", "enc-MLP-GEMM-2")
+    for mbs in MBS:
+        path = d / f"gpt_1_3B_mbs{mbs}_tp2_algo1.csv"
+        rows = list(csv.reader(open(path)))
+        for r in rows[1:]:
+            if r[0] in gemms:
+                r[1], r[2] = f"{float(r[1]) * 0.4:.3f}", f"{float(r[2]) * 0.4:.3f}"
+        csv.writer(open(path, "w", newline="")).writerows(rows)
+    layers = 2
+    profiles = {"fast-gpu": ProfileDB.load(str(d), "fast-gpu", "1_3B", MBS, 2, p2p_dir=str(tmp_path / "fast-gpu"))}
+    cost = CostModel(profiles, layers, {"fast-gpu": 64000.0}, CostOptions())
+    refiner = Refiner(cost, layers, "layer", MBS, 2, 16, 2048, max_hops=3, allow_exchange=False)
+    start = plan_from_layers([layers], [(2, 2, 1, ("fast-gpu",))], 4, layers)
+    best = refiner.refine(start, time.time() + 10)
+    assert best.plan.stages[0].algo == 1 and best.per_sample_us() < refiner.score(start).per_sample_us()
+    searcher = S.PipelineSearcher(cost, layers, 2, [4], 16, 2048, time.time() + 10, refiner=refiner)
+    result = searcher._from_scored(best, "multi-hop")
+    pipe = S.pipeline_to_pipe_dict(result, 64, layers)
+    assert pipe["algo_of_each_op"] == [[1] * total_ops(layers)] and pipe["resharding_stages"] == [True]
+    cfg = S.make_config([pipe], num_layers=layers, hidden_size=2048, num_attention_heads=16, seq_length=2048)
+    assert normalize_flexpipe_config(cfg)["pipe"][0]["algo_of_each_op"][0][0] == 1
+    # and it round-trips as a start point
+    assert searcher._to_plan(result).stages[0].algo == 1
