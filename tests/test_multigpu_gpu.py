@@ -85,14 +85,15 @@ def test_peer_allreduce_two_gpus():
         assert max(errs) < 1e-4, errs
 
 
-def _engine_loss(rank, world, tp):
+def _engine_loss(rank, world, tp, algo=0):
     from eth_b200.contract.config import make_config, make_pipe, manifest_size
     from eth_b200.ops import native
     from eth_b200.runtime.arguments import parse_args
     from eth_b200.runtime.engine import TrainEngine
     layers = 2
-    cfg = make_config([make_pipe([manifest_size(layers)], [tp], [world // tp], gbs=8, mbs=4)], num_layers=layers,
-                      hidden_size=512, num_attention_heads=4, seq_length=256)
+    pipe = make_pipe([manifest_size(layers)], [tp], [world // tp], gbs=8, mbs=4, algo=[algo])
+    pipe["resharding_stages"] = [bool(algo)]
+    cfg = make_config([pipe], num_layers=layers, hidden_size=512, num_attention_heads=4, seq_length=256)
     args = parse_args(["--bf16", "--hidden-dropout", "0.0", "--vocab-size", "2000", "--lr", "1e-3",
                        "--lr-warmup-fraction", "0.0", "--make-vocab-size-divisible-by", "64"],
                       config=cfg, rank=rank, world_size=world)
@@ -110,9 +111,10 @@ def test_engine_tp2_and_dp2_match_single_gpu():
     single = run_ranks(1, _engine_loss, 1, backend="nccl")[0]
     tp2 = run_ranks(2, _engine_loss, 2, backend="nccl")[0]
     dp2 = run_ranks(2, _engine_loss, 1, backend="nccl")[0]
-    for (l1, n1), (l2, n2), (l3, n3) in zip(single, tp2, dp2):
-        assert abs(l1 - l2) < 3e-2 and abs(l1 - l3) < 3e-2, (single, tp2, dp2)
-        assert abs(n1 - n2) / n1 < 5e-2 and abs(n1 - n3) / n1 < 5e-2, (single, tp2, dp2)
+    swapped = run_ranks(2, _engine_loss, 2, 1, backend="nccl")[0]   # TP2 with the GEMMs in their other sharding
+    for (l1, n1), (l2, n2), (l3, n3), (l4, n4) in zip(single, tp2, dp2, swapped):
+        assert abs(l1 - l2) < 3e-2 and abs(l1 - l3) < 3e-2 and abs(l1 - l4) < 3e-2, (single, tp2, dp2, swapped)
+        assert max(abs(n1 - n2), abs(n1 - n3), abs(n1 - n4)) / n1 < 5e-2, (single, tp2, dp2, swapped)
 
 
 def _fused_rs_ag(rank, world):
