@@ -42,18 +42,39 @@ def snapshot_rank(engine, phase: str, iteration: int, out_dir: str, extra=None) 
             "logical_param_id": e.spec.logical_id, "full_shape": tuple(e.spec.full_shape),
             "partition_dim": e.spec.partition_dim, "partition_stride": e.spec.partition_stride,
             "tp_degree": ps.tp_size, "tp_rank": ps.tp_rank, "dp_rank": ps.dp_rank, "pipeline_id": ps.pipeline_id,
-            "stage_id": ps.stage_id, "param": e.param.detach().float().cpu(),
+            "stage_id": ps.stage_id, "weight_decay": bool(e.spec.weight_decay),
+            "param": e.param.detach().float().cpu(),
             "main_grad": e.param.main_grad.detach().float().cpu(),
             "master": st.get("master", e.param).detach().float().cpu(),
             "exp_avg": st["exp_avg"].detach().cpu(), "exp_avg_sq": st["exp_avg_sq"].detach().cpu()})
-    payload = {"version": 1, "global_rank": engine.args.rank, "phase": phase, "iteration": iteration,
+    loss_scale = engine.scaler.value() if engine.scaler is not None else 1.0
+    payload = {"version": 2, "global_rank": engine.args.rank, "phase": phase, "iteration": iteration,
                "records": records, "metrics": dict(extra or {}), "lr": opt.lr, "step_count": opt.step_count,
-               "loss_scale": engine.scaler.value() if engine.scaler is not None else 1.0}
+               "loss_scale": loss_scale,
+               "clock": {"learning_rate": opt.lr, "global_data_cursor": engine.clock.global_data_cursor,
+                         "successful_optimizer_steps": engine.clock.successful_optimizer_steps,
+                         "loss_scale": loss_scale},
+               "run": run_metadata(engine)}
     d = os.path.join(out_dir, f"rank-{engine.args.rank:05d}")
     os.makedirs(d, exist_ok=True)
     path = os.path.join(d, f"iter-{iteration:05d}-{phase}.pt")
     torch.save(payload, path)
     return path
+
+
+def run_metadata(engine) -> dict:
+    """What an offline checker needs to re-derive an iteration: batch and loss normalisation,
+    clipping, the optimizer's hyper-parameters, the learning-rate schedule, the loss-scale mode."""
+    a, opt, sched = engine.args, engine.optimizer, engine.lr_scheduler
+    dynamic = engine.scaler is not None and getattr(a, "loss_scale", None) is None
+    return {"total_gbs": int(a.total_gbs), "nominal_global_loss_scale": float(a.nominal_global_loss_scale),
+            "clip_grad": float(a.clip_grad), "optimizer": getattr(a, "optimizer", "adam"),
+            "beta1": float(getattr(a, "adam_beta1", 0.9)), "beta2": float(getattr(a, "adam_beta2", 0.999)),
+            "eps": float(getattr(a, "adam_eps", 1e-8)), "weight_decay": float(getattr(a, "weight_decay", 0.0)),
+            "lr": sched.max_lr, "min_lr": sched.min_lr, "lr_warmup_samples": int(sched.warmup_steps),
+            "lr_decay_samples": int(sched.decay_steps), "lr_decay_style": sched.decay_style,
+            "loss_scale_mode": "none" if engine.scaler is None else ("dynamic" if dynamic else "static"),
+            "world_size": int(a.world_size)}
 
 
 def load_snapshots(run_dir: str, iteration: int, phase: str) -> List[dict]:
@@ -133,3 +154,97 @@ def adamw_reference_step(param, grad, exp_avg, exp_avg_sq, step, lr, beta1, beta
     denom = v.sqrt() / math.sqrt(1 - beta2 ** step) + eps
     p = p - lr / (1 - beta1 ** step) * m / denom
     return p, m, v
+
+
+# ------------------------------------------------------------------------------------------
+# references that need every holder of a parameter, not one replica
+# ------------------------------------------------------------------------------------------
+def holders(snapshots: Iterable[dict]) -> List[Tuple[int, int, int]]:
+    """Every (pipeline, DP rank, stage) that holds parameters. A tied weight has two holders in one
+    replica (the embedding stage and the head stage), pipelines with different layouts hold the
+    same logical parameters under different TP degrees."""
+    return sorted({(r["pipeline_id"], r["dp_rank"], r["stage_id"]) for s in snapshots for r in s["records"]})
+
+
+def reconstruct_holder(snapshots: Iterable[dict], field: str, holder: Tuple[int, int, int]) -> Dict[str, torch.Tensor]:
+    """Full logical tensors of `field` from the shards one holder's TP ranks wrote, each record
+    laid out by its own (tp_degree, partition_dim, stride): holders may disagree on the layout."""
+    pid, dpr, stage = holder
+    narrowed = [{"records": [r for r in s["records"]
+                             if (r["pipeline_id"], r["dp_rank"], r["stage_id"]) == holder]} for s in snapshots]
+    return reconstruct(narrowed, field, pid, dpr)
+
+
+def full_gradient_reference(pre_sync: Iterable[dict]) -> Dict[str, torch.Tensor]:
+    """What gradient synchronisation has to produce: for every logical parameter the sum, in fp64,
+    of the full gradients of all its holders before the sync (all pipelines, all DP replicas, both
+    ends of a tied weight). Reference: evidence.py:418-449 (there followed by the normalisation
+    scale, which this engine applies in the optimizer instead)."""
+    pre_sync = list(pre_sync)
+    total: Dict[str, torch.Tensor] = {}
+    for holder in holders(pre_sync):
+        for lid, g in reconstruct_holder(pre_sync, "main_grad", holder).items():
+            total[lid] = g.double() if lid not in total else total[lid] + g.double()
+    return total
+
+
+def reconstruct_agreed(snapshots: Iterable[dict], field: str, rtol: float = 0.0) -> Tuple[Dict[str, torch.Tensor], List[str]]:
+    """(logical tensors, disagreements): `field` reconstructed from every holder; all holders of a
+    logical parameter must agree within `rtol` (relative to the largest magnitude)."""
+    snapshots = list(snapshots)
+    agreed: Dict[str, torch.Tensor] = {}
+    problems: List[str] = []
+    for holder in holders(snapshots):
+        for lid, value in reconstruct_holder(snapshots, field, holder).items():
+            if lid not in agreed:
+                agreed[lid] = value
+                continue
+            bound = rtol * float(agreed[lid].abs().max()) if rtol else 0.0
+            if value.shape != agreed[lid].shape or float((value.double() - agreed[lid].double()).abs().max()) > bound:
+                problems.append(f"{field} of {lid} differs at holder (pipeline, dp, stage) = {holder}")
+    return agreed, problems
+
+
+def compare_logical_tensors(actual: Dict[str, torch.Tensor], expected: Dict[str, torch.Tensor], rtol: float,
+                            atol: float) -> dict:
+    """Per-parameter report: worst absolute and relative error with their coordinates, and whether
+    |actual - expected| <= atol + rtol * |expected| holds everywhere (non-finite values must match
+    in kind and sign)."""
+    rows = []
+    for lid in sorted(set(actual) | set(expected)):
+        if lid not in actual or lid not in expected:
+            rows.append({"logical_param_id": lid, "passed": False,
+                         "error": "missing actual" if lid not in actual else "missing expected"})
+            continue
+        a, e = actual[lid].detach().double().cpu(), expected[lid].detach().double().cpu()
+        if a.shape != e.shape:
+            rows.append({"logical_param_id": lid, "passed": False, "error": "shape mismatch",
+                         "actual_shape": list(a.shape), "expected_shape": list(e.shape)})
+            continue
+        finite = torch.isfinite(a) & torch.isfinite(e)
+        same_special = (~finite) & ((torch.isinf(a) & torch.isinf(e) & (torch.signbit(a) == torch.signbit(e)))
+                                    | (torch.isnan(a) & torch.isnan(e)))
+        diff = torch.where(finite, (a - e).abs(), torch.where(same_special, torch.zeros_like(a),
+                                                              torch.full_like(a, float("inf"))))
+        rel = diff / e.abs().clamp_min(max(atol, 1e-300))
+        i_abs, i_rel = int(diff.reshape(-1).argmax()), int(rel.reshape(-1).argmax())
+        where = lambda i: [int(v) for v in torch.unravel_index(torch.tensor(i), a.shape)] if a.dim() else []
+        rows.append({"logical_param_id": lid, "passed": bool((diff <= atol + rtol * e.abs()).all()),
+                     "max_abs_error": float(diff.reshape(-1)[i_abs]), "max_abs_index": where(i_abs),
+                     "max_rel_error": float(rel.reshape(-1)[i_rel]), "max_rel_index": where(i_rel)})
+    return {"passed": all(r["passed"] for r in rows), "rtol": rtol, "atol": atol, "parameters": rows}
+
+
+def expected_learning_rate(run: dict, samples: int) -> float:
+    """The schedule restated from the run metadata alone: linear warm-up over `lr_warmup_samples`,
+    then constant, or linear / cosine decay to `min_lr` at `lr_decay_samples`."""
+    top, low, warm, end = run["lr"], run["min_lr"], run["lr_warmup_samples"], run["lr_decay_samples"]
+    if warm > 0 and samples <= warm:
+        return top * samples / warm
+    if run["lr_decay_style"] == "constant":
+        return top
+    if samples > end:
+        return low
+    progress = (samples - warm) / (end - warm)
+    shape = 1.0 - progress if run["lr_decay_style"] == "linear" else 0.5 * (math.cos(math.pi * progress) + 1.0)
+    return low + shape * (top - low)

@@ -376,10 +376,12 @@ class TrainEngine:
             schedules.forward_backward_1f1b(self, n_mb)
         raw_ops.join_async_wgrad(self.device)
         # global loss weight -> normalisation factor (device scalar)
+        local_weight = float(self.loss_acc[1]) if evidence_dir else None
         self.coll.all_reduce_sum(self.loss_acc)
         normalization = a.nominal_global_loss_scale / self.loss_acc[1]
         if evidence_dir:
-            self._evidence("pre_sync", evidence_dir)
+            self._evidence("pre_sync", evidence_dir, local_loss_weight=local_weight,
+                           global_loss_weight=float(self.loss_acc[1]), normalization_scale=float(normalization))
         if self._needs_reduction:
             gs = self._grad_sync_events()
             if gs:
@@ -405,11 +407,13 @@ class TrainEngine:
                 detail = f" (this rank: {err})"
             raise RuntimeError("a bounded device wait ran out on some rank during this iteration; the update was "
                                f"skipped on every rank{detail}")
-        if evidence_dir:
-            self._evidence("post_step", evidence_dir, update_successful=bool(ok))
         increment = self.clock.after_attempt(ok)
         if ok:
             self.lr_scheduler.step(increment)
+        if evidence_dir:   # after the clock moved: the snapshot's clock is the state the next iteration starts from
+            clip = min(1.0, a.clip_grad / (grad_norm + 1.0e-6)) if (ok and grad_norm is not None and a.clip_grad > 0) else 1.0
+            self._evidence("post_step", evidence_dir, update_successful=bool(ok), grad_norm=grad_norm,
+                           clip_coefficient=clip)
         self.iteration += 1
         stats = {"iteration": self.iteration, "update_successful": ok, "grad_norm": grad_norm,
                  "loss_scale": self.scaler.value() if self.scaler is not None else 1.0, "lr": self.optimizer.lr,
