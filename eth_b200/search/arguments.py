@@ -64,6 +64,9 @@ def build_parser():
     g.add_argument("--config-suffix", type=str, default="", help="Suffix of generated file names.")
     g.add_argument("--save-prefix", type=str, default="eth_gpt", help="Prefix of generated file names.")
     g.add_argument("--num-of-saved-configs", type=int, default=1, help="How many top configs to keep.")
+    g.add_argument("--multi-process", action="store_true",
+                   help="Solve the device groups in worker processes before combining them.")
+    g.add_argument("--num-multi-process", type=int, default=4, help="Worker processes of --multi-process.")
     g.add_argument("--reduce-output", action="store_true", help="Less console output.")
     return p
 

@@ -320,11 +320,10 @@ def plan_signature(plan: "HybridPlan") -> tuple:
                  for p, b in zip(plan.pipelines, plan.batch_sizes)) + (plan.node_order,)
 
 
-def run_search(args) -> Tuple[Optional[HybridPlan], dict]:
-    t0 = time.time()
-    deadline = t0 + float(args.time_budget_total)
-    log = SearchLog(args.log_path, quiet=args.reduce_output)
-    timers = Timers()
+def build_searcher(args, deadline: float, timers: Optional[Timers] = None):
+    """(cost model, refiner or None, pipeline searcher, memory, tflops) for a parsed argument set:
+    what the driver and every worker process of a multi-process search set up alike."""
+    timers = timers or Timers()
     gpu_types = sorted({n["GPU"] for n in args.nodes})
     profiles = {}
     with timers.phase("load-profiles"):
@@ -352,16 +351,95 @@ def run_search(args) -> Tuple[Optional[HybridPlan], dict]:
                                 args.hidden_size, deadline, homo_stage=args.homo_stage, refiner=refiner,
                                 refine_seconds=float(args.time_budget_total) * args.refine_share,
                                 elastic=args.elastic_time, initial_point=args.initial_point)
+    return cost, refiner, searcher, memory, tflops
+
+
+def search_nodes(args):
+    """(nodes as searched, GPUs per node): a single node may be split into pipelines of whole GPUs."""
+    base_nodes = list(args.nodes)                # list of {"GPU": type, "GPU_NUM": n}
+    gpn = max(n["GPU_NUM"] for n in base_nodes)
+    if len(base_nodes) == 1 and base_nodes[0]["GPU_NUM"] > 1 and args.max_num_pipeline > 1:
+        base_nodes = [{"GPU": base_nodes[0]["GPU"], "GPU_NUM": 1} for _ in range(base_nodes[0]["GPU_NUM"])]
+    return base_nodes, gpn
+
+
+def device_groups_needed(args) -> List[Tuple[str, ...]]:
+    """Every distinct device group (tuple of GPU types, in device order) that some node order and
+    some contiguous split into pipelines will ask the pipeline searcher about."""
+    base_nodes, _ = search_nodes(args)
+    n_nodes = len(base_nodes)
+    orders = node_orders(base_nodes, args.max_node_orders) if args.permute_nodes else [tuple(range(n_nodes))]
+    seen, out = set(), []
+    for order in orders:
+        nodes = [base_nodes[i] for i in order]
+        for a in range(n_nodes):
+            for b in range(a + 1, n_nodes + 1):
+                if n_nodes - (b - a) < args.min_num_pipeline - 1:
+                    continue      # too few nodes left for the other pipelines
+                g = tuple(t for n in nodes[a:b] for t in [n["GPU"]] * n["GPU_NUM"])
+                if g not in seen:
+                    seen.add(g)
+                    out.append(g)
+    return out
+
+
+def _solve_groups(payload):
+    """Worker of the multi-process search: solve a share of the device groups, return the cache entries."""
+    args, groups, deadline = payload
+    _, refiner, searcher, _, _ = build_searcher(args, deadline)
+    _, gpn = search_nodes(args)
+    stage_range = (args.start_num_stages, args.end_num_stages)
+    solved = [(g, searcher.best(g, stage_range, gpn)) for g in groups]
+    return solved, searcher.evaluated, searcher.refined, refiner.evaluated if refiner else 0
+
+
+def presolve_in_processes(args, searcher, deadline: float, log) -> dict:
+    """Solve all device groups in `--num-multi-process` worker processes and fill the searcher's
+    cache, so that the driver loop below only combines cached results (reference: one process per
+    (stage count, device group, node order), eth/searching/search.py:961-1021; here the unit is the
+    device group, which is what the cache is keyed by). Largest groups first, dealt round-robin."""
+    import multiprocessing
+    groups = sorted(device_groups_needed(args), key=lambda g: -len(g))
+    workers = max(1, min(int(args.num_multi_process), len(groups)))
+    shares = [groups[i::workers] for i in range(workers)]
+    stage_range = (args.start_num_stages, args.end_num_stages)
+    stats = {"processes": workers, "device_groups": len(groups), "evaluated": 0, "refined": 0, "refine_evaluations": 0}
+    quiet = argparse_copy(args)
+    with multiprocessing.get_context("spawn").Pool(workers) as pool:
+        for solved, evaluated, refined, refine_evals in pool.imap_unordered(_solve_groups, [(quiet, s, deadline) for s in shares]):
+            for g, res in solved:
+                searcher.cache[(g, stage_range)] = res
+            stats["evaluated"] += evaluated
+            stats["refined"] += refined
+            stats["refine_evaluations"] += refine_evals
+    log.write(f"multi-process: {len(groups)} device groups solved in {workers} processes")
+    return stats
+
+
+def argparse_copy(args):
+    """The argument set a worker gets: the same search, nothing written from the worker."""
+    import copy
+    quiet = copy.copy(args)
+    quiet.log_path, quiet.reduce_output = None, True
+    return quiet
+
+
+def run_search(args) -> Tuple[Optional[HybridPlan], dict]:
+    t0 = time.time()
+    deadline = t0 + float(args.time_budget_total)
+    log = SearchLog(args.log_path, quiet=args.reduce_output)
+    timers = Timers()
+    cost, refiner, searcher, memory, tflops = build_searcher(args, deadline, timers)
     bounds = ThroughputBounds(tflops, memory)
+    presolved = None
+    if getattr(args, "multi_process", False) and int(getattr(args, "num_multi_process", 1)) > 1:
+        with timers.phase("multi-process-presolve"):
+            presolved = presolve_in_processes(args, searcher, deadline, log)
     ranking = Ranking(args.num_of_saved_configs, plan_signature)
     stage_range = (args.start_num_stages, args.end_num_stages)
     stats = {"splits_evaluated": 0, "splits_pruned": 0, "node_orders": 0}
 
-    base_nodes = list(args.nodes)                # list of {"GPU": type, "GPU_NUM": n}
-    gpn = max(n["GPU_NUM"] for n in base_nodes)
-    # a single node may still be split into several pipelines of whole GPUs
-    if len(base_nodes) == 1 and base_nodes[0]["GPU_NUM"] > 1 and args.max_num_pipeline > 1:
-        base_nodes = [{"GPU": base_nodes[0]["GPU"], "GPU_NUM": 1} for _ in range(base_nodes[0]["GPU_NUM"])]
+    base_nodes, gpn = search_nodes(args)
     n_nodes = len(base_nodes)
     max_pipes = min(args.max_num_pipeline, n_nodes)
 
@@ -433,6 +511,11 @@ def run_search(args) -> Tuple[Optional[HybridPlan], dict]:
                               f"iteration={plan.iteration_us / 1e3:.2f} ms throughput={plan.throughput:.2f} samples/s")
     stats.update(seconds=time.time() - t0, pipelines_evaluated=searcher.evaluated, groups_refined=searcher.refined,
                  refine_evaluations=refiner.evaluated if refiner else 0, timers=timers.report())
+    if presolved is not None:
+        stats["multi_process"] = presolved
+        stats["pipelines_evaluated"] += presolved["evaluated"]
+        stats["groups_refined"] += presolved["refined"]
+        stats["refine_evaluations"] += presolved["refine_evaluations"]
     stats["ranking"] = ranking
     return ranking.best, stats
 

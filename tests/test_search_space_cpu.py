@@ -172,3 +172,16 @@ def test_swapped_sharding_is_chosen_where_the_profile_says_it_is_faster(tmp_path
     assert normalize_flexpipe_config(cfg)["pipe"][0]["algo_of_each_op"][0][0] == 1
     # and it round-trips as a start point
     assert searcher._to_plan(result).stages[0].algo == 1
+
+
+def test_multi_process_search_finds_the_same_plan(two_types, tmp_path):
+    """Device groups solved in worker processes, combined by the driver: same plan, same config hash
+    as the single-process search, and the driver itself evaluates no pipeline."""
+    one, s_one, _ = _search(two_types, tmp_path, "one", [])
+    many, s_many, _ = _search(two_types, tmp_path, "many", ["--multi-process", "--num-multi-process", "3"])
+    assert s_many["config_hash"] == s_one["config_hash"]
+    assert abs(s_many["iteration_ms"] - s_one["iteration_ms"]) < 1e-9
+    mp = s_many["multi_process"]
+    assert mp["processes"] == 3 and mp["device_groups"] >= 4
+    assert mp["evaluated"] == s_many["pipelines_evaluated"] > 0        # every evaluation happened in a worker
+    assert S.plan_signature(many) == S.plan_signature(one)
