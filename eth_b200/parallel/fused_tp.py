@@ -68,13 +68,13 @@ class FusedTPBackend:
         # slot per CTA and source, because slots are assigned per CTA
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.stage_elems = rows * cols + (sms + 1) * self.world * 128 * 256
-        self.stage = SymmetricBuffer(self.stage_elems * esize, group_ranks, my_rank, group, device)
-        self.out = SymmetricBuffer(self.out_slot_bytes * RING, group_ranks, my_rank, group, device)
+        self.stage = SymmetricBuffer(self.stage_elems * esize, group_ranks, my_rank, group, device, holds_data=True)
+        self.out = SymmetricBuffer(self.out_slot_bytes * RING, group_ranks, my_rank, group, device, holds_data=True)
         self.flags = SymmetricBuffer(MAX_TILES * 9 * 4, group_ranks, my_rank, group, device)
         # all-gather + GEMM: a ring of [max_tokens, hidden-or-wider] operand buffers and their own flags
         self.ag_cols = max(hidden, cols)
         self.ag_slot_bytes = rows * self.ag_cols * esize
-        self.ag = SymmetricBuffer(self.ag_slot_bytes * RING, group_ranks, my_rank, group, device)
+        self.ag = SymmetricBuffer(self.ag_slot_bytes * RING, group_ranks, my_rank, group, device, holds_data=True)
         self.ag_flags = SymmetricBuffer((64 + rows // 8) * 4, group_ranks, my_rank, group, device)
         self.ag_slot = 0
         self.rank = self.stage.index

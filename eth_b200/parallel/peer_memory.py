@@ -7,6 +7,7 @@ per-rank base pointers.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Sequence
 
 import torch
@@ -18,7 +19,14 @@ from ..ops import native
 class SymmetricBuffer:
     """One symmetric allocation: `ptrs[i]` is the address of group-rank i's copy in this process."""
 
-    def __init__(self, nbytes: int, group_ranks: Sequence[int], my_global_rank: int, group, device):
+    def __init__(self, nbytes: int, group_ranks: Sequence[int], my_global_rank: int, group, device,
+                 holds_data: bool = False):
+        """`holds_data`: the buffer is a staging area that peers fill before it is read (not flags or
+        counters, which must start at zero). With ETHB_POISON_STAGING=1 in the environment such a
+        buffer starts as all-ones bytes, a NaN in every floating-point type, instead of zeros: a
+        kernel that reads a slot before its producer wrote it then yields NaNs, which the overflow
+        check of the optimizer and every numerics test catch, where stale zeros would pass silently.
+        (A stand-in for an initcheck tool on memory that other GPUs write.)"""
         lib = native.lib()
         self.nbytes = int(nbytes)
         self.group_ranks = tuple(group_ranks)
@@ -36,6 +44,10 @@ class SymmetricBuffer:
                 p = lib.peer_open(h)
                 self._opened.append(p)
                 self.ptrs.append(p)
+        if holds_data and os.environ.get("ETHB_POISON_STAGING", "0") == "1":
+            import torch as _torch
+            self.tensor((self.nbytes,), _torch.uint8).fill_(0xFF)
+            _torch.cuda.synchronize(self.device)
         # nobody may touch a peer's buffer before everyone has mapped it
         dist.barrier(group=group)
 

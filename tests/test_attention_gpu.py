@@ -18,7 +18,8 @@ def _rel_err(a, b):
     a, b = a.float(), b.float()
     fro = ((a - b).norm() / (b.norm() + 1e-12)).item()
     worst = ((a - b).abs().max() / (b.abs().max() + 1e-12)).item()
-    return max(fro, worst)
+    err = max(fro, worst)
+    return err if err == err else float("inf")   # a NaN anywhere must fail every `< tolerance` check
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
