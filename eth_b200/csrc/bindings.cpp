@@ -555,6 +555,36 @@ void peer_flags(const std::vector<int64_t>& flags, int64_t rank, int64_t epoch, 
                          status.data_ptr<int>(), cur_stream()), "peer_flags");
 }
 
+ethb::FlagList to_flag_list(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(!ptrs.empty() && ptrs.size() <= 2 * ethb::kMaxPeers, "between 1 and 16 flag addresses");
+  ethb::FlagList f{};
+  f.count = static_cast<int>(ptrs.size());
+  for (size_t i = 0; i < ptrs.size(); ++i) {
+    TORCH_CHECK(ptrs[i] != 0 && ptrs[i] % 4 == 0, "flag addresses must be non-null and 4-byte aligned");
+    f.ptrs[i] = reinterpret_cast<int*>(ptrs[i]);
+  }
+  return f;
+}
+// Raw-address 2-D copy on the current stream of `device` (addresses may be peer-mapped).
+void peer_copy_2d(int64_t dst, int64_t dst_pitch, int64_t src, int64_t src_pitch, int64_t width_bytes, int64_t rows,
+                  int64_t device) {
+  TORCH_CHECK(dst != 0 && src != 0 && width_bytes >= 0 && rows >= 0, "bad copy arguments");
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  check(ethb::peer_copy_2d(reinterpret_cast<void*>(dst), static_cast<size_t>(dst_pitch),
+                           reinterpret_cast<const void*>(src), static_cast<size_t>(src_pitch),
+                           static_cast<size_t>(width_bytes), static_cast<size_t>(rows), cur_stream()),
+        "peer_copy_2d");
+}
+void flags_post(const std::vector<int64_t>& ptrs, int64_t value, int64_t device) {
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  check(ethb::flags_post(to_flag_list(ptrs), static_cast<int>(value), cur_stream()), "flags_post");
+}
+void flags_wait(const std::vector<int64_t>& ptrs, int64_t value, int64_t limit_scale, const Tensor& status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  check(ethb::flags_wait(to_flag_list(ptrs), static_cast<int>(value), static_cast<int>(limit_scale),
+                         status.data_ptr<int>(), cur_stream()), "flags_wait");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -605,4 +635,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_allreduce", &peer_allreduce);
   m.def("peer_reduce_pieces", &peer_reduce_pieces);
   m.def("peer_flags", &peer_flags);
+  m.def("peer_copy_2d", &peer_copy_2d);
+  m.def("flags_post", &flags_post);
+  m.def("flags_wait", &flags_wait);
 }

@@ -57,6 +57,20 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int target, int* stat
   return true;
 }
 
+__global__ void __launch_bounds__(32, 1) flags_post_kernel(FlagList flags, int value) {
+  if (threadIdx.x < flags.count) {
+    __threadfence_system();
+    st_release_sys(flags.ptrs[threadIdx.x], value);
+  }
+}
+
+// Waits up to `limit_scale` wait limits per flag; the first flag that gives up records the status.
+__global__ void __launch_bounds__(32, 1) flags_wait_kernel(FlagList flags, int value, int limit_scale, int* status) {
+  if (threadIdx.x >= flags.count) return;
+  for (int round = 0; round < limit_scale; ++round)
+    if (wait_flag_ge(flags.ptrs[threadIdx.x], value, round + 1 == limit_scale ? status : nullptr)) return;
+}
+
 __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* status) {
   const int p = threadIdx.x;
   if (p < world) {
@@ -254,6 +268,29 @@ cudaError_t peer_flags(const PeerPtrs& flags, int rank, int world, int epoch, in
                        int wait_base, int* status, cudaStream_t st) {
   if (world > kMaxPeers || world < 1) return cudaErrorInvalidValue;
   peer_flags_kernel<<<1, 32, 0, st>>>(flags, rank, world, epoch, signal_base, wait_base, status);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t peer_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                         size_t rows, cudaStream_t st) {
+  if (rows == 0 || width_bytes == 0) return cudaSuccess;
+  if (width_bytes > dst_pitch || width_bytes > src_pitch) return cudaErrorInvalidValue;
+  if (rows == 1 || (dst_pitch == width_bytes && src_pitch == width_bytes))
+    return cudaMemcpyAsync(dst, src, width_bytes * rows, cudaMemcpyDeviceToDevice, st);
+  return cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice, st);
+}
+
+cudaError_t flags_post(const FlagList& flags, int value, cudaStream_t st) {
+  if (flags.count < 1 || flags.count > 2 * kMaxPeers) return cudaErrorInvalidValue;
+  flags_post_kernel<<<1, 32, 0, st>>>(flags, value);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t flags_wait(const FlagList& flags, int value, int limit_scale, int* status, cudaStream_t st) {
+  if (flags.count < 1 || flags.count > 2 * kMaxPeers || limit_scale < 1 || limit_scale > 64) return cudaErrorInvalidValue;
+  flags_wait_kernel<<<1, 32, 0, st>>>(flags, value, limit_scale, status);
   count_launch();
   return cudaGetLastError();
 }

@@ -71,4 +71,21 @@ cudaError_t peer_reduce_pieces(const PieceReduceArgs& a, cudaStream_t st);
 cudaError_t peer_flags(const PeerPtrs& flags, int rank, int world, int epoch, int signal_base,
                        int wait_base, int* status, cudaStream_t st);
 
+// ---- pipeline transfers through peer memory ---------------------------------------------------
+// A stage boundary moves rectangles of activations (or gradients) from the ranks of one stage into
+// ring slots that the ranks of the next stage own. The payload travels as 2-D device-to-device
+// copies on a copy stream (`peer_copy_2d`: rows x width bytes, independent pitches), so no SM takes
+// part; afterwards the sender posts the micro-batch's sequence number to one flag per receiver
+// (`flags_post`, ordered behind the copies by the stream), and the receiver's compute stream waits
+// on its flags with a one-warp kernel (`flags_wait`, bounded: `limit_scale` times the wait limit)
+// before the first kernel that reads the slot.
+struct FlagList {
+  int* ptrs[2 * kMaxPeers];   // flag words, in this process' address space (local or peer-mapped)
+  int count;
+};
+cudaError_t peer_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                         size_t rows, cudaStream_t st);
+cudaError_t flags_post(const FlagList& flags, int value, cudaStream_t st);
+cudaError_t flags_wait(const FlagList& flags, int value, int limit_scale, int* status, cudaStream_t st);
+
 }  // namespace ethb

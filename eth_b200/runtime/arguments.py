@@ -101,6 +101,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--local_rank", "--local-rank", type=int, default=None, help="Local rank passed by the launcher.")
     g.add_argument("--tp-comm", default="auto", choices=["auto", "nccl", "fused"],
                    help="Tensor-parallel reductions: NCCL all-reduce, or the fused GEMM + peer all-reduce kernel.")
+    g.add_argument("--p2p-backend", default="auto", choices=["auto", "nccl", "peer"],
+                   help="Pipeline transfers: NCCL isend/irecv, or copies into ring slots in peer memory with flag "
+                        "waits (one node, non-interleaved schedule; auto picks it where it applies).")
     g.add_argument("--device", default=None, help="Device override (cpu for validation runs).")
 
     g = p.add_argument_group("data")

@@ -118,6 +118,10 @@ class TrainEngine:
         self.seq_len = cfg["seq_length"]
         self.comm = PipelineComm(ps, cfg["hidden_size"], self.seq_len, self.stage.input_spec, self.stage.output_spec,
                                  args.params_dtype, self.device) if ps.num_stages > 1 else None
+        # forward-only passes always use the NCCL channels; training may move to peer memory below
+        self.eval_comm = self.comm
+        self.p2p_backend = "nccl" if self.comm is not None else None
+        self._setup_peer_p2p(cfg)
         # interleaved pipelining: one set of channels per model chunk, wired to the stage that holds
         # the previous / next virtual stage
         self.chunk_comms = None
@@ -356,6 +360,35 @@ class TrainEngine:
         finally:
             if last:
                 self.stage.after_op_backward = None
+
+    def _setup_peer_p2p(self, cfg) -> None:
+        """Pipeline transfers of the 1F1B schedule through peer memory (`parallel/peer_p2p.py`) when
+        the whole job sits in one NVLink domain. The decision is the same on every rank (the inboxes
+        are allocated collectively), also on ranks whose pipeline has a single stage."""
+        a, ps = self.args, self.pstate
+        want = getattr(a, "p2p_backend", "auto")
+        multi_stage = any(p["num_stages"] > 1 for p in cfg["pipe"])
+        one_node = int(os.environ.get("LOCAL_WORLD_SIZE", a.world_size)) == a.world_size
+        usable = (self.device.type == "cuda" and a.world_size > 1 and multi_stage and one_node and ps.interleave == 1
+                  and a.world_size <= 8)
+        if want == "nccl" or not usable:
+            if want == "peer":
+                raise RuntimeError("--p2p-backend peer needs CUDA ranks of one node, a pipeline with several stages "
+                                   "and no interleaving")
+            return
+        from ..parallel.peer_p2p import PeerPipelineComm
+        try:
+            peer = PeerPipelineComm(ps, cfg["hidden_size"], self.seq_len, self.stage.input_spec, self.stage.output_spec,
+                                    a.params_dtype, self.device, tuple(range(a.world_size)))
+        except Exception as err:
+            if want == "peer":
+                raise
+            print(f"[eth_b200] rank {a.rank}: peer-memory pipeline transfers unavailable ({err}); using NCCL",
+                  flush=True)
+            return
+        if ps.num_stages > 1:
+            self.comm, self.p2p_backend = peer, "peer"
+        self._peer_p2p = peer
 
     # ------------------------------------------------------------------ one iteration
     def train_step(self, sync: Optional[bool] = None) -> Dict[str, object]:

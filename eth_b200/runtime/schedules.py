@@ -145,7 +145,7 @@ def forward_backward_interleaved(engine, num_microbatches: int) -> None:
 def forward_only(engine, num_microbatches: int) -> None:
     """Evaluation pass: forwards only, activations dropped at once (reference: schedules.py
     `forward_only=True` branches of the same schedules)."""
-    ps, comm = engine.pstate, engine.comm
+    ps, comm = engine.pstate, getattr(engine, "eval_comm", None) or engine.comm
     for i in range(num_microbatches):
         inputs = comm.recv_forward() if ps.num_stages > 1 else None
         out = engine.forward_step(i, inputs)
