@@ -121,6 +121,7 @@ def run_ours(opts):
             "--vocab-size", str(VOCAB)]
     if opts.bf16:
         argv = ["--bf16"] + argv[3:]
+    argv += opts.engine_args.split()
     args = parse_args(argv, config=config, rank=rank, world_size=world, local_rank=local_rank)
     engine = TrainEngine(args)
 
@@ -190,7 +191,7 @@ def run_ours(opts):
             "impl": "eth_b200",
             "config": {"model": "GPT-1.3B (24 layers, hidden 2048, 16 heads)", "global_batch": gbs,
                        "seq_len": MODEL["seq_length"], "micro_batch": MICRO_BATCH, "pipeline_micro_batch": MICRO_BATCH * dp,
-                       "parallelism": f"pp{pp}tp{tp}dp{dp}", "grad_sync": "block, 32 MiB buckets",
+                       "parallelism": f"pp{pp}tp{tp}dp{dp}", "grad_sync": "block, 32 MiB buckets", **({"engine_args": opts.engine_args} if opts.engine_args else {}),
                        "l2": "inputs larger than L2 (each step streams several GB of weights and activations)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / opts.steps,
@@ -221,6 +222,8 @@ def main():
     ap.add_argument("--layout", default=None,
                     help="pp,tp,dp to use instead of the default layout of --gpus (same model, batch per GPU and "
                          "metric; for studying a layout, e.g. 2,2,1 on four GPUs)")
+    ap.add_argument("--engine-args", default="",
+                    help="extra engine flags for studying a variant, e.g. '--p2p-backend nccl' (own arm only)")
     opts = ap.parse_args()
     if opts.layout:
         pp, tp, dp = (int(v) for v in opts.layout.split(","))

@@ -239,8 +239,15 @@ class TrainEngine:
         if self._overlap_by_op:
             self._sync_stream = torch.cuda.Stream(device=self.device)
 
-    def _reduce_ready_buckets(self, op_index: int) -> None:
-        buckets = self._overlap_by_op.get(op_index)
+    def _reduce_ready_buckets(self, op_index: Optional[int]) -> None:
+        """Start the peer reduction of the buckets whose first op is `op_index` (None: of all buckets
+        not started yet) on the sync stream, behind everything enqueued so far."""
+        if op_index is None:
+            # plan order: the same on every rank of a group, whatever ops the rank holds
+            buckets = sorted((b for bs in self._overlap_by_op.values() for b in bs
+                              if b.bucket_id not in self._overlap_done), key=lambda b: b.bucket_id)
+        else:
+            buckets = self._overlap_by_op.get(op_index)
         if not buckets:
             return
         ready = torch.cuda.Event()
@@ -351,8 +358,15 @@ class TrainEngine:
             rec = self.stage.context_of(mb_index, chunk)["mb"]
             scale = self.scaler.value() if self.scaler is not None else 1.0
             grad_outputs = {"output": rec.loss_mask * (scale / self.args.nominal_global_loss_scale)}
-        # start reductions during the very last backward of the iteration (chunk 0 runs last when interleaved)
-        last = self._sync_stream is not None and mb_index == self.pstate.num_microbatches - 1 and ps.interleave == 1
+        # Start reductions during the very last backward of the iteration -- without pipeline stages only.
+        # A reduction begins with a wait for the group's peers. The tied embedding's group spans the
+        # first and the last stage, and the first stage cannot arrive before it has received the last
+        # gradient from downstream, which this rank sends after this backward: a wait enqueued now
+        # could sit in front of that send (streams may share a hardware queue) and close a cycle
+        # that only the wait limit breaks. With stages, reductions start after the schedule instead
+        # (`train_step`), when every send of the iteration has been enqueued.
+        last = (self._sync_stream is not None and mb_index == self.pstate.num_microbatches - 1 and ps.interleave == 1
+                and ps.num_stages == 1)
         if last:
             self.stage.after_op_backward = self._reduce_ready_buckets
         try:
@@ -407,6 +421,10 @@ class TrainEngine:
             schedules.forward_backward_interleaved(self, n_mb)
         else:
             schedules.forward_backward_1f1b(self, n_mb)
+            if self._sync_stream is not None:
+                # later stages finish their last backward while earlier ones still drain the pipeline:
+                # their reductions run beside that
+                self._reduce_ready_buckets(None)
         raw_ops.join_async_wgrad(self.device)
         # global loss weight -> normalisation factor (device scalar)
         local_weight = float(self.loss_acc[1]) if evidence_dir else None

@@ -301,6 +301,6 @@ def test_pipeline_transfers_through_peer_memory_match_nccl(cut):
     for r in (0, 1):
         diff = (peer[r]["params"] - nccl[r]["params"]).abs()
         # same kernels on the same data: only the embedding's atomic accumulation order may differ
-        assert diff.max().item() <= 2 ** -7 and diff.mean().item() < 1e-6, (r, diff.max().item(), diff.mean().item())
+        assert diff.max().item() <= 2 ** -7 and diff.mean().item() < 1e-5, (r, diff.max().item(), diff.mean().item())
     for a, b in zip(peer[1]["losses"] + [peer[1]["eval"]], nccl[1]["losses"] + [nccl[1]["eval"]]):
         assert abs(a - b) < 2e-3 and a == a, (peer[1], nccl[1])
