@@ -141,3 +141,53 @@ def apply_reshard(x: torch.Tensor, step: ReshardStep, group=None, group_rank: Op
             dist.all_to_all(recv, send, group=group)
         return torch.cat(recv, dim=step.src_dim)
     raise ValueError(f"unknown primitive {step.primitive!r}")
+
+
+# ------------------------------------------------------------------------------------------
+# autograd adapters (library use; the stage program calls `apply_reshard` with explicit duals)
+# ------------------------------------------------------------------------------------------
+class _Reshard(torch.autograd.Function):
+    """One placement change whose backward is its dual, whatever the primitive: the table `DUAL`
+    replaces one autograd class per primitive (reference: mpu/mappings.py:212-303)."""
+
+    @staticmethod
+    def forward(ctx, x, step, group, group_rank):
+        ctx.step, ctx.group, ctx.group_rank = step, group, group_rank
+        return apply_reshard(x, step, group, group_rank)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return apply_reshard(grad.contiguous(), ctx.step.dual(), ctx.group, ctx.group_rank), None, None, None
+
+
+def reshard(x: torch.Tensor, step: ReshardStep, group=None, group_rank: Optional[int] = None) -> torch.Tensor:
+    """`apply_reshard` that autograd can differentiate."""
+    if step.primitive == "identity" and step.group_size <= 1:
+        return x
+    return _Reshard.apply(x, step, group, group_rank)
+
+
+def tensor_adapter(x: torch.Tensor, src_spec, dst_spec, group=None, group_rank: Optional[int] = None) -> torch.Tensor:
+    """Move `x` from placement `src_spec` to `dst_spec` (reference: mpu/mappings.py:381-467)."""
+    return reshard(x, plan_reshard(src_spec, dst_spec), group, group_rank)
+
+
+def copy_to_region(x, group=None):
+    """Identity forward, all-reduce backward: the input of a column-parallel layer."""
+    n = dist.get_world_size(group)
+    return reshard(x, ReshardStep("identity", n), group)
+
+
+def reduce_from_region(x, group=None):
+    """All-reduce forward, identity backward: the output of a row-parallel layer."""
+    return reshard(x, ReshardStep("all_reduce", dist.get_world_size(group)), group)
+
+
+def scatter_to_region(x, group=None, dim: int = -1):
+    """Keep this rank's slice along `dim` forward, all-gather backward."""
+    return reshard(x, ReshardStep("split", dist.get_world_size(group), dst_dim=dim % x.dim()), group)
+
+
+def gather_from_region(x, group=None, dim: int = -1):
+    """All-gather along `dim` forward, slice backward."""
+    return reshard(x, ReshardStep("all_gather", dist.get_world_size(group), src_dim=dim % x.dim()), group)
