@@ -148,12 +148,25 @@ def run_ours(opts):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), native.launch_count() - l0, losses
 
-    for _ in range(opts.warmup):
-        engine.train_step()
     # A bounded device wait that expired during warm-up (ranks of a peer group that started more than
-    # the wait limit apart) is reported in the JSON line and cleared; one inside the timed region
-    # invalidates the measurement and raises below.
+    # the wait limit apart) is reported in the JSON line and cleared: the engine raises on every rank
+    # in the same step (the fault mark travels with the overflow flag), the update of that step was
+    # skipped everywhere, and the ranks go on together. One inside the timed region invalidates the
+    # measurement and ends the run.
     warmup_status = None
+    barrier_sync()          # all ranks begin their first step together
+    for _ in range(opts.warmup):
+        try:
+            engine.train_step()
+        except RuntimeError as err:
+            if "bounded device wait" not in str(err):
+                raise
+            warmup_status = str(err)
+            try:
+                native.check_status()      # reads and clears this rank's status word
+            except RuntimeError:
+                pass
+            barrier_sync()
     try:
         native.check_status()
     except RuntimeError as err:

@@ -23,19 +23,20 @@ import torch.nn.functional as F
 
 from . import native
 
-_WS = {}
 
 
 def _workspace(device, numel: int) -> torch.Tensor:
-    """Grow-only fp32 scratch per device and stream (partial sums of LayerNorm-backward and column sums)."""
+    """Grow-only fp32 scratch per device and stream (partial sums of LayerNorm-backward and column
+    sums), kept as named buffers in the process-wide registry of `utils.memory`."""
+    from ..utils import memory
     # one scratch per (device, stream): kernels of different streams may run concurrently
     stream = torch.cuda.current_stream(device).cuda_stream if device.type == "cuda" else 0
-    key = (device.type, device.index, stream)
-    ws = _WS.get(key)
-    if ws is None or ws.numel() < numel:
-        ws = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
-        _WS[key] = ws
-    return ws
+    name = f"colsum-workspace {device.type}:{device.index} stream {stream}"
+    buf = memory._BUFFERS.get(name)
+    if buf is None or buf.numel < numel:
+        memory.free_mem_buff(name)
+        buf = memory.allocate_mem_buff(name, max(numel, 1 << 20), torch.float32, device=device)
+    return buf.data
 
 
 def _main_grad(p) -> Optional[torch.Tensor]:
