@@ -35,6 +35,9 @@ def collect_gpt_gradient_metadata(stage, pstate, normalized_config) -> Tuple[Lis
             raise ValueError(f"op {op.op_index} is {op.name!r} but the manifest says {want!r}")
     descriptors, bindings = [], []
     seen = set()
+
+    def chunk_of(op_index: int) -> int:
+        return next(c for c, (lo, hi) in enumerate(have_ranges) if lo <= op_index < hi)
     tp, tp_rank = pstate.tp_size, pstate.tp_rank
     for e in stage.unique_entries():
         spec, p = e.spec, e.param
@@ -52,7 +55,7 @@ def collect_gpt_gradient_metadata(stage, pstate, normalized_config) -> Tuple[Lis
             logical_param_id=spec.logical_id, shared_weight_id=None, shared_weight_root=False,
             logical_region_key=spec.logical_id, semantic_order_key=order_key, global_rank=pstate.rank,
             model_impl=normalized_config["model_impl"], op_manifest_hash=manifest["hash"],
-            pipeline_id=pstate.pipeline_id, stage_id=pstate.stage_id, model_chunk_id=0,
+            pipeline_id=pstate.pipeline_id, stage_id=pstate.stage_id, model_chunk_id=chunk_of(e.op.op_index),
             global_op_index=e.op.op_index, manifest_op_name=e.op.name, runtime_op_name=type(e.op).__name__,
             relative_parameter_name=spec.local_name, stage_global_op_begin=begin, stage_global_op_end=end,
             local_tp_degree=tp, local_tp_rank=tp_rank, local_dp_degree=pstate.dp_size, local_dp_rank=pstate.dp_rank,
