@@ -9,7 +9,6 @@ not on any benchmarked path.
 """
 from __future__ import annotations
 
-import math
 
 import torch
 

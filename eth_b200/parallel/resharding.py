@@ -18,7 +18,7 @@ stage program does not call this; it serves per-op layouts in profiling and sear
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -29,7 +29,7 @@ import sys
 import torch
 import torch.distributed as dist
 
-from ..contract.config import make_config, make_pipe, manifest_size
+from ..contract.config import manifest_size
 from ..models.gpt_ops import LIVE_AFTER, GPTModelConfig, TPComm
 from ..models.stage import GPTStage, MicroBatch
 from ..search.profile_db import OP_HEADER

@@ -13,10 +13,8 @@ scalar that the optimizer kernels read.
 """
 from __future__ import annotations
 
-import math
 import os
 import time
-from types import SimpleNamespace
 from typing import Callable, Dict, List, Optional
 
 import torch

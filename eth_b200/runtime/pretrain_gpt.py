@@ -10,9 +10,7 @@ from __future__ import annotations
 
 import csv
 import math
-import json
 import os
-import sys
 import time
 
 import torch

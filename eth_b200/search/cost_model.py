@@ -18,7 +18,6 @@ largest op, and allocator reserve; recomputed ops keep only their input.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from functools import lru_cache
 from typing import Dict, List, Optional, Sequence, Tuple
 
 from ..contract.config import LAYER_OPS

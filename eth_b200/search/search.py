@@ -33,7 +33,6 @@ from __future__ import annotations
 
 import itertools
 import json
-import math
 import os
 import time
 from dataclasses import dataclass, field

@@ -10,7 +10,6 @@ groups and scratch buffers stable over the run.
 """
 import argparse
 import json
-import sys
 from pathlib import Path
 
 
