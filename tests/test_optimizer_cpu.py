@@ -71,3 +71,43 @@ def test_sgd_skips_on_overflow_and_factory():
     ok, _, _ = opt.step(sync=False)
     assert torch.equal(st.param_buf, before)
     assert coalesce_ranges([(0, 10), (10, 5), (200, 4)]) == [(0, 15), (200, 4)]
+
+
+def test_learning_rate_schedule_and_checkpoint_policy():
+    import math
+    import pytest
+    from eth_b200.optim.lr import AnnealingLR, Schedule
+
+    class Opt:
+        lr = None
+
+        def set_lr(self, v):
+            self.lr = v
+
+    s = Schedule(1e-2, 1e-3, warmup_steps=10, decay_steps=110, style="cosine")
+    assert s.at(0) == 0.0 and abs(s.at(5) - 5e-3) < 1e-15 and s.at(10) == 1e-2
+    assert abs(s.at(60) - (1e-3 + 0.5 * 9e-3)) < 1e-12           # half way down the cosine
+    assert abs(s.at(110) - 1e-3) < 1e-12 and s.at(500) == 1e-3
+    assert abs(Schedule(1e-2, 1e-3, 10, 110, "linear").at(35) - (1e-3 + 0.75 * 9e-3)) < 1e-12
+    assert Schedule(1e-2, 1e-3, 10, 110, "constant").at(10 ** 6) == 1e-2
+    for bad in (dict(peak=1e-3, floor=1e-2), dict(warmup_steps=200), dict(style="exponential")):
+        with pytest.raises(ValueError):
+            Schedule(**{**dict(peak=1e-2, floor=1e-3, warmup_steps=10, decay_steps=110, style="cosine"), **bad})
+    opt = Opt()
+    sched = AnnealingLR(opt, 1e-2, 1e-3, 10, 110, "cosine")
+    assert opt.lr == 0.0
+    sched.step(60)
+    assert math.isclose(opt.lr, s.at(60))
+    saved = sched.state_dict()
+    assert set(saved) == {"max_lr", "min_lr", "warmup_steps", "decay_steps", "decay_style", "num_steps"}
+    # checkpoint values win by default; the counter is restored
+    other = AnnealingLR(Opt(), 5e-3, 1e-4, 1, 50, "linear")
+    other.load_state_dict(saved)
+    assert other.max_lr == 1e-2 and other.decay_style == "cosine" and other.num_steps == 60
+    # neither flag: a differing value is an error; override: the command line wins, the counter still loads
+    strict = AnnealingLR(Opt(), 5e-3, 1e-4, 1, 50, "linear", use_checkpoint_lr_scheduler=False)
+    with pytest.raises(ValueError, match="do not match"):
+        strict.load_state_dict(saved)
+    mine = AnnealingLR(Opt(), 5e-3, 1e-4, 1, 50, "linear", use_checkpoint_lr_scheduler=False, override_lr_scheduler=True)
+    mine.load_state_dict(saved)
+    assert mine.max_lr == 5e-3 and mine.num_steps == 60
