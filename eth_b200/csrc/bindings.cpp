@@ -36,7 +36,8 @@ void need_cuda(const Tensor& t, const char* name) {
 // B: [N,K] (b_mn=0) or [K,N] (b_mn=1). Row strides are taken from the tensors.
 void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& d, const OptTensor& bias,
           const OptTensor& aux, int64_t aux_mode, const OptTensor& d2, bool accumulate,
-          double alpha, const OptTensor& status, int64_t sm_count) {
+          double alpha, const OptTensor& status, int64_t sm_count, double drop_p, int64_t drop_seed,
+          int64_t drop_offset) {
   need_cuda(a, "a"); need_cuda(b, "b"); need_cuda(d, "d");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2, "gemm expects 2-D tensors");
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "inner stride must be 1");
@@ -70,6 +71,10 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, Tensor& d, con
   g.alpha = static_cast<float>(alpha);
   g.status = status.has_value() ? status->data_ptr<int>() : nullptr;
   g.sm_count = static_cast<int>(sm_count);
+  g.drop_p = static_cast<float>(drop_p);
+  g.drop_seed = static_cast<unsigned long long>(drop_seed);
+  g.drop_offset = static_cast<unsigned long long>(drop_offset);
+  if (drop_p != 0.0) TORCH_CHECK(d.is_contiguous(), "epilogue dropout draws the mask of a contiguous output");
   check(ethb::gemm_tcgen05(g, cur_stream()), "gemm_tcgen05");
 }
 
@@ -118,7 +123,8 @@ void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, cons
                     const OptTensor& aux, double alpha, const OptTensor& status,
                     const std::vector<int64_t>& stage_ptrs, const std::vector<int64_t>& out_ptrs,
                     const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, int64_t max_tiles,
-                    int64_t stage_elems, int64_t ldd, int64_t mode) {
+                    int64_t stage_elems, int64_t ldd, int64_t mode, double drop_p, int64_t drop_seed,
+                    int64_t drop_offset) {
   need_cuda(a, "a"); need_cuda(b, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1);
   TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a/b dtype mismatch");
@@ -149,6 +155,10 @@ void gemm_allreduce(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, cons
   g.comm.max_tiles = static_cast<int>(max_tiles);
   g.comm.stage_elems = stage_elems;
   g.comm.mode = static_cast<int>(mode);
+  g.drop_p = static_cast<float>(drop_p);
+  g.drop_seed = static_cast<unsigned long long>(drop_seed);
+  g.drop_offset = static_cast<unsigned long long>(drop_offset);
+  if (drop_p != 0.0) TORCH_CHECK(ldd == g.N, "epilogue dropout draws the mask of a contiguous output");
   for (size_t i = 0; i < w; ++i) {
     g.comm.stage[i] = reinterpret_cast<void*>(stage_ptrs[i]);
     g.comm.out[i] = reinterpret_cast<void*>(out_ptrs[i]);
@@ -588,9 +598,14 @@ void flags_wait(const std::vector<int64_t>& ptrs, int64_t value, int64_t limit_s
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("a"), py::arg("a_mn"), py::arg("b"), py::arg("b_mn"), py::arg("d"), py::arg("bias"),
+        py::arg("aux"), py::arg("aux_mode"), py::arg("d2"), py::arg("accumulate"), py::arg("alpha"), py::arg("status"),
+        py::arg("sm_count"), py::arg("drop_p") = 0.0, py::arg("drop_seed") = 0, py::arg("drop_offset") = 0);
   m.def("gemm_batched", &gemm_batched);
-  m.def("gemm_allreduce", &gemm_allreduce);
+  m.def("gemm_allreduce", &gemm_allreduce, py::arg("a"), py::arg("a_mn"), py::arg("b"), py::arg("b_mn"),
+        py::arg("bias"), py::arg("aux"), py::arg("alpha"), py::arg("status"), py::arg("stage_ptrs"), py::arg("out_ptrs"),
+        py::arg("flag_ptrs"), py::arg("rank"), py::arg("epoch"), py::arg("max_tiles"), py::arg("stage_elems"),
+        py::arg("ldd"), py::arg("mode"), py::arg("drop_p") = 0.0, py::arg("drop_seed") = 0, py::arg("drop_offset") = 0);
   m.def("gemm_allgather", &gemm_allgather);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("ln_bwd_parts", &ln_bwd_parts);

@@ -240,6 +240,17 @@ __device__ __forceinline__ void comm_reduce_tile(const GemmArgs& p, int tm, int 
           }
         }
       }
+      if (p.drop_p > 0.f && col0 < p.N) {   // after the reduction: one rank draws the mask for all
+        const float inv_keep = 1.0f / (1.0f - p.drop_p);
+        const int64_t vec0 = (static_cast<int64_t>(row) * p.N + col0) >> 3;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          bool keep[8];
+          keep8(p.drop_seed, p.drop_offset, vec0 + q, p.drop_p, keep);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[q * 8 + e] = keep[e] ? v[q * 8 + e] * inv_keep : 0.f;
+        }
+      }
       if (row_ok && p.aux_mode == kAuxAdd && col0 < p.N) {
         const uint4* ap = reinterpret_cast<const uint4*>(
             reinterpret_cast<const uint16_t*>(p.aux) +
@@ -346,6 +357,17 @@ __device__ __forceinline__ void epilogue_tile_staged(const GemmArgs& p, uint32_t
           }
         }
       }
+      if (p.drop_p > 0.f) {
+        const float inv_keep = 1.0f / (1.0f - p.drop_p);
+        const int64_t vec0 = (static_cast<int64_t>(row0 + lane) * p.N + col0) >> 3;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          bool keep[8];
+          keep8(p.drop_seed, p.drop_offset, vec0 + q, p.drop_p, keep);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[half][q * 8 + e] = keep[e] ? v[half][q * 8 + e] * inv_keep : 0.f;
+        }
+      }
       if (p.aux_mode != kAuxNone) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -433,6 +455,17 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, uint32_t taddr,
             v[q * 8 + e * 2 + 1] += f.y;
           }
         }
+      }
+    }
+    if (p.drop_p > 0.f) {
+      const float inv_keep = 1.0f / (1.0f - p.drop_p);
+      const int64_t vec0 = (static_cast<int64_t>(row) * p.N + col0) >> 3;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        bool keep[8];
+        keep8(p.drop_seed, p.drop_offset, vec0 + q, p.drop_p, keep);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[q * 8 + e] = keep[e] ? v[q * 8 + e] * inv_keep : 0.f;
       }
     }
     if (row_ok) {
@@ -1427,6 +1460,10 @@ cudaError_t gemm_tcgen05(const GemmArgs& a, cudaStream_t stream) {
   if (a.N % 8 != 0 || a.ldd % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a.D) & 15) != 0) return cudaErrorMisalignedAddress;
   if (a.ab_dtype != kF16 && a.ab_dtype != kBF16) return cudaErrorInvalidValue;
+  if (a.drop_p != 0.f)
+    ETHB_RETURN_IF(!(a.drop_p > 0.f && a.drop_p < 1.f) || a.aux_mode == kAuxGeluGrad || a.D2 != nullptr ||
+                       a.accumulate || (a.comm.world > 1 && a.comm.mode != 0),
+                   cudaErrorInvalidValue, "epilogue dropout: needs 0 < p < 1 and a plain or residual-add epilogue");
   if (a.comm.world > 1) {
     ETHB_RETURN_IF(a.comm.world > kGemmMaxPeers, cudaErrorInvalidValue, "fused all-reduce: too many peers");
     ETHB_RETURN_IF(a.comm.mode != 2 && (a.d_dtype != a.ab_dtype || a.accumulate || a.D2 != nullptr ||

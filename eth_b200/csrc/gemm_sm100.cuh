@@ -60,6 +60,11 @@ struct GemmArgs {
   const void* bias;                  // optional [N], ab_dtype
   const void* aux; int64_t ldaux; int aux_mode;  // optional [M,N], ab_dtype
   int accumulate;                    // D += value instead of D = value
+  // Optional dropout of (alpha * acc + bias), applied before `aux` is added (aux_mode none or
+  // add): the bias-dropout-add of a transformer sub-block in the epilogue of its output GEMM. The
+  // mask is that of a contiguous [M, N] tensor (sm100_common.cuh: keep8); needs N % 8 == 0.
+  float drop_p;                      // 0 = no dropout
+  unsigned long long drop_seed, drop_offset;
   float alpha;
   int* status;                       // device status word (0 == ok)
   int sm_count;                      // CTAs to launch at most (0 = all SMs)

@@ -416,4 +416,38 @@ __device__ __forceinline__ float2 unpack2(uint32_t u, int dtype) {
   }
 }
 
+// ---- dropout masks ---------------------------------------------------------------------------
+// The mask of a [rows, cols] tensor is a pure function of (seed, offset, vector index), the vector
+// index being (row * cols + col) / 8: every kernel that applies or re-applies a dropout (the
+// element-wise kernels, the GEMM epilogues, the backward kernels) calls the same function and gets
+// the same bits, so no mask is ever stored.
+// Philox-4x32-10 keyed by (seed, offset); one call yields 4 x 32 random bits for counter `ctr`.
+__device__ __forceinline__ uint4 philox4(uint64_t seed, uint64_t ctr, uint64_t offset) {
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+  uint32_t c0 = static_cast<uint32_t>(ctr), c1 = static_cast<uint32_t>(ctr >> 32);
+  uint32_t c2 = static_cast<uint32_t>(offset), c3 = static_cast<uint32_t>(offset >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+// keep-bits for the 8 elements of vector i: 16 random bits per element
+__device__ __forceinline__ void keep8(uint64_t seed, uint64_t offset, int64_t i, float p,
+                                      bool (&keep)[8]) {
+  const uint4 r = philox4(seed, static_cast<uint64_t>(i), offset);
+  const uint32_t thr = static_cast<uint32_t>(p * 65536.0f);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    keep[2 * j] = (w[j] & 0xffffu) >= thr;
+    keep[2 * j + 1] = (w[j] >> 16) >= thr;
+  }
+}
+
+
 }  // namespace ethb

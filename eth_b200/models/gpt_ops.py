@@ -92,15 +92,32 @@ class TPComm:
             torch.distributed.all_reduce(t, group=self.group)
         return t
 
-    def linear_all_reduce(self, x, weight, *, b_mn=False):
+    def linear_all_reduce(self, x, weight, *, b_mn=False, bias=None, residual=None, dropout=None):
         """sum over the TP group of x W^T (b_mn False) or x W (b_mn True): one fused kernel when the
-        peer-memory backend is available, else a GEMM followed by an all-reduce."""
+        peer-memory backend is available, else a GEMM followed by an all-reduce. `bias`, `dropout`
+        = (p, seed, offset) and `residual` are applied to the sum, once, in the same kernel; see
+        `can_fuse_epilogue` for when that is possible."""
         if self.size > 1 and self.backend is not None and x.is_cuda:
             n = weight.shape[1] if b_mn else weight.shape[0]
             if self.backend.supports(x.shape[0], n):
-                return self.backend.gemm_all_reduce(x, weight, b_mn=b_mn)
+                return self.backend.gemm_all_reduce(x, weight, b_mn=b_mn, bias=bias, residual=residual,
+                                                    dropout=dropout)
+        if self.size == 1:
+            if bias is None and residual is None and dropout is None:
+                return raw.gemm(x, weight, b_mn=b_mn)
+            return raw.gemm(x, weight, b_mn=b_mn, bias=bias, aux=residual,
+                            aux_mode=raw.AUX_ADD if residual is not None else raw.AUX_NONE, dropout=dropout)
+        if bias is not None or residual is not None or dropout is not None:
+            raise RuntimeError("an epilogue on the reduced sum needs the fused tensor-parallel kernel")
         y = raw.gemm(x, weight, b_mn=b_mn)
         return self.all_reduce_(y)
+
+    def can_fuse_epilogue(self, rows: int, cols: int, on_gpu: bool) -> bool:
+        """Whether `linear_all_reduce` can apply bias / dropout / residual to the reduced sum itself:
+        always without tensor parallelism, else only inside the fused kernel."""
+        if self.size == 1:
+            return True
+        return self.backend is not None and on_gpu and self.backend.supports(rows, cols)
 
     def reshard(self, x: torch.Tensor, step) -> torch.Tensor:
         """Run one placement change (`parallel.resharding.ReshardStep`) of a token-major tensor over
@@ -361,6 +378,7 @@ class RowLinearOp(Op):
     def __init__(self, *a, in_features: int, out_features: int, suffix: str, **k):
         super().__init__(*a, **k)
         self.in_features, self.out_features, self.suffix = in_features, out_features, suffix
+        self.fused_dropout_add = None   # the following BiasDropoutAddOp when the stage builder fused it in
 
     def specs(self):
         # algo 1 runs this GEMM column-parallel (weight cut along its output features); the bias stays
@@ -380,6 +398,15 @@ class RowLinearOp(Op):
             return
         x = env["hidden_states"]
         ctx["x"] = x
+        nxt = self.fused_dropout_add
+        if nxt is not None and self.tp.can_fuse_epilogue(x.shape[0], self.out_features, x.is_cuda):
+            # the following bias-dropout-add runs in this GEMM's epilogue (on the reduced sum under TP);
+            # that op then only records what its backward needs
+            drop = (self.cfg.hidden_dropout, self.cfg.seed + nxt.op_index, nxt.dropout_offset(mb))
+            env["hidden_states"] = self.tp.linear_all_reduce(x, self.p("weight"), bias=self.p("bias"),
+                                                             residual=env[nxt.residual_name], dropout=drop)
+            env["_dropout_add_done"] = drop
+            return
         env["hidden_states"] = self.tp.linear_all_reduce(x, self.p("weight"))
 
     def bwd(self, genv, ctx, mb):
@@ -513,6 +540,11 @@ class BiasDropoutAddOp(Op):
         p = self.cfg.hidden_dropout
         ctx["drop"] = (p, self.cfg.seed + self.op_index, self.dropout_offset(mb))
         ctx["bias"] = bias
+        done = env.pop("_dropout_add_done", None)
+        if done is not None:      # the producing GEMM already applied bias, this dropout and the residual
+            if done != ctx["drop"]:
+                raise RuntimeError("fused dropout-add used other dropout parameters than this op")
+            return
         env["hidden_states"] = raw.bias_dropout_add_fwd(x, bias, res, *ctx["drop"])
 
     def bwd(self, genv, ctx, mb):

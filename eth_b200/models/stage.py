@@ -173,6 +173,10 @@ class GPTStage:
                     a.fuse_next = True
                 if a.name == "enc-MLP-gelu" and b.name == "enc-MLP-GEMM-2" and b.algo == 0:
                     b.fuse_prev = True
+                # bias-dropout-add in the epilogue of the row-parallel GEMM that feeds it
+                if (a.name in ("enc-attention-dense", "enc-MLP-GEMM-2") and a.algo == 0
+                        and b.name in ("enc-post-attention-dropout", "enc-post-MLP-dropout")):
+                    a.fused_dropout_add = b
 
     # ------------------------------------------------------------------ recompute segments
     def _plan_segments(self, start: int = 0, end: Optional[int] = None) -> List[Tuple[int, int, bool]]:

@@ -50,19 +50,22 @@ AUX_NONE, AUX_ADD, AUX_GELU_GRAD = 0, 1, 2
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, bias=None, aux=None,
-         aux_mode=AUX_NONE, gelu_out=None, accumulate=False, alpha=1.0):
-    """D[M,N] = alpha * A x B^T (+bias) (aux op) (+D).
+         aux_mode=AUX_NONE, gelu_out=None, accumulate=False, alpha=1.0, dropout=None):
+    """D[M,N] = alpha * A x B^T (+bias) (dropout) (aux op) (+D).
 
     A is [M,K] (a_mn False) or [K,M] (a_mn True); B is [N,K] (b_mn False) or [K,N] (b_mn True).
-    `gelu_out`, when given, additionally receives gelu(D).
+    `gelu_out`, when given, additionally receives gelu(D). `dropout` = (p, seed, offset) drops
+    alpha * A x B^T + bias in the epilogue, before a residual `aux` is added: the mask is the one
+    `bias_dropout_add` and `dropout_bwd` draw for the same (seed, offset) on an [M, N] tensor.
     """
     M = a.shape[1] if a_mn else a.shape[0]
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
     if native.use_native(a):
+        p_drop, seed, offset = dropout if dropout is not None else (0.0, 0, 0)
         native.lib().gemm(a, a_mn, b, b_mn, out, bias, aux, aux_mode, gelu_out, accumulate,
-                          float(alpha), native.status(a.device), 0)
+                          float(alpha), native.status(a.device), 0, float(p_drop), int(seed), int(offset))
         return out
     # reference
     af = (a.t() if a_mn else a).float()
@@ -70,6 +73,9 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, bias=None, a
     v = alpha * (af @ bf)
     if bias is not None:
         v = v + bias.float()
+    if dropout is not None and dropout[0] > 0:
+        keep = _keep_mask_ref(v.shape, dropout[0], dropout[1], dropout[2], v.device)
+        v = torch.where(keep, v / (1.0 - dropout[0]), torch.zeros_like(v))
     if aux is not None and aux_mode == AUX_ADD:
         v = v + aux.float()
     elif aux is not None and aux_mode == AUX_GELU_GRAD:

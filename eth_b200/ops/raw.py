@@ -99,16 +99,19 @@ def ln_bwd(dy, x, gamma, beta, mean, rstd, residual_grad=None, slabs=None, ws_mo
 
 
 # ---------------------------------------------------------------------------------- linear
-def linear_fwd(x, weight, bias=None, gelu=False, residual=None):
-    """x W^T (+bias) (+residual). With gelu=True returns (pre_activation, gelu(pre_activation))."""
+def linear_fwd(x, weight, bias=None, gelu=False, residual=None, dropout=None):
+    """x W^T (+bias) (dropout) (+residual). With gelu=True returns (pre_activation, gelu(pre_activation)).
+    `dropout` = (p, seed, offset): the bias-dropout-add of a sub-block in the GEMM's epilogue."""
     if gelu:
         pre = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
         act = torch.empty_like(pre)
         gemm(x, weight, out=pre, bias=bias, gelu_out=act)
         return pre, act
+    if dropout is not None and dropout[0] <= 0:
+        dropout = None
     if residual is not None:
-        return gemm(x, weight, bias=bias, aux=residual, aux_mode=AUX_ADD)
-    return gemm(x, weight, bias=bias)
+        return gemm(x, weight, bias=bias, aux=residual, aux_mode=AUX_ADD, dropout=dropout)
+    return gemm(x, weight, bias=bias, dropout=dropout)
 
 
 def linear_dgrad(dy, weight, gelu_pre=None):

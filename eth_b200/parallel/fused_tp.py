@@ -91,9 +91,10 @@ class FusedTPBackend:
     def supports(self, m: int, n: int) -> bool:
         return m <= self.max_tokens and n <= self.hidden and n % 8 == 0
 
-    def gemm_all_reduce(self, a, b, *, b_mn=False, bias=None, residual=None, alpha=1.0):
-        """sum over the TP group of (a x b^T) (+ bias + residual, added once). Returns a view of a
-        ring slot holding the [M, N] result."""
+    def gemm_all_reduce(self, a, b, *, b_mn=False, bias=None, residual=None, alpha=1.0, dropout=None):
+        """sum over the TP group of (a x b^T) (+ bias, dropout, + residual, applied once, by the rank
+        that reduces a tile). `dropout` = (p, seed, offset). Returns a view of a ring slot holding
+        the [M, N] result."""
         m = a.shape[0]
         n = b.shape[1] if b_mn else b.shape[0]
         if not self.supports(m, n):
@@ -102,9 +103,10 @@ class FusedTPBackend:
         slot = self.slot
         self.slot = (self.slot + 1) % RING
         off = slot * self.out_slot_bytes
+        p_drop, seed, offset = dropout if (dropout is not None and dropout[0] > 0) else (0.0, 0, 0)
         native.lib().gemm_allreduce(a, False, b, b_mn, bias, residual, float(alpha), native.status(a.device),
                                     self.stage.ptrs, self.out.offset_ptrs(off), self.flags.ptrs, self.rank,
-                                    self.epoch, MAX_TILES, self.stage_elems, n, 0)
+                                    self.epoch, MAX_TILES, self.stage_elems, n, 0, float(p_drop), int(seed), int(offset))
         out = self.out.tensor((m, n), self.dtype, off)
         out._ethb_ring = True   # short-lived: valid until RING further fused calls
         return out

@@ -431,3 +431,36 @@ def test_gemm_tail_split_half_tiles(a_mn, b_mn, shape):
     for x, y in zip(outs[1], outs[0]):
         assert torch.equal(x, y)
     native.check_status()
+
+
+@pytest.mark.parametrize("shape", [(4096, 2048, 512), (1000, 1024, 256), (256, 128, 64)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_gemm_epilogue_dropout_draws_the_mask_of_the_elementwise_kernel(shape, with_residual):
+    """bias + dropout (+ residual) in the GEMM epilogue against the GEMM followed by the
+    bias-dropout-add kernel with the same (seed, offset): exactly the same elements are dropped, so
+    the backward kernels, which regenerate the mask, fit both; kept values agree to rounding."""
+    from eth_b200.ops import raw
+    m, n, k = shape
+    torch.manual_seed(31)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.05).to(torch.bfloat16)
+    bias = (torch.randn(n, device=DEV) * 0.1).to(torch.bfloat16)
+    res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16) if with_residual else None
+    p, seed, off = 0.1, 1234, (7 << 24) + 3
+    fused = raw.linear_fwd(x, w, bias, residual=res, dropout=(p, seed, off))
+    plain = raw.bias_dropout_add_fwd(raw.linear_fwd(x, w), bias, res, p, seed, off)
+    # fp32 reference with the mask taken from the kernel itself
+    keep = raw.dropout_bwd(torch.ones(m, n, device=DEV, dtype=torch.bfloat16), p, seed, off) != 0
+    ref = torch.where(keep, (x.float() @ w.float().t() + bias.float()) / (1 - p), torch.zeros((), device=DEV))
+    if with_residual:
+        ref = ref + res.float()
+        dropped_fused = (fused.float() - res.float()) == 0
+    else:
+        dropped_fused = fused == 0
+    # every element the mask drops is dropped by the fused kernel; a kept element only looks dropped
+    # where a small value vanishes in the rounding of (value + residual)
+    assert torch.equal(dropped_fused | keep, torch.ones_like(keep))
+    assert (dropped_fused & keep).float().mean() < (2e-2 if with_residual else 1e-3)
+    assert abs((~keep).float().mean().item() - p) < 0.02
+    assert _rel_err(fused, ref) < 1e-2 and _rel_err(plain, ref) < 1.5e-2
+    native.check_status()
