@@ -403,8 +403,13 @@ class RowLinearOp(Op):
             # the following bias-dropout-add runs in this GEMM's epilogue (on the reduced sum under TP);
             # that op then only records what its backward needs
             drop = (self.cfg.hidden_dropout, self.cfg.seed + nxt.op_index, nxt.dropout_offset(mb))
-            env["hidden_states"] = self.tp.linear_all_reduce(x, self.p("weight"), bias=self.p("bias"),
-                                                             residual=env[nxt.residual_name], dropout=drop)
+            out = self.tp.linear_all_reduce(x, self.p("weight"), bias=self.p("bias"),
+                                            residual=env[nxt.residual_name], dropout=drop)
+            if getattr(out, "_ethb_ring", False):
+                # the fused tensor-parallel kernel returns a slot of a short ring that peers write into;
+                # this tensor is the residual stream, which LayerNorm keeps for its backward: move it out
+                out = out.clone()
+            env["hidden_states"] = out
             env["_dropout_add_done"] = drop
             return
         env["hidden_states"] = self.tp.linear_all_reduce(x, self.p("weight"))
