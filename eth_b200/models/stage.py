@@ -237,7 +237,9 @@ class GPTStage:
         self._contexts[self._key(mb.index, chunk)] = {"ctxs": ctxs, "envs": saved_envs, "mb": mb}
         last_chunk = chunk == len(self.chunk_ranges) - 1
         keep = {name for name, *_ in self.chunk_specs[chunk][1]} | ({"output"} if (self.is_last and last_chunk) else set())
-        return {k: v for k, v in env.items() if k in keep}
+        # a tensor that lives in a short-lived ring slot is copied: what leaves the stage is read later,
+        # by a transfer on another stream
+        return {k: (v.clone() if getattr(v, "_ethb_ring", False) else v) for k, v in env.items() if k in keep}
 
     def context_of(self, mb_index: int, chunk: int = 0) -> dict:
         return self._contexts[self._key(mb_index, chunk)]
