@@ -463,29 +463,53 @@ __device__ __forceinline__ void wg_bar_sync(int wg) {
   asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");
 }
 
-// delta[b,h,s] = sum_d dO * O ; one warp per (b, s, h) row
-__global__ void attn_delta_kernel(const AttnArgs p) {
-  const int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+// delta[b,h,s] = sum_d dO * O. A (b, s, h) row of head_dim elements is covered by head_dim / 8
+// adjacent lanes with one 16-byte load each per tensor (head_dim is 64 or 128: 8 or 16 lanes); a
+// thread takes kDeltaRows rows, strided by the grid, and issues all their loads before any
+// arithmetic, so 2 * kDeltaRows requests are in flight per thread.
+constexpr int kDeltaRows = 4;
+__global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs p) {
+  const int lanes = p.head_dim >> 3;                        // lanes per row (power of two, <= 16)
+  const int rows_per_block = blockDim.x / lanes;
   const int64_t total = static_cast<int64_t>(p.batch) * p.seq_q * p.heads;
-  if (row >= total) return;
-  const int h = static_cast<int>(row % p.heads);
-  const int64_t bs = row / p.heads;
-  const int s = static_cast<int>(bs % p.seq_q);
-  const int b = static_cast<int>(bs / p.seq_q);
-  const uint16_t* o = reinterpret_cast<const uint16_t*>(p.o) + b * p.o_strides[0] +
-                      static_cast<int64_t>(s) * p.o_strides[1] + h * p.o_strides[2];
-  const uint16_t* g = reinterpret_cast<const uint16_t*>(p.d_o) + b * p.do_strides[0] +
-                      static_cast<int64_t>(s) * p.do_strides[1] + h * p.do_strides[2];
-  float acc = 0.f;
-  for (int c = lane * 2; c < p.head_dim; c += 64) {
-    const float2 a = unpack2(*reinterpret_cast<const uint32_t*>(o + c), p.dtype);
-    const float2 d = unpack2(*reinterpret_cast<const uint32_t*>(g + c), p.dtype);
-    acc += a.x * d.x + a.y * d.y;
+  const int sub = threadIdx.x / lanes, vec = threadIdx.x % lanes;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * rows_per_block;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_block + sub;
+  uint4 ov[kDeltaRows], gv[kDeltaRows];
+#pragma unroll
+  for (int u = 0; u < kDeltaRows; ++u) {
+    const int64_t row = row0 + u * stride;
+    if (row < total) {
+      const int h = static_cast<int>(row % p.heads);
+      const int64_t bs = row / p.heads;
+      const int s = static_cast<int>(bs % p.seq_q);
+      const int b = static_cast<int>(bs / p.seq_q);
+      ov[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.o) + b * p.o_strides[0] +
+                                              static_cast<int64_t>(s) * p.o_strides[1] + h * p.o_strides[2] + vec * 8);
+      gv[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.d_o) + b * p.do_strides[0] +
+                                              static_cast<int64_t>(s) * p.do_strides[1] + h * p.do_strides[2] + vec * 8);
+    } else {
+      ov[u] = make_uint4(0, 0, 0, 0);
+      gv[u] = make_uint4(0, 0, 0, 0);
+    }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) p.delta[(static_cast<int64_t>(b) * p.heads + h) * p.seq_q + s] = acc;
+  for (int u = 0; u < kDeltaRows; ++u) {
+    const uint32_t ow[4] = {ov[u].x, ov[u].y, ov[u].z, ov[u].w}, gw[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
+    float acc = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = unpack2(ow[e], p.dtype), d = unpack2(gw[e], p.dtype);
+      acc += a.x * d.x + a.y * d.y;
+    }
+    for (int off = lanes >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    const int64_t row = row0 + u * stride;
+    if (vec == 0 && row < total) {
+      const int h = static_cast<int>(row % p.heads);
+      const int64_t bs = row / p.heads;
+      p.delta[(static_cast<int64_t>(bs / p.seq_q) * p.heads + h) * p.seq_q + (bs % p.seq_q)] = acc;
+    }
+  }
 }
 
 // ---- dK / dV: one CTA per (key/value tile, head, batch) ---------------------------------------
@@ -940,7 +964,16 @@ cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
     attr = true;
   }
   const int64_t rows = static_cast<int64_t>(a.batch) * a.seq_q * a.heads;
-  attn_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(a);
+  for (int i = 0; i < 3; ++i)
+    ETHB_RETURN_IF(a.o_strides[i] % 8 != 0 || a.do_strides[i] % 8 != 0, cudaErrorMisalignedAddress,
+                   "attention backward: strides of o / d_o must be multiples of 8 elements");
+  ETHB_RETURN_IF((reinterpret_cast<uintptr_t>(a.o) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.d_o) & 15) != 0,
+                 cudaErrorMisalignedAddress, "attention backward: o / d_o must be 16-byte aligned");
+  {
+    const int rows_per_block = 256 / (a.head_dim / 8);
+    const int64_t blocks = (rows + static_cast<int64_t>(rows_per_block) * kDeltaRows - 1) / (rows_per_block * kDeltaRows);
+    attn_delta_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(a);
+  }
   dim3 gkv((a.seq_k + kTile - 1) / kTile, a.heads, a.batch);
   attn_bwd_dkdv_kernel<D><<<gkv, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
   dim3 gq((a.seq_q + kTile - 1) / kTile, a.heads, a.batch);
