@@ -768,7 +768,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       mbar_init(&bars->st_full[s], 1);
       mbar_init(&bars->st_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_full[s], 128);
+      mbar_init(&bars->p_full[s], 256);    // both softmax warpgroups work on every sub-tile
     }
     mbar_init(&bars->done, 1);
     fence_mbar_init();
@@ -844,9 +844,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         tc_fence_after();
         const uint64_t dK = desc_advance(dKm0, stage * C::kStageBytes + sub * 8192);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // dQ += dS K
-          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + 64 + k * 8, desc_advance(dK, k * 2048),
-                        idesc_acc, (u | k) != 0 ? 1u : 0u);
+        for (int k = 0; k < 4; ++k)   // dQ += dS K; keys 0-31 of dS sit at columns [0, 16), keys 32-63 at [32, 48)
+          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8,
+                        desc_advance(dK, k * 2048), idesc_acc, (u | k) != 0 ? 1u : 0u);
         if (sub == 1) tc_commit(&bars->st_empty[stage]);
         if (u + 2 < U) {
           const int u2 = u + 2;
@@ -867,48 +867,47 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const int q_row = i * kTile + r_local;
     const bool row_ok = q_row < p.seq_q;
     const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t s_addr = tmem_base + wg * 128 + lane_bits;
-    const uint32_t dp_addr = s_addr + 64;
     const float sl2 = p.scale * kLog2e;
     const int64_t bh = (static_cast<int64_t>(batch) * p.heads + head) * p.seq_q;
     const float lse2 = row_ok ? p.lse[bh + q_row] * kLog2e : INFINITY;
     const float delta = row_ok ? p.delta[bh + q_row] : 0.f;
     bool ok = true;
-    for (int t = 0; t < nkv && ok; ++t) {
-      ok = mbar_wait(&bars->s_full[wg], t & 1, p.status, kStatusTimeoutTmemFull);
+    // Both warpgroups work on every 64-key sub-tile, each on 32 of its columns: the time from
+    // "scores ready" to "dS ready" halves, so it fits under the score MMAs of the other buffer and
+    // the tensor core seldom waits for it. A warpgroup writes its 16-bit dS over the first half of
+    // the dP columns it has just read (its own input), never over the other warpgroup's.
+    for (int u = 0; u < U && ok; ++u) {
+      const int t = u >> 1, sub = u & 1;
+      const uint32_t s_addr = tmem_base + sub * 128 + wg * 32 + lane_bits;
+      const uint32_t dp_addr = s_addr + 64;
+      ok = mbar_wait(&bars->s_full[sub], t & 1, p.status, kStatusTimeoutTmemFull);
       if (!ok) break;
       tc_fence_after();
       const bool diag = p.causal && (t == i);
-      const int kv0 = t * kTile + wg * 64;       // first key index of this sub-tile
-      const bool ragged = kv0 + 64 > p.seq_k;
-      uint32_t rs[2][32], rd[2][32];
+      const int kv0 = t * kTile + sub * 64 + wg * 32;   // first key index of this warpgroup's columns
+      const bool ragged = kv0 + 32 > p.seq_k;
+      uint32_t rs[32], rd[32];
       __syncwarp();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld_32x32b_x32(s_addr + c * 32, rs[c]);
-        tmem_ld_32x32b_x32(dp_addr + c * 32, rd[c]);
-      }
+      tmem_ld_32x32b_x32(s_addr, rs);
+      tmem_ld_32x32b_x32(dp_addr, rd);
       tmem_ld_wait();
+      uint32_t dk[16];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t dk[16];
-#pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int col = c * 32 + 2 * x;
-          const int kl = wg * 64 + col;            // key row inside the 128-row tile
-          float p0 = exp2f(fmaf(__uint_as_float(rs[c][2 * x]), sl2, -lse2));
-          float p1 = exp2f(fmaf(__uint_as_float(rs[c][2 * x + 1]), sl2, -lse2));
-          if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
-          if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rd[c][2 * x]) - delta);
-          const float d1 = p1 * (__uint_as_float(rd[c][2 * x + 1]) - delta);
-          dk[x] = pack_pair(d0, d1, p.dtype);
-        }
-        tmem_st_32x32b_x16(dp_addr + c * 16, dk);
+      for (int x = 0; x < 16; ++x) {
+        const int col = 2 * x;
+        const int kl = sub * 64 + wg * 32 + col;      // key row inside the 128-row tile
+        float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, -lse2));
+        float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, -lse2));
+        if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
+        if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
+        const float d0 = p0 * (__uint_as_float(rd[2 * x]) - delta);
+        const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - delta);
+        dk[x] = pack_pair(d0, d1, p.dtype);
       }
+      tmem_st_32x32b_x16(dp_addr, dk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->p_full[wg]);
+      mbar_arrive(&bars->p_full[sub]);
     }
     if (ok) ok = mbar_wait(&bars->done, 0, p.status, kStatusTimeoutTmemFull);
     ok = __all_sync(0xffffffffu, ok);
