@@ -542,7 +542,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       mbar_init(&bars->st_full[s], 1);
       mbar_init(&bars->st_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_full[s], 128);
+      mbar_init(&bars->p_full[s], 256);    // both softmax warpgroups work on every sub-tile
     }
     mbar_init(&bars->done, 1);
     fence_mbar_init();
@@ -619,14 +619,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tc_fence_after();
         const uint64_t dQ = desc_advance(dQm0, stage * C::kStageBytes + sub * 8192);
         const uint64_t dDO = desc_advance(dQ, C::kTileBytes);
+        // queries 0-31 of P / dS sit at columns [0, 16) of their buffer, queries 32-63 at [32, 48)
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // dV += P^T dO
-          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + k * 8, desc_advance(dDO, k * 2048),
-                        idesc_acc, (u | k) != 0 ? 1u : 0u);
+          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + (k >> 1) * 32 + (k & 1) * 8,
+                        desc_advance(dDO, k * 2048), idesc_acc, (u | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // dK += dS^T Q
-          tc_mma_f16_ts(tmem_base + 384, tmem_base + b * 128 + 64 + k * 8, desc_advance(dQ, k * 2048),
-                        idesc_acc, (u | k) != 0 ? 1u : 0u);
+          tc_mma_f16_ts(tmem_base + 384, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8,
+                        desc_advance(dQ, k * 2048), idesc_acc, (u | k) != 0 ? 1u : 0u);
         if (sub == 1) tc_commit(&bars->st_empty[stage]);
         if (u + 2 < U) {
           const int u2 = u + 2;
@@ -646,58 +647,75 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     const int r_local = quarter * 32 + lane;     // key/value row inside the tile
     const int wg_tid = threadIdx.x - 64 - wg * 128;
     const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t s_addr = tmem_base + wg * 128 + lane_bits;
-    const uint32_t dp_addr = s_addr + 64;
     const float sl2 = p.scale * kLog2e;
     const float* lse_bh = p.lse + (static_cast<int64_t>(batch) * p.heads + head) * p.seq_q;
     const float* delta_bh = p.delta + (static_cast<int64_t>(batch) * p.heads + head) * p.seq_q;
     bool ok = true;
+    // Both warpgroups work on every 64-query sub-tile, each on 32 of its columns (see the dQ kernel),
+    // so the softmax of a sub-tile takes half as long and hides under the score MMAs of the other
+    // buffer; each warpgroup overwrites only columns it has read itself. The lse / delta values of a
+    // query tile are staged once per tile and warpgroup (its 2 x 32 columns), one tile ahead: the
+    // global loads for tile t + 1 are issued before tile t is processed and parked in shared memory
+    // after it, so their latency is never waited for.
+    const int a_sub = (wg_tid >> 5) & 1, a_col = wg_tid & 31;
+    auto aux_query = [&](int t) { return (i0 + t) * kTile + a_sub * 64 + wg * 32 + a_col; };
+    auto aux_slot = [&](int t) { return sAux + ((wg * 2 + (t & 1)) * 2) * 64; };   // [lse 2 x 32 | delta 2 x 32]
+    if (wg_tid < 64 && nq > 0) {
+      const int qi = aux_query(0);
+      const bool in = qi < p.seq_q;
+      aux_slot(0)[wg_tid] = in ? lse_bh[qi] * kLog2e : INFINITY;
+      aux_slot(0)[64 + wg_tid] = in ? delta_bh[qi] : 0.f;
+    }
     for (int t = 0; t < nq && ok; ++t) {
+      wg_bar_sync(wg);                 // tile t's values are staged; everyone has left tile t - 1
+      float next_lse = INFINITY, next_delta = 0.f;
+      if (wg_tid < 64 && t + 1 < nq) {
+        const int qi = aux_query(t + 1);
+        if (qi < p.seq_q) {
+          next_lse = lse_bh[qi] * kLog2e;
+          next_delta = delta_bh[qi];
+        }
+      }
       const int i = i0 + t;
-      const int q0 = i * kTile + wg * 64;
-      float* a_lse = sAux + ((wg * 2 + (t & 1)) * 2 + 0) * 64;
-      float* a_del = a_lse + 64;
-      if (wg_tid < 64) {
-        const int qi = q0 + wg_tid;
-        const bool in = qi < p.seq_q;
-        a_lse[wg_tid] = in ? lse_bh[qi] * kLog2e : INFINITY;
-        a_del[wg_tid] = in ? delta_bh[qi] : 0.f;
-      }
-      wg_bar_sync(wg);
-      ok = mbar_wait(&bars->s_full[wg], t & 1, p.status, kStatusTimeoutTmemFull);
-      if (!ok) break;
-      tc_fence_after();
       const bool diag = p.causal && (i == j);
-      uint32_t rs[2][32], rd[2][32];
-      __syncwarp();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld_32x32b_x32(s_addr + c * 32, rs[c]);
-        tmem_ld_32x32b_x32(dp_addr + c * 32, rd[c]);
-      }
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+#pragma unroll 1
+      for (int sub = 0; sub < 2 && ok; ++sub) {
+        const float* a_lse = aux_slot(t) + sub * 32;
+        const float* a_del = a_lse + 64;
+        const uint32_t s_addr = tmem_base + sub * 128 + wg * 32 + lane_bits;
+        const uint32_t dp_addr = s_addr + 64;
+        ok = mbar_wait(&bars->s_full[sub], t & 1, p.status, kStatusTimeoutTmemFull);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t rs[32], rd[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(s_addr, rs);
+        tmem_ld_32x32b_x32(dp_addr, rd);
+        tmem_ld_wait();
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int x = 0; x < 16; ++x) {
-          const int col = c * 32 + 2 * x;          // query column inside this 64-wide sub-tile
-          const int ql = wg * 64 + col;            // query row inside the 128-row tile
-          float p0 = exp2f(fmaf(__uint_as_float(rs[c][2 * x]), sl2, -a_lse[col]));
-          float p1 = exp2f(fmaf(__uint_as_float(rs[c][2 * x + 1]), sl2, -a_lse[col + 1]));
+          const int col = 2 * x;                           // query column among this warpgroup's 32
+          const int ql = sub * 64 + wg * 32 + col;         // query row inside the 128-row tile
+          float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, -a_lse[col]));
+          float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, -a_lse[col + 1]));
           if (diag && r_local > ql) p0 = 0.f;
           if (diag && r_local > ql + 1) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rd[c][2 * x]) - a_del[col]);
-          const float d1 = p1 * (__uint_as_float(rd[c][2 * x + 1]) - a_del[col + 1]);
+          const float d0 = p0 * (__uint_as_float(rd[2 * x]) - a_del[col]);
+          const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - a_del[col + 1]);
           pk[x] = pack_pair(p0, p1, p.dtype);
           dk[x] = pack_pair(d0, d1, p.dtype);
         }
-        tmem_st_32x32b_x16(s_addr + c * 16, pk);
-        tmem_st_32x32b_x16(dp_addr + c * 16, dk);
+        tmem_st_32x32b_x16(s_addr, pk);
+        tmem_st_32x32b_x16(dp_addr, dk);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[sub]);
       }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bars->p_full[wg]);
+      if (wg_tid < 64 && t + 1 < nq) {
+        aux_slot(t + 1)[wg_tid] = next_lse;
+        aux_slot(t + 1)[64 + wg_tid] = next_delta;
+      }
     }
     // epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK * scale
     if (ok) ok = mbar_wait(&bars->done, 0, p.status, kStatusTimeoutTmemFull);
