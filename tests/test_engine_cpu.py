@@ -79,3 +79,32 @@ def test_train_step_matches_adamw():
     for lid, p in eng.stage.named_parameters():
         err = (p - params[lid]).norm() / (params[lid].norm() + 1e-12)
         assert err < 1e-4, (lid, float(err))
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_dropout_add_fused_into_the_gemm_trains_like_the_separate_op(recompute):
+    """With hidden dropout on, the bias-dropout-add that runs in the epilogue of the row-parallel
+    GEMM draws the mask of the stand-alone op: a stage built with fusions and one built without
+    produce the same loss and the same gradients, also when the fused pair is recomputed."""
+    from eth_b200.runtime import schedules
+    layers = 2
+    n = manifest_size(layers)
+    rec = [[1 if 1 <= i <= 14 else 0 for i in range(n)]] if recompute else None
+    results = []
+    for fuse in (True, False):
+        args = _args(_tiny(rec, layers), ["--hidden-dropout", "0.2"])
+        eng = TrainEngine(args, device="cpu")
+        fused_ops = [op for op in eng.stage.ops if getattr(op, "fused_dropout_add", None) is not None]
+        assert len(fused_ops) == 2 * layers
+        if not fuse:
+            for op in fused_ops:
+                op.fused_dropout_add = None
+        eng.optimizer.zero_grad()
+        eng.loss_acc.zero_()
+        schedules.forward_backward_no_pipelining(eng, eng.pstate.num_microbatches)
+        results.append((float(eng.loss_acc[0]), {lid: p.main_grad.clone() for lid, p in eng.stage.named_parameters()}))
+    (loss_a, grads_a), (loss_b, grads_b) = results
+    assert abs(loss_a - loss_b) < 1e-5 * abs(loss_b)
+    for lid in grads_a:
+        err = (grads_a[lid] - grads_b[lid]).norm() / (grads_b[lid].norm() + 1e-12)
+        assert err < 1e-5, (lid, float(err))
