@@ -2,6 +2,7 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
         --master-port 29533 -m eth_b200.profiler.fused_collective_bench [--tokens 8192] [--hidden 2048]
+        [--sweep-k 64,1024,2048,4096,8192]
 
 For the GEMM shapes of one transformer layer at this tensor-parallel width it times
   * GEMM + all-reduce      (row-parallel forward, column-parallel data gradient),
@@ -10,6 +11,9 @@ For the GEMM shapes of one transformer layer at this tensor-parallel width it ti
 each as ONE fused kernel and as "GEMM kernel + NCCL collective", with CUDA events on the launching
 stream after warm-up, maximum over ranks, and prints one JSON line per case with the roofline
 fraction: target time = max(FLOPs / measured GEMM peak, bytes over NVLink / 770 GB/s per direction).
+`--sweep-k` instead times the fused GEMM + all-reduce at [tokens, hidden] for a list of reduction
+lengths: with almost no math (K = 64) the time is the communication floor of the kernel, and the K
+at which the time starts to grow is where it turns compute-bound.
 """
 from __future__ import annotations
 
@@ -34,6 +38,7 @@ def main(argv=None):
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--sweep-k", default=None, help="comma-separated reduction lengths (per rank) for the K sweep")
     a = ap.parse_args(argv)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -71,6 +76,18 @@ def main(argv=None):
 
     esz = 2
     frac = (world - 1) / world
+    if a.sweep_k:
+        for k in [int(v) for v in a.sweep_k.split(",")]:
+            x = torch.randn(M, k, device=dev, dtype=dt)
+            w = torch.randn(H, k, device=dev, dtype=dt) * 0.05
+            out = torch.empty(M, H, device=dev, dtype=dt)
+            report("gemm_allreduce", f"K sweep, {2 * frac * M * H * esz / 2 ** 20:.0f} MiB each way", H, k,
+                   timeit(lambda: be.gemm_all_reduce(x, w)), float("nan"), timeit(lambda: ops.gemm(x, w, out=out)),
+                   2 * frac * M * H * esz)
+        native.check_status()
+        be.close()
+        dist.destroy_process_group()
+        return
     for (n, k, b_mn, tag) in [(H, H // world, False, "attention-dense fwd"), (H, 4 * H // world, False, "MLP-GEMM-2 fwd"),
                               (H, 3 * H // world, True, "qkv dgrad"), (H, 4 * H // world, True, "MLP-GEMM-1 dgrad")]:
         x = torch.randn(M, k, device=dev, dtype=dt)
