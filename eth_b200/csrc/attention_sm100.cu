@@ -512,7 +512,12 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs p) {
   }
 }
 
-// ---- dK / dV: one CTA per (key/value tile, head, batch) ---------------------------------------
+// ---- dK / dV: persistent CTAs over (key/value tile, head, batch) --------------------------------
+// One CTA per SM walks a static list of tiles, heaviest first (under the causal mask key tile j
+// meets q_tiles - j query tiles): tile = blockIdx.x, + gridDim.x, ... with j = tile / (heads * batch).
+// TMEM, the barriers and the tensor-map prefetch are set up once per CTA instead of once per tile;
+// barrier parities therefore run on counters that persist across tiles (`it`: tiles done by this
+// CTA, `sbase`: query tiles streamed so far). Tiles are separated by a CTA-wide barrier.
 template <int D>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -529,12 +534,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(reinterpret_cast<uint8_t*>(sAux) + C::kAuxBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int j = blockIdx.x;  // key/value tile
   const int q_tiles = (p.seq_q + kTile - 1) / kTile;
-  const int i0 = p.causal ? j : 0;
-  const int nq = max(q_tiles - i0, 0);
-  const int U = 2 * nq;
+  const int kv_tiles = (p.seq_k + kTile - 1) / kTile;
+  const int hb = p.heads * p.batch;
+  const int total_tiles = kv_tiles * hb;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->res_full, 1);
@@ -553,7 +556,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  int p_stage = 0;           // producer: ring position of the next query-tile stage (persists across tiles)
+  uint32_t p_phase = 0;
+  int sbase = 0;             // query tiles streamed by this CTA before the current tile
 
+  for (int tile = blockIdx.x, it = 0; tile < total_tiles; tile += gridDim.x, ++it) {
+  const int j = tile / hb;                       // key/value tile
+  const int head = (tile % hb) % p.heads, batch = (tile % hb) / p.heads;
+  const int i0 = p.causal ? j : 0;
+  const int nq = max(q_tiles - i0, 0);
+  const int U = 2 * nq;
   if (warp == 0) {
     if (elect_one()) {
       mbar_expect_tx(&bars->res_full, C::kResidentBytes);
@@ -562,8 +574,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tma_load_4d(sK + h * 16384, &tk, &bars->res_full, h * 64, j * kTile, head, batch);
         tma_load_4d(sV + h * 16384, &tv, &bars->res_full, h * 64, j * kTile, head, batch);
       }
-      int stage = 0;
-      uint32_t phase = 0;
+      int stage = p_stage;
+      uint32_t phase = p_phase;
       for (int t = 0; t < nq; ++t) {
         if (!mbar_wait(&bars->st_empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
         uint8_t* sq = sStage + stage * C::kStageBytes;
@@ -577,6 +589,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         if (++stage == 2) { stage = 0; phase ^= 1; }
       }
     }
+    // every lane tracks the ring position, whichever lane is elected next time
+    p_phase ^= static_cast<uint32_t>(((p_stage + nq) >> 1) & 1);
+    p_stage = (p_stage + nq) & 1;
   } else if (warp == 1) {
     if (elect_one()) {
       const int fmt = p.dtype == kBF16 ? 1 : 0;
@@ -589,7 +604,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       const uint64_t dQk0 = make_smem_desc_sw128(smem_u32(sStage), 16, 1024);          // K-major view
       const uint64_t dQm0 = make_smem_desc_sw128(smem_u32(sStage), 16384, 1024);       // MN-major view
       auto issue_sdp = [&](int u) {
-        const int stage = (u >> 1) & 1, sub = u & 1, b = u & 1;
+        const int stage = (sbase + (u >> 1)) & 1, sub = u & 1, b = u & 1;
         const uint64_t dQ = desc_advance(dQk0, stage * C::kStageBytes + sub * 8192);
         const uint64_t dDO = desc_advance(dQ, C::kTileBytes);
 #pragma unroll
@@ -606,15 +621,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
                        desc_advance(dDO, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
         tc_commit(&bars->s_full[b]);
       };
-      bool ok = mbar_wait(&bars->res_full, 0, p.status, kStatusTimeoutFull);
+      bool ok = mbar_wait(&bars->res_full, it & 1, p.status, kStatusTimeoutFull);
       if (ok && U > 0) {
-        ok = mbar_wait(&bars->st_full[0], 0, p.status, kStatusTimeoutFull);
+        ok = mbar_wait(&bars->st_full[sbase & 1], (sbase >> 1) & 1, p.status, kStatusTimeoutFull);
         tc_fence_after();
         if (ok) { issue_sdp(0); issue_sdp(1); }
       }
       for (int u = 0; u < U && ok; ++u) {
-        const int b = u & 1, stage = (u >> 1) & 1, sub = u & 1;
-        ok = mbar_wait(&bars->p_full[b], (u >> 1) & 1, p.status, kStatusTimeoutTmemFull);
+        const int b = u & 1, stage = (sbase + (u >> 1)) & 1, sub = u & 1;
+        ok = mbar_wait(&bars->p_full[b], (sbase + (u >> 1)) & 1, p.status, kStatusTimeoutTmemFull);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dQ = desc_advance(dQm0, stage * C::kStageBytes + sub * 8192);
@@ -632,7 +647,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         if (u + 2 < U) {
           const int u2 = u + 2;
           if ((u2 & 1) == 0) {
-            ok = mbar_wait(&bars->st_full[(u2 >> 1) & 1], (u2 >> 2) & 1, p.status, kStatusTimeoutFull);
+            const int sq = sbase + (u2 >> 1);
+            ok = mbar_wait(&bars->st_full[sq & 1], (sq >> 1) & 1, p.status, kStatusTimeoutFull);
             if (!ok) break;
             tc_fence_after();
           }
@@ -684,7 +700,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         const float* a_del = a_lse + 64;
         const uint32_t s_addr = tmem_base + sub * 128 + wg * 32 + lane_bits;
         const uint32_t dp_addr = s_addr + 64;
-        ok = mbar_wait(&bars->s_full[sub], t & 1, p.status, kStatusTimeoutTmemFull);
+        ok = mbar_wait(&bars->s_full[sub], (sbase + t) & 1, p.status, kStatusTimeoutTmemFull);
         if (!ok) break;
         tc_fence_after();
         uint32_t rs[32], rd[32];
@@ -693,18 +709,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tmem_ld_32x32b_x32(dp_addr, rd);
         tmem_ld_wait();
         uint32_t pk[16], dk[16];
+        // lse / delta come as 16-byte broadcast loads (four query columns each); only the tile on
+        // the diagonal pays for the causal mask
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int col = 2 * x;                           // query column among this warpgroup's 32
-          const int ql = sub * 64 + wg * 32 + col;         // query row inside the 128-row tile
-          float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, -a_lse[col]));
-          float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, -a_lse[col + 1]));
-          if (diag && r_local > ql) p0 = 0.f;
-          if (diag && r_local > ql + 1) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rd[2 * x]) - a_del[col]);
-          const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - a_del[col + 1]);
-          pk[x] = pack_pair(p0, p1, p.dtype);
-          dk[x] = pack_pair(d0, d1, p.dtype);
+        for (int y = 0; y < 8; ++y) {
+          const float4 l4 = *reinterpret_cast<const float4*>(a_lse + 4 * y);
+          const float4 e4 = *reinterpret_cast<const float4*>(a_del + 4 * y);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, ev[4] = {e4.x, e4.y, e4.z, e4.w};
+          float pv[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) pv[c] = exp2f(fmaf(__uint_as_float(rs[4 * y + c]), sl2, -lv[c]));
+          if (diag) {
+            const int ql = sub * 64 + wg * 32 + 4 * y;     // query row inside the 128-row tile
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              if (r_local > ql + c) pv[c] = 0.f;
+          }
+          float dv[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) dv[c] = pv[c] * (__uint_as_float(rd[4 * y + c]) - ev[c]);
+          pk[2 * y] = pack_pair(pv[0], pv[1], p.dtype);
+          pk[2 * y + 1] = pack_pair(pv[2], pv[3], p.dtype);
+          dk[2 * y] = pack_pair(dv[0], dv[1], p.dtype);
+          dk[2 * y + 1] = pack_pair(dv[2], dv[3], p.dtype);
         }
         tmem_st_32x32b_x16(s_addr, pk);
         tmem_st_32x32b_x16(dp_addr, dk);
@@ -718,7 +745,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       }
     }
     // epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK * scale
-    if (ok) ok = mbar_wait(&bars->done, 0, p.status, kStatusTimeoutTmemFull);
+    if (ok) ok = mbar_wait(&bars->done, it & 1, p.status, kStatusTimeoutTmemFull);
     ok = __all_sync(0xffffffffu, ok);
     if (ok && U > 0) {
       tc_fence_after();
@@ -749,6 +776,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         }
       }
     }
+  }
+  // end of tile: the accumulators have been read, every MMA and copy of the tile has completed
+  sbase += nq;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) break;   // a wait gave up: stop
   }
   tc_fence_before();
   __syncthreads();
@@ -910,17 +944,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       tmem_ld_32x32b_x32(dp_addr, rd);
       tmem_ld_wait();
       uint32_t dk[16];
+      const float neg_lse = -lse2;
+      if (!(diag || ragged)) {   // the common case carries no mask
 #pragma unroll
-      for (int x = 0; x < 16; ++x) {
-        const int col = 2 * x;
-        const int kl = sub * 64 + wg * 32 + col;      // key row inside the 128-row tile
-        float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, -lse2));
-        float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, -lse2));
-        if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
-        if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
-        const float d0 = p0 * (__uint_as_float(rd[2 * x]) - delta);
-        const float d1 = p1 * (__uint_as_float(rd[2 * x + 1]) - delta);
-        dk[x] = pack_pair(d0, d1, p.dtype);
+        for (int x = 0; x < 16; ++x) {
+          const float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, neg_lse));
+          const float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, neg_lse));
+          dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
+                            p.dtype);
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const int col = 2 * x;
+          const int kl = sub * 64 + wg * 32 + col;      // key row inside the 128-row tile
+          float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, neg_lse));
+          float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, neg_lse));
+          if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
+          if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
+          dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
+                            p.dtype);
+        }
       }
       tmem_st_32x32b_x16(dp_addr, dk);
       tmem_st_wait();
@@ -964,6 +1008,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   }
 }
 
+// SMs of the current device (persistent kernels launch one CTA per SM).
+static int attn_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
+  }
+  return cached[dev];
+}
+
 template <int D>
 cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
   using C = BwdCfg<D>;
@@ -991,8 +1049,11 @@ cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
     const int64_t blocks = (rows + static_cast<int64_t>(rows_per_block) * kDeltaRows - 1) / (rows_per_block * kDeltaRows);
     attn_delta_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(a);
   }
-  dim3 gkv((a.seq_k + kTile - 1) / kTile, a.heads, a.batch);
-  attn_bwd_dkdv_kernel<D><<<gkv, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+  {
+    const int tiles = ((a.seq_k + kTile - 1) / kTile) * a.heads * a.batch;
+    const int sms = attn_sm_count();
+    attn_bwd_dkdv_kernel<D><<<tiles < sms ? tiles : sms, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+  }
   dim3 gq((a.seq_q + kTile - 1) / kTile, a.heads, a.batch);
   attn_bwd_dq_kernel<D><<<gq, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
   count_launch(3);
