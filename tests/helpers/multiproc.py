@@ -45,11 +45,24 @@ def run_ranks(world, fn, *args, timeout=240, backend="gloo"):
             p.start()
         for p in procs:
             p.join(timeout)
-        hung = [p for p in procs if p.is_alive()]
-        for p in hung:
-            p.terminate()
+        hung = [r for r, p in enumerate(procs) if p.is_alive()]
+        for r in hung:
+            procs[r].terminate()
         if hung:
-            raise RuntimeError(f"{len(hung)} rank(s) did not finish within {timeout}s (deadlock watchdog)")
+            # a rank that failed or died leaves its peers waiting in their next collective: say what
+            # happened to the ranks that did finish, not only that the others never did
+            notes = []
+            for r in range(world):
+                path = os.path.join(outdir, f"rank{r}.pt")
+                if r in hung:
+                    notes.append(f"rank {r}: still running")
+                elif not os.path.exists(path):
+                    notes.append(f"rank {r}: exited with code {procs[r].exitcode} and no result")
+                else:
+                    rec = torch.load(path, weights_only=False)
+                    notes.append(f"rank {r}: finished" if rec["ok"] else f"rank {r} failed:\n{rec['error']}")
+            raise RuntimeError(f"{len(hung)} rank(s) did not finish within {timeout}s (deadlock watchdog)\n" +
+                               "\n".join(notes))
         out = []
         for r in range(world):
             path = os.path.join(outdir, f"rank{r}.pt")
