@@ -125,7 +125,7 @@ struct FwdBarriers {
   uint32_t pad;
 };
 
-template <int D>
+template <int D, int DT>
 __global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const AttnArgs p) {
@@ -202,7 +202,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      const int fmt = p.dtype == kBF16 ? 1 : 0;
+      const int fmt = DT == kBF16 ? 1 : 0;
       const uint32_t idesc_qk = make_idesc_f16(fmt, 0, 0, 128, 128);
       const uint32_t idesc_pv = make_idesc_f16(fmt, 0, 1, 128, D);
       bool ok = mbar_wait(&bars->q_full, 0, p.status, kStatusTimeoutFull);
@@ -352,7 +352,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           const float p1 = exp2f(fmaf(__uint_as_float(r[c][2 * i + 1]), sl2, -m_run));
           ls0 += p0;
           ls1 += p1;
-          pk[i] = pack_pair(p0, p1, p.dtype);
+          pk[i] = pack_pair(p0, p1, DT);
         }
         tmem_st_32x32b_x16(s_addr + c * 16, pk);
       }
@@ -383,10 +383,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 o;
-            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l, p.dtype);
-            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l, p.dtype);
-            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l, p.dtype);
-            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l, p.dtype);
+            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l, DT);
+            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l, DT);
+            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l, DT);
+            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l, DT);
             dst[q] = o;
           }
         }
@@ -405,7 +405,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   }
 }
 
-template <int D>
+template <int D, int DT>
 cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
   using C = FwdCfg<D>;
   CUtensorMap tq, tk, tv;
@@ -418,13 +418,13 @@ cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
   if (e != cudaSuccess) return e;
   static bool attr = false;
   if (!attr) {
-    e = cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(attn_fwd_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr = true;
   }
   dim3 grid((a.seq_q + 2 * kTile - 1) / (2 * kTile), a.heads, a.batch);
-  attn_fwd_kernel<D><<<grid, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a);
+  attn_fwd_kernel<D, DT><<<grid, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a);
   count_launch();
   return cudaGetLastError();
 }
@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs p) {
 // TMEM, the barriers and the tensor-map prefetch are set up once per CTA instead of once per tile;
 // barrier parities therefore run on counters that persist across tiles (`it`: tiles done by this
 // CTA, `sbase`: query tiles streamed so far). Tiles are separated by a CTA-wide barrier.
-template <int D>
+template <int D, int DT>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                      const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
@@ -594,7 +594,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     p_stage = (p_stage + nq) & 1;
   } else if (warp == 1) {
     if (elect_one()) {
-      const int fmt = p.dtype == kBF16 ? 1 : 0;
+      const int fmt = DT == kBF16 ? 1 : 0;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, 128, 64);
       const uint32_t idesc_acc = make_idesc_f16(fmt, 0, 1, 128, D);
       // One thread issues every MMA and the score MMAs are short (N = 64), so the issue path must
@@ -728,10 +728,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
           float dv[4];
 #pragma unroll
           for (int c = 0; c < 4; ++c) dv[c] = pv[c] * (__uint_as_float(rd[4 * y + c]) - ev[c]);
-          pk[2 * y] = pack_pair(pv[0], pv[1], p.dtype);
-          pk[2 * y + 1] = pack_pair(pv[2], pv[3], p.dtype);
-          dk[2 * y] = pack_pair(dv[0], dv[1], p.dtype);
-          dk[2 * y + 1] = pack_pair(dv[2], dv[3], p.dtype);
+          pk[2 * y] = pack_pair(pv[0], pv[1], DT);
+          pk[2 * y + 1] = pack_pair(pv[2], pv[3], DT);
+          dk[2 * y] = pack_pair(dv[0], dv[1], DT);
+          dk[2 * y + 1] = pack_pair(dv[2], dv[3], DT);
         }
         tmem_st_32x32b_x16(s_addr, pk);
         tmem_st_32x32b_x16(dp_addr, dk);
@@ -767,10 +767,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 o;
-            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul, p.dtype);
-            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul, p.dtype);
-            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul, p.dtype);
-            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul, p.dtype);
+            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul, DT);
+            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul, DT);
+            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul, DT);
+            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul, DT);
             dst[q] = o;
           }
         }
@@ -793,7 +793,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
 }
 
 // ---- dQ: one CTA per (query tile, head, batch) ---------------------------------------------------
-template <int D>
+template <int D, int DT>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
@@ -857,7 +857,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      const int fmt = p.dtype == kBF16 ? 1 : 0;
+      const int fmt = DT == kBF16 ? 1 : 0;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, 128, 64);
       const uint32_t idesc_acc = make_idesc_f16(fmt, 0, 1, 128, D);
       // short issue path: tile-origin descriptors once, constants added per MMA
@@ -951,7 +951,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           const float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, neg_lse));
           const float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, neg_lse));
           dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
-                            p.dtype);
+                            DT);
         }
       } else {
 #pragma unroll
@@ -963,7 +963,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
           if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
           dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
-                            p.dtype);
+                            DT);
         }
       }
       tmem_st_32x32b_x16(dp_addr, dk);
@@ -990,10 +990,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 o;
-            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * p.scale, __uint_as_float(r[q * 8 + 1]) * p.scale, p.dtype);
-            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * p.scale, __uint_as_float(r[q * 8 + 3]) * p.scale, p.dtype);
-            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * p.scale, __uint_as_float(r[q * 8 + 5]) * p.scale, p.dtype);
-            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * p.scale, __uint_as_float(r[q * 8 + 7]) * p.scale, p.dtype);
+            o.x = pack_pair(__uint_as_float(r[q * 8 + 0]) * p.scale, __uint_as_float(r[q * 8 + 1]) * p.scale, DT);
+            o.y = pack_pair(__uint_as_float(r[q * 8 + 2]) * p.scale, __uint_as_float(r[q * 8 + 3]) * p.scale, DT);
+            o.z = pack_pair(__uint_as_float(r[q * 8 + 4]) * p.scale, __uint_as_float(r[q * 8 + 5]) * p.scale, DT);
+            o.w = pack_pair(__uint_as_float(r[q * 8 + 6]) * p.scale, __uint_as_float(r[q * 8 + 7]) * p.scale, DT);
             dst[q] = o;
           }
         }
@@ -1022,7 +1022,7 @@ static int attn_sm_count() {
   return cached[dev];
 }
 
-template <int D>
+template <int D, int DT>
 cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
   using C = BwdCfg<D>;
   CUtensorMap tq, tk, tv, tdo;
@@ -1032,9 +1032,9 @@ cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
   ETHB_TRY(make_tmap_bshd(&tdo, a.d_o, a.dtype, D, a.seq_q, a.heads, a.batch, a.do_strides, kTile), "bwd tensor map dO");
   static bool attr = false;
   if (!attr) {
-    ETHB_TRY(cudaFuncSetAttribute(attn_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    ETHB_TRY(cudaFuncSetAttribute(attn_bwd_dkdv_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   C::kSmemBytes), "bwd smem attribute dkdv");
-    ETHB_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    ETHB_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   C::kSmemBytes), "bwd smem attribute dq");
     attr = true;
   }
@@ -1052,10 +1052,10 @@ cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
   {
     const int tiles = ((a.seq_k + kTile - 1) / kTile) * a.heads * a.batch;
     const int sms = attn_sm_count();
-    attn_bwd_dkdv_kernel<D><<<tiles < sms ? tiles : sms, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+    attn_bwd_dkdv_kernel<D, DT><<<tiles < sms ? tiles : sms, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
   }
   dim3 gq((a.seq_q + kTile - 1) / kTile, a.heads, a.batch);
-  attn_bwd_dq_kernel<D><<<gq, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+  attn_bwd_dq_kernel<D, DT><<<gq, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
   count_launch(3);
   ETHB_TRY(cudaGetLastError(), "bwd kernel launch");
   return cudaSuccess;
@@ -1069,8 +1069,10 @@ cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(a.o) & 15) || a.o_strides[1] % 8 || a.o_strides[2] % 8 ||
       a.o_strides[0] % 8)
     return cudaErrorMisalignedAddress;
-  if (a.head_dim == 128) return launch_fwd<128>(a, st);
-  if (a.head_dim == 64) return launch_fwd<64>(a, st);
+  // one instantiation per element type: conversions in the softmax loops compile to one instruction
+  const bool bf = a.dtype == kBF16;
+  if (a.head_dim == 128) return bf ? launch_fwd<128, kBF16>(a, st) : launch_fwd<128, kF16>(a, st);
+  if (a.head_dim == 64) return bf ? launch_fwd<64, kBF16>(a, st) : launch_fwd<64, kF16>(a, st);
   return cudaErrorInvalidValue;
 }
 
@@ -1084,8 +1086,9 @@ cudaError_t attention_bwd(const AttnArgs& a, cudaStream_t st) {
     for (int k = 0; k < 3; ++k)
       if (strs[i][k] % 8) return cudaErrorMisalignedAddress;
   }
-  if (a.head_dim == 128) return launch_bwd<128>(a, st);
-  if (a.head_dim == 64) return launch_bwd<64>(a, st);
+  const bool bf = a.dtype == kBF16;
+  if (a.head_dim == 128) return bf ? launch_bwd<128, kBF16>(a, st) : launch_bwd<128, kF16>(a, st);
+  if (a.head_dim == 64) return bf ? launch_bwd<64, kBF16>(a, st) : launch_bwd<64, kF16>(a, st);
   ETHB_RETURN_IF(true, cudaErrorInvalidValue, "head_dim must be 64 or 128");
 }
 
