@@ -105,21 +105,22 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b, int dtype) {
 // ==============================================================================================
 template <int D> struct FwdCfg {
   static constexpr int kHalves = D / 64;
-  static constexpr int kStages = (D == 128) ? 2 : 4;
   static constexpr int kQBytes = 2 * kHalves * 16384;       // two query tiles
-  static constexpr int kKBytes = kHalves * 16384;
-  static constexpr int kVBytes = kHalves * 16384;
-  static constexpr int kStageBytes = kKBytes + kVBytes;
-  static constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + 1024 + 256;
+  // K and V tiles travel through one ring of equal slots in the order K_0 V_0 K_1 V_1 ...: a K
+  // slot is free again as soon as both score MMAs of its tile are done, a whole iteration before
+  // the V slot of the same tile, so five slots keep the loads a full iteration ahead of their use.
+  static constexpr int kSlotBytes = kHalves * 16384;
+  static constexpr int kSlots = (D == 128) ? 5 : 8;
+  static constexpr int kSmemBytes = kQBytes + kSlots * kSlotBytes + 1024 + 256;
   static constexpr int kThreads = 320;
 };
 
 struct FwdBarriers {
   uint64_t q_full;
-  uint64_t kv_full[4];
-  uint64_t kv_empty[4];
+  uint64_t kv_full[8];
+  uint64_t kv_empty[8];
   uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t p_half[4];     // [tile * 2 + half]: P columns 0-63 / 64-127 of a tile are written
   uint64_t o_done[2];
   uint32_t tmem_base;
   uint32_t pad;
@@ -135,7 +136,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + C::kQBytes;
-  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(sKV + C::kStages * C::kStageBytes);
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(sKV + C::kSlots * C::kSlotBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -154,13 +155,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < C::kSlots; ++s) {
       mbar_init(&bars->kv_full[s], 1);
       mbar_init(&bars->kv_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->p_half[2 * t], 4);       // one arrival per softmax warp
+      mbar_init(&bars->p_half[2 * t + 1], 4);
       mbar_init(&bars->o_done[t], 1);
     }
     fence_mbar_init();
@@ -184,19 +186,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         for (int h = 0; h < C::kHalves; ++h)
           tma_load_4d(sQ + (t * C::kHalves + h) * 16384, &tq, &bars->q_full, h * 64,
                       (2 * qb + t) * kTile, head, batch);
-      int stage = 0;
+      int slot = 0;
       uint32_t phase = 0;
-      for (int j = 0; j < n; ++j) {
-        if (!mbar_wait(&bars->kv_empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
-        uint8_t* sk = sKV + stage * C::kStageBytes;
-        uint8_t* sv = sk + C::kKBytes;
-        mbar_expect_tx(&bars->kv_full[stage], C::kStageBytes);
+      for (int i = 0; i < 2 * n; ++i) {   // item 2j is K_j, item 2j + 1 is V_j
+        if (!mbar_wait(&bars->kv_empty[slot], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
+        uint8_t* dst = sKV + slot * C::kSlotBytes;
+        mbar_expect_tx(&bars->kv_full[slot], C::kSlotBytes);
 #pragma unroll
-        for (int h = 0; h < C::kHalves; ++h) {
-          tma_load_4d(sk + h * 16384, &tk, &bars->kv_full[stage], h * 64, j * kTile, head, batch);
-          tma_load_4d(sv + h * 16384, &tv, &bars->kv_full[stage], h * 64, j * kTile, head, batch);
-        }
-        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        for (int h = 0; h < C::kHalves; ++h)
+          tma_load_4d(dst + h * 16384, (i & 1) ? &tv : &tk, &bars->kv_full[slot], h * 64, (i >> 1) * kTile, head,
+                      batch);
+        if (++slot == C::kSlots) { slot = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -210,10 +210,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       // origins are built once, each MMA only adds a constant to them.
       const uint64_t dq0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dk0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);
-      const uint64_t dv0 = make_smem_desc_sw128(smem_u32(sKV + C::kKBytes), 16384, 1024);
-      auto issue_qk = [&](int t, int stage) {
+      const uint64_t dv0 = make_smem_desc_sw128(smem_u32(sKV), 16384, 1024);
+      auto issue_qk = [&](int t, int slot) {
         const uint64_t dq = desc_advance(dq0, t * C::kHalves * 16384);
-        const uint64_t dk = desc_advance(dk0, stage * C::kStageBytes);
+        const uint64_t dk = desc_advance(dk0, slot * C::kSlotBytes);
 #pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
@@ -222,50 +222,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
                        desc_advance(dk, h * 16384 + k * 32), idesc_qk, (h | k) != 0 ? 1u : 0u);
         tc_commit(&bars->s_full[t]);
       };
-      auto issue_pv = [&](int t, int stage, int j) {
-        const uint64_t dv = desc_advance(dv0, stage * C::kStageBytes);
+      // O_t += P_t V_j in two halves of the key range: the first four MMAs start as soon as the
+      // softmax warps have written P columns 0-63, while they still compute columns 64-127.
+      auto issue_pv = [&](int t, int slot, int j) {
+        const uint64_t dv = desc_advance(dv0, slot * C::kSlotBytes);
+        bool got = true;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          tc_mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
-                        desc_advance(dv, k * 2048), idesc_pv, (j | k) != 0 ? 1u : 0u);
-        tc_commit(&bars->o_done[t]);
+        for (int half = 0; half < 2 && got; ++half) {
+          got = mbar_wait(&bars->p_half[2 * t + half], j & 1, p.status, kStatusTimeoutTmemFull);
+          tc_fence_after();
+          if (!got) break;
+#pragma unroll
+          for (int k = half * 4; k < half * 4 + 4; ++k)
+            tc_mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+                          desc_advance(dv, k * 2048), idesc_pv, (j | k) != 0 ? 1u : 0u);
+        }
+        if (got) tc_commit(&bars->o_done[t]);
+        return got;
+      };
+      // ring position of item i (K_j is item 2j, V_j item 2j + 1)
+      auto wait_item = [&](int i) {
+        const bool got = mbar_wait(&bars->kv_full[i % C::kSlots], (i / C::kSlots) & 1, p.status, kStatusTimeoutFull);
+        tc_fence_after();
+        return got;
       };
       if (ok && n > 0) {
-        ok = mbar_wait(&bars->kv_full[0], 0, p.status, kStatusTimeoutFull);
-        tc_fence_after();
+        ok = wait_item(0);
         if (ok) {
           if (n_t[0] > 0) issue_qk(0, 0);
           if (n_t[1] > 0) issue_qk(1, 0);
+          tc_commit(&bars->kv_empty[0]);
         }
       }
-      int stage = 0;
-      uint32_t phase = 0;
       for (int j = 0; j < n && ok; ++j) {
-        int nstage = stage + 1;
-        uint32_t nphase = phase;
-        if (nstage == C::kStages) { nstage = 0; nphase ^= 1; }
+        const int vslot = (2 * j + 1) % C::kSlots, kslot = (2 * j + 2) % C::kSlots;
+        ok = wait_item(2 * j + 1);
+        if (!ok) break;
         if (j < n_t[0]) {
-          ok = mbar_wait(&bars->p_full[0], j & 1, p.status, kStatusTimeoutTmemFull);
+          ok = issue_pv(0, vslot, j);
           if (!ok) break;
-          tc_fence_after();
-          issue_pv(0, stage, j);
         }
         if (j + 1 < n) {
-          ok = mbar_wait(&bars->kv_full[nstage], nphase, p.status, kStatusTimeoutFull);
+          ok = wait_item(2 * j + 2);
           if (!ok) break;
-          tc_fence_after();
         }
-        if (j + 1 < n_t[0]) issue_qk(0, nstage);
+        if (j + 1 < n_t[0]) issue_qk(0, kslot);
         if (j < n_t[1]) {
-          ok = mbar_wait(&bars->p_full[1], j & 1, p.status, kStatusTimeoutTmemFull);
+          ok = issue_pv(1, vslot, j);
           if (!ok) break;
-          tc_fence_after();
-          issue_pv(1, stage, j);
         }
-        tc_commit(&bars->kv_empty[stage]);
-        if (j + 1 < n_t[1]) issue_qk(1, nstage);
-        stage = nstage;
-        phase = nphase;
+        tc_commit(&bars->kv_empty[vslot]);
+        if (j + 1 < n_t[1]) issue_qk(1, kslot);
+        if (j + 1 < n) tc_commit(&bars->kv_empty[kslot]);
       }
     }
   } else {
@@ -355,12 +363,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           pk[i] = pack_pair(p0, p1, DT);
         }
         tmem_st_32x32b_x16(s_addr + c * 16, pk);
+        if (c & 1) {   // a half of the key range is complete: hand it to the MMA warp
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->p_half[2 * t + (c >> 1)]);
+        }
       }
       const float lsum = ls0 + ls1;
       l_run += lsum;
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bars->p_full[t]);
     }
     if (ok && nt > 0) {
       ok = mbar_wait(&bars->o_done[t], (nt - 1) & 1, p.status, kStatusTimeoutTmemFull);
@@ -545,7 +556,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       mbar_init(&bars->st_full[s], 1);
       mbar_init(&bars->st_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_full[s], 256);    // both softmax warpgroups work on every sub-tile
+      mbar_init(&bars->p_full[s], 8);      // both softmax warpgroups work on every sub-tile, one arrival per warp
     }
     mbar_init(&bars->done, 1);
     fence_mbar_init();
@@ -737,7 +748,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tmem_st_32x32b_x16(dp_addr, dk);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&bars->p_full[sub]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[sub]);   // one arrival per warp
       }
       if (wg_tid < 64 && t + 1 < nq) {
         aux_slot(t + 1)[wg_tid] = next_lse;
@@ -820,7 +832,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       mbar_init(&bars->st_full[s], 1);
       mbar_init(&bars->st_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_full[s], 256);    // both softmax warpgroups work on every sub-tile
+      mbar_init(&bars->p_full[s], 8);      // both softmax warpgroups work on every sub-tile, one arrival per warp
     }
     mbar_init(&bars->done, 1);
     fence_mbar_init();
@@ -969,7 +981,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       tmem_st_32x32b_x16(dp_addr, dk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->p_full[sub]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full[sub]);   // one arrival per warp
     }
     if (ok) ok = mbar_wait(&bars->done, 0, p.status, kStatusTimeoutTmemFull);
     ok = __all_sync(0xffffffffu, ok);
