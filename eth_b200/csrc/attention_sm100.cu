@@ -140,9 +140,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y, batch = blockIdx.z;
-  // heavy (late) query blocks first so the causal triangle balances across waves
-  const int qb = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  // 1-D grid, dispatched in index order: all (head, batch) pairs of the heaviest (latest) query
+  // block first, the lightest last, so that the causal triangle balances across the SMs and the
+  // last CTAs to start are the short ones
+  const int bh = blockIdx.x % (p.heads * p.batch), slot = blockIdx.x / (p.heads * p.batch);
+  const int head = bh % p.heads, batch = bh / p.heads;
+  const int q_blocks = gridDim.x / (p.heads * p.batch);
+  const int qb = p.causal ? (q_blocks - 1 - slot) : slot;
   const int kv_tiles = (p.seq_k + kTile - 1) / kTile;
   int n_t[2];
 #pragma unroll
@@ -434,8 +438,8 @@ cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     attr = true;
   }
-  dim3 grid((a.seq_q + 2 * kTile - 1) / (2 * kTile), a.heads, a.batch);
-  attn_fwd_kernel<D, DT><<<grid, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a);
+  const int q_blocks = (a.seq_q + 2 * kTile - 1) / (2 * kTile);
+  attn_fwd_kernel<D, DT><<<q_blocks * a.heads * a.batch, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a);
   count_launch();
   return cudaGetLastError();
 }
@@ -820,8 +824,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(sStage + C::kStages * C::kStageBytes + C::kAuxBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int i = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // query tile, heavy first
+  // 1-D grid in dispatch order: every (head, batch) pair of the heaviest query tile first
+  const int bh = blockIdx.x % (p.heads * p.batch), slot = blockIdx.x / (p.heads * p.batch);
+  const int head = bh % p.heads, batch = bh / p.heads;
+  const int q_tiles_total = gridDim.x / (p.heads * p.batch);
+  const int i = p.causal ? (q_tiles_total - 1 - slot) : slot;  // query tile, heavy first
   const int kv_tiles = (p.seq_k + kTile - 1) / kTile;
   const int nkv = p.causal ? min(i + 1, kv_tiles) : kv_tiles;
   const int U = 2 * nkv;
@@ -1067,7 +1074,7 @@ cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
     const int sms = attn_sm_count();
     attn_bwd_dkdv_kernel<D, DT><<<tiles < sms ? tiles : sms, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
   }
-  dim3 gq((a.seq_q + kTile - 1) / kTile, a.heads, a.batch);
+  const int gq = ((a.seq_q + kTile - 1) / kTile) * a.heads * a.batch;
   attn_bwd_dq_kernel<D, DT><<<gq, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
   count_launch(3);
   ETHB_TRY(cudaGetLastError(), "bwd kernel launch");
