@@ -120,7 +120,7 @@ struct FwdBarriers {
   uint64_t kv_full[8];
   uint64_t kv_empty[8];
   uint64_t s_full[2];
-  uint64_t p_half[4];     // [tile * 2 + half]: P columns 0-63 / 64-127 of a tile are written
+  uint64_t p_half[8];     // [tile * 4 + quarter]: 32 more P columns of a tile are written
   uint64_t o_done[2];
   uint32_t tmem_base;
   uint32_t pad;
@@ -165,8 +165,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_half[2 * t], 4);       // one arrival per softmax warp
-      mbar_init(&bars->p_half[2 * t + 1], 4);
+      for (int q = 0; q < 4; ++q) mbar_init(&bars->p_half[4 * t + q], 4);   // one arrival per softmax warp
       mbar_init(&bars->o_done[t], 1);
     }
     fence_mbar_init();
@@ -232,12 +231,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const uint64_t dv = desc_advance(dv0, slot * C::kSlotBytes);
         bool got = true;
 #pragma unroll
-        for (int half = 0; half < 2 && got; ++half) {
-          got = mbar_wait(&bars->p_half[2 * t + half], j & 1, p.status, kStatusTimeoutTmemFull);
+        for (int half = 0; half < 4 && got; ++half) {
+          got = mbar_wait(&bars->p_half[4 * t + half], j & 1, p.status, kStatusTimeoutTmemFull);
           tc_fence_after();
           if (!got) break;
 #pragma unroll
-          for (int k = half * 4; k < half * 4 + 4; ++k)
+          for (int k = half * 2; k < half * 2 + 2; ++k)
             tc_mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
                           desc_advance(dv, k * 2048), idesc_pv, (j | k) != 0 ? 1u : 0u);
         }
@@ -367,11 +366,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           pk[i] = pack_pair(p0, p1, DT);
         }
         tmem_st_32x32b_x16(s_addr + c * 16, pk);
-        if (c & 1) {   // a half of the key range is complete: hand it to the MMA warp
+        {   // a quarter of the key range is complete: hand it to the MMA warp
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->p_half[2 * t + (c >> 1)]);
+          if (lane == 0) mbar_arrive(&bars->p_half[4 * t + c]);
         }
       }
       const float lsum = ls0 + ls1;
