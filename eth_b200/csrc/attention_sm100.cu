@@ -528,7 +528,8 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs p) {
 
 // ---- dK / dV: persistent CTAs over (key/value tile, head, batch) --------------------------------
 // One CTA per SM walks a static list of tiles, heaviest first (under the causal mask key tile j
-// meets q_tiles - j query tiles): tile = blockIdx.x, + gridDim.x, ... with j = tile / (heads * batch).
+// meets q_tiles - j query tiles), handed out round by round in alternating CTA order, with
+// j = tile / (heads * batch).
 // TMEM, the barriers and the tensor-map prefetch are set up once per CTA instead of once per tile;
 // barrier parities therefore run on counters that persist across tiles (`it`: tiles done by this
 // CTA, `sbase`: query tiles streamed so far). Tiles are separated by a CTA-wide barrier.
@@ -574,7 +575,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   uint32_t p_phase = 0;
   int sbase = 0;             // query tiles streamed by this CTA before the current tile
 
-  for (int tile = blockIdx.x, it = 0; tile < total_tiles; tile += gridDim.x, ++it) {
+  // Round r hands out tiles [r * grid, (r + 1) * grid), heaviest first, in alternating direction
+  // (CTA 0 gets the heaviest tile of an even round and the lightest of an odd one), so the tile
+  // weights of a CTA add up to nearly the same total everywhere; `it` counts the tiles this CTA
+  // has processed (barrier parities run on it).
+  for (int round = 0, it = 0; round * static_cast<int>(gridDim.x) < total_tiles; ++round) {
+  const int tile = round * gridDim.x + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+  if (tile >= total_tiles) continue;             // only in the last round
   const int j = tile / hb;                       // key/value tile
   const int head = (tile % hb) % p.heads, batch = (tile % hb) / p.heads;
   const int i0 = p.causal ? j : 0;
@@ -794,6 +801,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   }
   // end of tile: the accumulators have been read, every MMA and copy of the tile has completed
   sbase += nq;
+  ++it;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();

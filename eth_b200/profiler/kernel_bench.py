@@ -123,6 +123,13 @@ def main(argv=None):
             native.check_status()
             rec = {"kernel": "attention_bwd", "B": B, "S": S, "H": H, "D": D, "ms_median": med,
                    "tflops": 2.5 * fl / med / 1e9}
+            if args.compare:   # the library backward (cuDNN / flash kernels behind torch SDPA) on the same tensors
+                qt, kt, vt = (t.detach().permute(0, 2, 1, 3).clone().requires_grad_(True) for t in (q, k, v))
+                ot = torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
+                dot = torch.randn_like(ot)
+                med2, _ = time_fn(lambda: torch.autograd.grad(ot, (qt, kt, vt), dot, retain_graph=True),
+                                  args.warmup, args.repeat)
+                rec["torch_sdpa_bwd_ms"] = med2
         out.append(rec)
     elif args.kind == "ln":
         x = torch.randn(args.rows, args.hidden, device="cuda", dtype=dt)
