@@ -532,7 +532,9 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs p) {
 // j = tile / (heads * batch).
 // TMEM, the barriers and the tensor-map prefetch are set up once per CTA instead of once per tile;
 // barrier parities therefore run on counters that persist across tiles (`it`: tiles done by this
-// CTA, `sbase`: query tiles streamed so far). Tiles are separated by a CTA-wide barrier.
+// CTA, `sbase`: query tiles streamed so far). No CTA-wide barrier
+// separates the tiles: the loads and first score MMAs of the next tile overlap the accumulator stores
+// of the current one.
 template <int D, int DT>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -589,15 +591,20 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   const int U = 2 * nq;
   if (warp == 0) {
     if (elect_one()) {
-      mbar_expect_tx(&bars->res_full, C::kResidentBytes);
+      // the resident K / V buffers are free once every MMA of the previous tile has completed; the
+      // loads of this tile then run while the other warps still store the previous accumulators
+      bool free_kv = it == 0 || mbar_wait(&bars->done, (it - 1) & 1, p.status, kStatusTimeoutTmemFull);
+      if (free_kv) {
+        mbar_expect_tx(&bars->res_full, C::kResidentBytes);
 #pragma unroll
-      for (int h = 0; h < C::kHalves; ++h) {
-        tma_load_4d(sK + h * 16384, &tk, &bars->res_full, h * 64, j * kTile, head, batch);
-        tma_load_4d(sV + h * 16384, &tv, &bars->res_full, h * 64, j * kTile, head, batch);
+        for (int h = 0; h < C::kHalves; ++h) {
+          tma_load_4d(sK + h * 16384, &tk, &bars->res_full, h * 64, j * kTile, head, batch);
+          tma_load_4d(sV + h * 16384, &tv, &bars->res_full, h * 64, j * kTile, head, batch);
+        }
       }
       int stage = p_stage;
       uint32_t phase = p_phase;
-      for (int t = 0; t < nq; ++t) {
+      for (int t = 0; t < nq && free_kv; ++t) {
         if (!mbar_wait(&bars->st_empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
         uint8_t* sq = sStage + stage * C::kStageBytes;
         uint8_t* sdo = sq + C::kTileBytes;
@@ -799,12 +806,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       }
     }
   }
-  // end of tile: the accumulators have been read, every MMA and copy of the tile has completed
+  // End of tile, without a CTA-wide barrier: the roles meet again only through the mbarriers. The
+  // producer waits for `done` before it refills K / V; the first dV / dK MMAs of the next tile
+  // (which overwrite the accumulators) wait for that tile's first P, and a softmax warp writes that
+  // only after it has stored its part of these accumulators.
   sbase += nq;
   ++it;
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) break;   // a wait gave up: stop
   }
   tc_fence_before();
