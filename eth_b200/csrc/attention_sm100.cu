@@ -822,7 +822,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   }
 }
 
-// ---- dQ: one CTA per (query tile, head, batch) ---------------------------------------------------
+// ---- dQ: persistent CTAs over (query tile, head, batch) -----------------------------------------
+// Like the dK / dV kernel: one CTA per SM, tiles heaviest first (query tile i meets i + 1 key tiles
+// under the causal mask) handed out round by round in alternating CTA order, TMEM and barriers set
+// up once, parities on counters that persist across tiles (`it`, `sbase`), and no CTA-wide barrier
+// between tiles: the Q / dO loads and first score MMAs of the next tile overlap the dQ store.
 template <int D, int DT>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -838,14 +842,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(sStage + C::kStages * C::kStageBytes + C::kAuxBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid in dispatch order: every (head, batch) pair of the heaviest query tile first
-  const int bh = blockIdx.x % (p.heads * p.batch), slot = blockIdx.x / (p.heads * p.batch);
-  const int head = bh % p.heads, batch = bh / p.heads;
-  const int q_tiles_total = gridDim.x / (p.heads * p.batch);
-  const int i = p.causal ? (q_tiles_total - 1 - slot) : slot;  // query tile, heavy first
+  const int hb = p.heads * p.batch;
+  const int q_tiles_total = (p.seq_q + kTile - 1) / kTile;
   const int kv_tiles = (p.seq_k + kTile - 1) / kTile;
-  const int nkv = p.causal ? min(i + 1, kv_tiles) : kv_tiles;
-  const int U = 2 * nkv;
+  const int total_tiles = q_tiles_total * hb;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->res_full, 1);
@@ -864,18 +864,33 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  int p_stage = 0;           // producer: ring position of the next key/value stage (persists across tiles)
+  uint32_t p_phase = 0;
+  int sbase = 0;             // key/value tiles streamed by this CTA before the current tile
 
+  for (int round = 0, it = 0; round * static_cast<int>(gridDim.x) < total_tiles; ++round) {
+  const int tile = round * gridDim.x + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+  if (tile >= total_tiles) continue;             // only in the last round
+  const int slot = tile / hb;
+  const int head = (tile % hb) % p.heads, batch = (tile % hb) / p.heads;
+  const int i = p.causal ? (q_tiles_total - 1 - slot) : slot;  // query tile, heavy first
+  const int nkv = p.causal ? min(i + 1, kv_tiles) : kv_tiles;
+  const int U = 2 * nkv;
   if (warp == 0) {
     if (elect_one()) {
-      mbar_expect_tx(&bars->res_full, C::kResidentBytes);
+      // Q / dO are free once every MMA of the previous tile has completed
+      const bool free_q = it == 0 || mbar_wait(&bars->done, (it - 1) & 1, p.status, kStatusTimeoutTmemFull);
+      if (free_q) {
+        mbar_expect_tx(&bars->res_full, C::kResidentBytes);
 #pragma unroll
-      for (int h = 0; h < C::kHalves; ++h) {
-        tma_load_4d(sQ + h * 16384, &tq, &bars->res_full, h * 64, i * kTile, head, batch);
-        tma_load_4d(sDO + h * 16384, &tdo, &bars->res_full, h * 64, i * kTile, head, batch);
+        for (int h = 0; h < C::kHalves; ++h) {
+          tma_load_4d(sQ + h * 16384, &tq, &bars->res_full, h * 64, i * kTile, head, batch);
+          tma_load_4d(sDO + h * 16384, &tdo, &bars->res_full, h * 64, i * kTile, head, batch);
+        }
       }
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int t = 0; t < nkv; ++t) {
+      int stage = p_stage;
+      uint32_t phase = p_phase;
+      for (int t = 0; t < nkv && free_q; ++t) {
         if (!mbar_wait(&bars->st_empty[stage], phase ^ 1, p.status, kStatusTimeoutEmpty)) break;
         uint8_t* sk = sStage + stage * C::kStageBytes;
         uint8_t* sv = sk + C::kTileBytes;
@@ -888,6 +903,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         if (++stage == 2) { stage = 0; phase ^= 1; }
       }
     }
+    // every lane tracks the ring position, whichever lane is elected next time
+    p_phase ^= static_cast<uint32_t>(((p_stage + nkv) >> 1) & 1);
+    p_stage = (p_stage + nkv) & 1;
   } else if (warp == 1) {
     if (elect_one()) {
       const int fmt = DT == kBF16 ? 1 : 0;
@@ -899,7 +917,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       const uint64_t dKk0 = make_smem_desc_sw128(smem_u32(sStage), 16, 1024);          // K-major view
       const uint64_t dKm0 = make_smem_desc_sw128(smem_u32(sStage), 16384, 1024);       // MN-major view
       auto issue_sdp = [&](int u) {
-        const int stage = (u >> 1) & 1, sub = u & 1, b = u & 1;
+        const int stage = (sbase + (u >> 1)) & 1, sub = u & 1, b = u & 1;
         const uint64_t dK = desc_advance(dKk0, stage * C::kStageBytes + sub * 8192);
         const uint64_t dV = desc_advance(dK, C::kTileBytes);
 #pragma unroll
@@ -916,15 +934,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
                        desc_advance(dV, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
         tc_commit(&bars->s_full[b]);
       };
-      bool ok = mbar_wait(&bars->res_full, 0, p.status, kStatusTimeoutFull);
+      bool ok = mbar_wait(&bars->res_full, it & 1, p.status, kStatusTimeoutFull);
       if (ok && U > 0) {
-        ok = mbar_wait(&bars->st_full[0], 0, p.status, kStatusTimeoutFull);
+        ok = mbar_wait(&bars->st_full[sbase & 1], (sbase >> 1) & 1, p.status, kStatusTimeoutFull);
         tc_fence_after();
         if (ok) { issue_sdp(0); issue_sdp(1); }
       }
       for (int u = 0; u < U && ok; ++u) {
-        const int b = u & 1, stage = (u >> 1) & 1, sub = u & 1;
-        ok = mbar_wait(&bars->p_full[b], (u >> 1) & 1, p.status, kStatusTimeoutTmemFull);
+        const int b = u & 1, stage = (sbase + (u >> 1)) & 1, sub = u & 1;
+        ok = mbar_wait(&bars->p_full[b], (sbase + (u >> 1)) & 1, p.status, kStatusTimeoutTmemFull);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dK = desc_advance(dKm0, stage * C::kStageBytes + sub * 8192);
@@ -936,7 +954,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         if (u + 2 < U) {
           const int u2 = u + 2;
           if ((u2 & 1) == 0) {
-            ok = mbar_wait(&bars->st_full[(u2 >> 1) & 1], (u2 >> 2) & 1, p.status, kStatusTimeoutFull);
+            const int sq = sbase + (u2 >> 1);
+            ok = mbar_wait(&bars->st_full[sq & 1], (sq >> 1) & 1, p.status, kStatusTimeoutFull);
             if (!ok) break;
             tc_fence_after();
           }
@@ -965,7 +984,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       const int t = u >> 1, sub = u & 1;
       const uint32_t s_addr = tmem_base + sub * 128 + wg * 32 + lane_bits;
       const uint32_t dp_addr = s_addr + 64;
-      ok = mbar_wait(&bars->s_full[sub], t & 1, p.status, kStatusTimeoutTmemFull);
+      ok = mbar_wait(&bars->s_full[sub], (sbase + t) & 1, p.status, kStatusTimeoutTmemFull);
       if (!ok) break;
       tc_fence_after();
       const bool diag = p.causal && (t == i);
@@ -1005,7 +1024,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full[sub]);   // one arrival per warp
     }
-    if (ok) ok = mbar_wait(&bars->done, 0, p.status, kStatusTimeoutTmemFull);
+    if (ok) ok = mbar_wait(&bars->done, it & 1, p.status, kStatusTimeoutTmemFull);
     ok = __all_sync(0xffffffffu, ok);
     if (ok && U > 0) {
       tc_fence_after();
@@ -1033,6 +1052,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         }
       }
     }
+  }
+  // End of tile, without a CTA-wide barrier: the producer waits for `done` before it reloads Q / dO;
+  // the first dQ MMAs of the next tile (which overwrite the accumulator) wait for that tile's first
+  // dS, and a softmax warp writes that only after it has stored its part of this accumulator.
+  sbase += nkv;
+  ++it;
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) break;   // a wait gave up: stop
   }
   tc_fence_before();
   __syncthreads();
@@ -1088,8 +1114,11 @@ cudaError_t launch_bwd(const AttnArgs& a, cudaStream_t st) {
     const int sms = attn_sm_count();
     attn_bwd_dkdv_kernel<D, DT><<<tiles < sms ? tiles : sms, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
   }
-  const int gq = ((a.seq_q + kTile - 1) / kTile) * a.heads * a.batch;
-  attn_bwd_dq_kernel<D, DT><<<gq, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+  {
+    const int tiles = ((a.seq_q + kTile - 1) / kTile) * a.heads * a.batch;
+    const int sms = attn_sm_count();
+    attn_bwd_dq_kernel<D, DT><<<tiles < sms ? tiles : sms, C::kThreads, C::kSmemBytes, st>>>(tq, tk, tv, tdo, a);
+  }
   count_launch(3);
   ETHB_TRY(cudaGetLastError(), "bwd kernel launch");
   return cudaSuccess;
