@@ -469,6 +469,7 @@ struct BwdBarriers {
   uint64_t s_full[2];
   uint64_t p_full[2];
   uint64_t done;
+  uint64_t qdo_full;      // dQ kernel: the Q and dO rows of the tile sit in TMEM
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -856,6 +857,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       mbar_init(&bars->p_full[s], 8);      // both softmax warpgroups work on every sub-tile, one arrival per warp
     }
     mbar_init(&bars->done, 1);
+    mbar_init(&bars->qdo_full, 8);         // one arrival per softmax warp
     fence_mbar_init();
     prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv); prefetch_tmap(&tdo);
   }
@@ -912,10 +914,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, 128, 64);
       const uint32_t idesc_acc = make_idesc_f16(fmt, 0, 1, 128, D);
       // short issue path: tile-origin descriptors once, constants added per MMA
-      const uint64_t dQ0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t dDO0 = make_smem_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t dKk0 = make_smem_desc_sw128(smem_u32(sStage), 16, 1024);          // K-major view
       const uint64_t dKm0 = make_smem_desc_sw128(smem_u32(sStage), 16384, 1024);       // MN-major view
+      // Q and dO are A operands read from TMEM (columns [384, 448) and [448, 512), staged there by
+      // the softmax warps): a score MMA then reads only its 2 KB B operand from shared memory, where
+      // with both operands in shared memory the N = 64 MMAs ran into the 128 B/clk of the SM.
       auto issue_sdp = [&](int u) {
         const int stage = (sbase + (u >> 1)) & 1, sub = u & 1, b = u & 1;
         const uint64_t dK = desc_advance(dKk0, stage * C::kStageBytes + sub * 8192);
@@ -924,17 +927,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + b * 128, desc_advance(dQ0, h * 16384 + k * 32),
-                       desc_advance(dK, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
+            tc_mma_f16_ts(tmem_base + b * 128, tmem_base + 384 + (h * 4 + k) * 8,
+                          desc_advance(dK, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + b * 128 + 64, desc_advance(dDO0, h * 16384 + k * 32),
-                       desc_advance(dV, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
+            tc_mma_f16_ts(tmem_base + b * 128 + 64, tmem_base + 448 + (h * 4 + k) * 8,
+                          desc_advance(dV, h * 16384 + k * 32), idesc_s, (h | k) != 0 ? 1u : 0u);
         tc_commit(&bars->s_full[b]);
       };
-      bool ok = mbar_wait(&bars->res_full, it & 1, p.status, kStatusTimeoutFull);
+      bool ok = mbar_wait(&bars->qdo_full, it & 1, p.status, kStatusTimeoutFull);
       if (ok && U > 0) {
         ok = mbar_wait(&bars->st_full[sbase & 1], (sbase >> 1) & 1, p.status, kStatusTimeoutFull);
         tc_fence_after();
@@ -976,6 +979,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const float lse2 = row_ok ? p.lse[bh + q_row] * kLog2e : INFINITY;
     const float delta = row_ok ? p.delta[bh + q_row] : 0.f;
     bool ok = true;
+    // Stage the tile's rows as TMEM operands: warpgroup 0 copies the Q rows, warpgroup 1 the dO rows,
+    // one thread per row, out of the 128-byte-swizzled tiles the TMA wrote (16-byte chunk c of row r
+    // sits at chunk c ^ (r & 7)); element d of a row lands in TMEM column d / 2 of the operand.
+    ok = mbar_wait(&bars->res_full, it & 1, p.status, kStatusTimeoutFull);
+    if (ok) {
+      const uint8_t* src = (wg == 0 ? sQ : sDO) + r_local * 128;
+      const uint32_t dst = tmem_base + 384 + wg * 64 + lane_bits;
+      __syncwarp();
+#pragma unroll
+      for (int h = 0; h < C::kHalves; ++h)
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          uint32_t v[16];
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int c = g * 4 + c4;
+            const uint4 x = *reinterpret_cast<const uint4*>(src + h * 16384 + ((c ^ (r_local & 7)) << 4));
+            v[c4 * 4 + 0] = x.x; v[c4 * 4 + 1] = x.y; v[c4 * 4 + 2] = x.z; v[c4 * 4 + 3] = x.w;
+          }
+          tmem_st_32x32b_x16(dst + h * 32 + g * 16, v);
+        }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->qdo_full);
+    }
     // Both warpgroups work on every 64-key sub-tile, each on 32 of its columns: the time from
     // "scores ready" to "dS ready" halves, so it fits under the score MMAs of the other buffer and
     // the tensor core seldom waits for it. A warpgroup writes its 16-bit dS over the first half of
