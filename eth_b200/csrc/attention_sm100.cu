@@ -470,6 +470,7 @@ struct BwdBarriers {
   uint64_t p_full[2];
   uint64_t done;
   uint64_t qdo_full;      // dQ kernel: the Q and dO rows of the tile sit in TMEM
+  uint64_t p_early[2];    // dQ kernel: the first 16 of each warpgroup's 32 dS columns are written
   uint32_t tmem_base;
   uint32_t pad;
 };
@@ -855,6 +856,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       mbar_init(&bars->st_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->p_full[s], 8);      // both softmax warpgroups work on every sub-tile, one arrival per warp
+      mbar_init(&bars->p_early[s], 8);
     }
     mbar_init(&bars->done, 1);
     mbar_init(&bars->qdo_full, 8);         // one arrival per softmax warp
@@ -945,14 +947,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       }
       for (int u = 0; u < U && ok; ++u) {
         const int b = u & 1, stage = (sbase + (u >> 1)) & 1, sub = u & 1;
+        // dQ += dS K; keys 0-31 of dS sit at columns [0, 16), keys 32-63 at [32, 48). The first 16
+        // keys of each warpgroup (k-steps 0 and 2) are handed over before the other 16 (1 and 3).
+        const uint64_t dK = desc_advance(dKm0, stage * C::kStageBytes + sub * 8192);
+        ok = mbar_wait(&bars->p_early[b], (sbase + (u >> 1)) & 1, p.status, kStatusTimeoutTmemFull);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; k += 2)
+          tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8,
+                        desc_advance(dK, k * 2048), idesc_acc, (u | k) != 0 ? 1u : 0u);
         ok = mbar_wait(&bars->p_full[b], (sbase + (u >> 1)) & 1, p.status, kStatusTimeoutTmemFull);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t dK = desc_advance(dKm0, stage * C::kStageBytes + sub * 8192);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // dQ += dS K; keys 0-31 of dS sit at columns [0, 16), keys 32-63 at [32, 48)
+        for (int k = 1; k < 4; k += 2)
           tc_mma_f16_ts(tmem_base + 256, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8,
-                        desc_advance(dK, k * 2048), idesc_acc, (u | k) != 0 ? 1u : 0u);
+                        desc_advance(dK, k * 2048), idesc_acc, 1u);
         if (sub == 1) tc_commit(&bars->st_empty[stage]);
         if (u + 2 < U) {
           const int u2 = u + 2;
@@ -1026,28 +1037,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       tmem_ld_wait();
       uint32_t dk[16];
       const float neg_lse = -lse2;
-      if (!(diag || ragged)) {   // the common case carries no mask
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, neg_lse));
-          const float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, neg_lse));
-          dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
-                            DT);
+      for (int part = 0; part < 2; ++part) {   // 16 keys at a time, handed over as soon as they are written
+        if (!(diag || ragged)) {   // the common case carries no mask
+#pragma unroll
+          for (int x = part * 8; x < part * 8 + 8; ++x) {
+            const float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, neg_lse));
+            const float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, neg_lse));
+            dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
+                              DT);
+          }
+        } else {
+#pragma unroll
+          for (int x = part * 8; x < part * 8 + 8; ++x) {
+            const int col = 2 * x;
+            const int kl = sub * 64 + wg * 32 + col;      // key row inside the 128-row tile
+            float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, neg_lse));
+            float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, neg_lse));
+            if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
+            if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
+            dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
+                              DT);
+          }
         }
-      } else {
-#pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int col = 2 * x;
-          const int kl = sub * 64 + wg * 32 + col;      // key row inside the 128-row tile
-          float p0 = exp2f(fmaf(__uint_as_float(rs[2 * x]), sl2, neg_lse));
-          float p1 = exp2f(fmaf(__uint_as_float(rs[2 * x + 1]), sl2, neg_lse));
-          if ((diag && kl > r_local) || (ragged && kv0 + col >= p.seq_k)) p0 = 0.f;
-          if ((diag && kl + 1 > r_local) || (ragged && kv0 + col + 1 >= p.seq_k)) p1 = 0.f;
-          dk[x] = pack_pair(p0 * (__uint_as_float(rd[2 * x]) - delta), p1 * (__uint_as_float(rd[2 * x + 1]) - delta),
-                            DT);
+        if (part == 0) {
+          tmem_st_32x32b_x8(dp_addr, dk);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->p_early[sub]);
         }
       }
-      tmem_st_32x32b_x16(dp_addr, dk);
+      tmem_st_32x32b_x8(dp_addr + 8, dk + 8);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
