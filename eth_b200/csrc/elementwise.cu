@@ -182,11 +182,22 @@ ln_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T
   const int lane = threadIdx.x & 31;
   const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int nwarps = gridDim.x * (blockDim.x >> 5);
-  for (int row = warp; row < rows; row += nwarps) {
-    const T* xr = x + static_cast<int64_t>(row) * kHidden;
-    uint4 raw[VPL];
+  // A warp walks its rows with the next row's loads already in flight while it reduces and stores
+  // the current one (the grid is two CTAs per SM, not one warp per row).
+  uint4 raw[VPL], nxt[VPL];
+  if (warp < rows) {
+    const T* xr = x + static_cast<int64_t>(warp) * kHidden;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) raw[i] = *reinterpret_cast<const uint4*>(xr + (lane + 32 * i) * 8);
+    for (int i = 0; i < VPL; ++i) nxt[i] = *reinterpret_cast<const uint4*>(xr + (lane + 32 * i) * 8);
+  }
+  for (int row = warp; row < rows; row += nwarps) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) raw[i] = nxt[i];
+    if (row + nwarps < rows) {
+      const T* xn = x + static_cast<int64_t>(row + nwarps) * kHidden;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) nxt[i] = *reinterpret_cast<const uint4*>(xn + (lane + 32 * i) * 8);
+    }
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
@@ -976,8 +987,8 @@ cudaError_t layernorm_fwd(const void* x, const void* gamma, const void* beta, vo
                           cudaStream_t st) {
   if (hidden % 8 != 0 || hidden / 8 > 4 * 1024) return cudaErrorInvalidValue;
   if (dtype != kF32 && hidden % 256 == 0 && hidden / 256 <= 16 && hidden / 256 >= 1) {
-    // warp per row, 8 warps per CTA; one row per warp, so the block scheduler balances the SMs
-    const int grid = (rows + 7) / 8;
+    // warp per row, 8 warps per CTA, at most two CTAs per SM: every warp walks several rows
+    const int grid = (rows + 7) / 8 < 2 * kSMs ? (rows + 7) / 8 : 2 * kSMs;
 #define ETHB_LN_WARP(V)                                                                          \
   case V:                                                                                         \
     if (dtype == kBF16)                                                                           \
