@@ -589,6 +589,27 @@ def flash_attention(q, k, v, scale=None, causal=True):
     return _FlashAttnFn.apply(q, k, v, float(scale), bool(causal))
 
 
+def attention_backward_tile_order(num_ctas: int, tiles_per_pair: int, pairs: int, causal: bool = True):
+    """Host mirror of the tile assignment of the two persistent backward kernels
+    (attn_bwd_dkdv_kernel / attn_bwd_dq_kernel in csrc/attention_sm100.cu): tile id T in
+    [0, tiles_per_pair * pairs) means slot T // pairs of (head, batch) pair T % pairs, slot 0 being
+    the heaviest tile under the causal mask; round r hands out ids [r * num_ctas, (r + 1) * num_ctas)
+    in ascending CTA order when r is even and descending when it is odd. Returns, per CTA, the list
+    of (slot, pair, weight) it processes, weight = number of partner tiles the tile meets (key tile j
+    meets tiles_per_pair - j query tiles, and the other way round for the dQ kernel)."""
+    total = tiles_per_pair * pairs
+    out = [[] for _ in range(num_ctas)]
+    rnd = 0
+    while rnd * num_ctas < total:
+        for cta in range(num_ctas):
+            tile = rnd * num_ctas + (num_ctas - 1 - cta if rnd & 1 else cta)
+            if tile < total:
+                slot, pair = divmod(tile, pairs)
+                out[cta].append((slot, pair, tiles_per_pair - slot if causal else tiles_per_pair))
+        rnd += 1
+    return out
+
+
 def unfused_attention(q, k, v, scale=None, causal=True, dropout_p=0.0, seed=0, offset=0):
     """Attention as the four ops of the 13-op layer manifest: scores (batched GEMM) -> fused
     scale + causal-mask softmax -> dropout -> context (batched GEMM). q, k, v: [b, s, h, d]; returns

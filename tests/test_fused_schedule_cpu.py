@@ -1,5 +1,7 @@
-"""The tile schedule of the fused GEMM + reduce-scatter covers every tile exactly once, keeps each
-tile inside its owner's row block and alternates owners along every CTA's tile list."""
+"""Host mirrors of device tile schedules. The fused GEMM + reduce-scatter covers every tile exactly
+once, keeps each tile inside its owner's row block and alternates owners along every CTA's tile
+list; the persistent attention backward kernels visit every tile once, heaviest first, with
+balanced totals per CTA."""
 import pytest
 
 from eth_b200.parallel.fused_tp import reduce_scatter_schedule
@@ -50,3 +52,20 @@ def test_all_reduce_order_puts_own_tiles_last(world, n_tiles):
                 for it in range(n_tiles):
                     if (okey + it) % world == owner:
                         assert peer_pos[it] <= own_pos[it]
+
+
+@pytest.mark.parametrize("ctas,tiles,pairs", [(148, 16, 64), (148, 8, 32), (148, 16, 3), (7, 5, 4), (148, 1, 10)])
+def test_attention_backward_tile_order_covers_every_tile_once_and_is_balanced(ctas, tiles, pairs):
+    from eth_b200.ops.functional import attention_backward_tile_order
+    order = attention_backward_tile_order(ctas, tiles, pairs)
+    seen = sorted((slot, pair) for lst in order for slot, pair, _ in lst)
+    assert seen == [(s, p) for s in range(tiles) for p in range(pairs)]
+    # every CTA walks its tiles heaviest first
+    for lst in order:
+        assert [w for _, _, w in lst] == sorted((w for _, _, w in lst), reverse=True)
+    loads = [sum(w for _, _, w in lst) for lst in order]
+    busy = [x for x in loads if x]
+    # alternating the direction per round keeps the heaviest CTA within one heaviest tile of the mean
+    assert max(busy) - sum(loads) / len(loads) <= tiles
+    if (ctas, tiles, pairs) == (148, 16, 64):      # b4 h16 s2048: 67 vs 51 with plain round-robin
+        assert max(loads) <= 61 and min(loads) >= 57
