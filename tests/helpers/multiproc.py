@@ -1,4 +1,5 @@
-"""Spawn N CPU ranks over Gloo on localhost, run `fn(rank, world, *args)` in each, collect results."""
+"""Spawn N ranks on localhost (Gloo on CPU, or NCCL with one GPU per rank), run `fn(rank, world, *args)`
+in each, collect results."""
 import os
 import socket
 import tempfile
@@ -23,6 +24,10 @@ def _worker(rank, world, port, fn, args, outdir, backend="gloo"):
     torch.set_num_threads(1)
     try:
         if backend == "nccl":
+            # The watchdog below may end a rank that hangs. A rank that dies while its memory is bound
+            # to an NVLink multicast object can raise faults on its peers' GPUs, so the test ranks keep
+            # NCCL off the in-switch (NVLS) path; nothing here measures NCCL's speed.
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             torch.cuda.set_device(rank)
             dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
         else:
