@@ -70,6 +70,29 @@ def test_attention_backward(dtype, B, S, H, D, causal):
     assert _rel_err(gq, rq) < 2e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_backward_more_tiles_than_sms(dtype, causal):
+    """384 key/value tiles and 384 query tiles: the persistent backward kernels take three rounds (the
+    second in reversed CTA order, the third partial), so a CTA processes up to three tiles back to back
+    with its barrier parities, ring positions and accumulators carried from tile to tile."""
+    torch.manual_seed(5)
+    B, S, H, D = 4, 1024, 12, 128
+    qkv = torch.randn(B, S, H, 3, D, device="cuda", dtype=dtype)
+    q, k, v = (qkv[:, :, :, i].detach().requires_grad_(True) for i in range(3))
+    o = ops.flash_attention(q, k, v, causal=causal)
+    do = torch.randn_like(o)
+    gq, gk, gv = torch.autograd.grad(o, (q, k, v), do)
+    native.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qr, kr, vr, 1.0 / math.sqrt(D), causal)
+    rq, rk, rv = torch.autograd.grad(ref, (qr, kr, vr), do.float())
+    assert _rel_err(o, ref) < 2e-2
+    assert _rel_err(gv, rv) < 2e-2
+    assert _rel_err(gk, rk) < 2e-2
+    assert _rel_err(gq, rq) < 2e-2
+
+
 def test_unfused_attention_matches_flash():
     """The four-op attention of the older manifest (library batched GEMMs + this library's softmax)
     agrees with the flash kernel, forward and backward."""
